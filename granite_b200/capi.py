@@ -1,0 +1,222 @@
+"""ctypes binding of include/granite_cuda.h.
+
+Mirrors the attention group of Granite's compute class (include/granite/metal_compute.h:749-920)
+with the same method names and argument order, taking raw device pointers (ints) in place of
+``MTL::Buffer*``.  Every call goes through the C ABI of libgranite_cuda.so; there is no Python or
+CPU implementation behind it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+
+
+def library_path() -> Path:
+    return _PKG / "libgranite_cuda.so"
+
+
+def _load() -> C.CDLL:
+    path = library_path()
+    if not path.exists():
+        raise ImportError(
+            f"{path} is missing: build it with `python -m granite_b200.build` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    return C.CDLL(str(path))
+
+
+lib = _load()
+
+
+class ErrorCode(enum.IntEnum):
+    """granite::ErrorCode values (include/granite/error.h:16-57)."""
+    Success = 0
+    FileNotFound = 1
+    InvalidFormat = 2
+    IOError = 3
+    OutOfMemory = 4
+    AllocationFailed = 5
+    BufferTooSmall = 6
+    BackendNotSupported = 7
+    BackendNotInitialized = 8
+    OperatorNotImplemented = 9
+    ShaderCompilationFailed = 10
+    ExecutionFailed = 11
+    Timeout = 12
+    InvalidShape = 13
+    ShapeMismatch = 14
+    DTypeMismatch = 15
+    InvalidArgument = 16
+    NullPointer = 17
+    InvalidGraph = 18
+    CycleDetected = 19
+    InvalidState = 20
+    UnsupportedModel = 21
+    CorruptedWeights = 22
+    MissingOperator = 23
+    InternalError = 24
+    NotImplemented = 25
+
+
+class GraniteCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        self.code = ErrorCode(code)
+        super().__init__(f"{self.code.name}: {message}")
+
+
+class PagedDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("block_tables", C.c_void_p), ("seq_lens", C.c_void_p), ("output", C.c_void_p),
+        ("batch_size", C.c_uint32), ("num_heads", C.c_uint32), ("num_kv_heads", C.c_uint32),
+        ("head_dim", C.c_uint32), ("block_size", C.c_uint32), ("max_blocks_per_seq", C.c_uint32),
+        ("num_blocks", C.c_uint32), ("seq_len", C.c_uint32), ("scale", C.c_float),
+    ]
+
+
+class AttentionArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("output", C.c_void_p),
+        ("num_heads", C.c_uint32), ("num_kv_heads", C.c_uint32), ("seq_q", C.c_uint32),
+        ("seq_kv", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32),
+        ("q_dtype", C.c_uint32), ("out_dtype", C.c_uint32), ("scale", C.c_float),
+    ]
+
+
+def _sig(name, restype, *argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+_sig("granite_cuda_last_error_message", C.c_char_p)
+_sig("granite_cuda_device_count", C.c_int)
+_sig("granite_cuda_compute_create", C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_void_p))
+_sig("granite_cuda_compute_destroy", None, C.c_void_p)
+_sig("granite_cuda_compute_stream", C.c_void_p, C.c_void_p)
+_sig("granite_cuda_compute_sm_count", C.c_int, C.c_void_p)
+_sig("granite_cuda_sync", C.c_int, C.c_void_p)
+_sig("granite_cuda_get_profiling_stats", None, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64))
+_sig("granite_cuda_malloc", C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p))
+_sig("granite_cuda_free", C.c_int, C.c_void_p, C.c_void_p)
+_sig("granite_cuda_malloc_host", C.c_int, C.c_size_t, C.POINTER(C.c_void_p))
+_sig("granite_cuda_free_host", C.c_int, C.c_void_p)
+_sig("granite_cuda_write_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
+_sig("granite_cuda_read_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
+_sig("granite_cuda_copy_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
+_sig("granite_cuda_memset", C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t)
+_sig("granite_cuda_batched_paged_attention_decode", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs))
+_sig("granite_cuda_multihead_attention", C.c_int, C.c_void_p, C.POINTER(AttentionArgs))
+
+
+def last_error() -> str:
+    return lib.granite_cuda_last_error_message().decode()
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise GraniteCudaError(code, last_error())
+
+
+def _ptr(x) -> int:
+    """Device/host address of a torch tensor, numpy array, or a plain int address."""
+    if x is None:
+        return 0
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+class CudaCompute:
+    """Python face of the compute object, method for method the attention group of MetalCompute.
+
+    ``stream``: a ``cudaStream_t`` as int (e.g. ``torch.cuda.current_stream().cuda_stream``; 0 is
+    taken as the default stream) or ``None`` to let the object create its own stream.
+    """
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._h = C.c_void_p()
+        if stream is None:
+            raw = 0          # NULL: the object creates its own stream
+        elif stream == 0:
+            raw = 1          # cudaStreamLegacy: the handle of the default stream (0 itself means "own")
+        else:
+            raw = stream
+        check(lib.granite_cuda_compute_create(device, C.c_void_p(raw), C.byref(self._h)))
+        self.device = device
+
+    def shutdown(self) -> None:
+        if self._h:
+            lib.granite_cuda_compute_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.shutdown()
+        except Exception:
+            pass
+
+    @property
+    def handle(self) -> C.c_void_p:
+        return self._h
+
+    @property
+    def stream(self) -> int:
+        return lib.granite_cuda_compute_stream(self._h) or 0
+
+    @property
+    def sm_count(self) -> int:
+        return lib.granite_cuda_compute_sm_count(self._h)
+
+    def sync(self) -> None:
+        check(lib.granite_cuda_sync(self._h))
+
+    def get_profiling_stats(self) -> tuple[int, int]:
+        d, s = C.c_uint64(), C.c_uint64()
+        lib.granite_cuda_get_profiling_stats(self._h, C.byref(d), C.byref(s))
+        return d.value, s.value
+
+    # ---- raw buffers
+    def create_buffer(self, size: int) -> int:
+        p = C.c_void_p()
+        check(lib.granite_cuda_malloc(self._h, size, C.byref(p)))
+        return p.value
+
+    def destroy_buffer(self, ptr: int) -> None:
+        check(lib.granite_cuda_free(self._h, C.c_void_p(ptr)))
+
+    def write_buffer(self, dev_ptr, host, nbytes: int) -> None:
+        check(lib.granite_cuda_write_buffer(self._h, C.c_void_p(_ptr(dev_ptr)), C.c_void_p(_ptr(host)), nbytes))
+
+    def read_buffer(self, host, dev_ptr, nbytes: int) -> None:
+        check(lib.granite_cuda_read_buffer(self._h, C.c_void_p(_ptr(host)), C.c_void_p(_ptr(dev_ptr)), nbytes))
+
+    # ---- attention group
+    def batched_paged_attention_decode(self, Q, K_cache, V_cache, block_tables, seq_lens, output,
+                                       batch_size, num_heads, num_kv_heads, head_dim, block_size,
+                                       max_blocks_per_seq, scale, *, num_blocks, seq_len=0) -> None:
+        a = PagedDecodeArgs(_ptr(Q), _ptr(K_cache), _ptr(V_cache), _ptr(block_tables), _ptr(seq_lens),
+                            _ptr(output), batch_size, num_heads, num_kv_heads, head_dim, block_size,
+                            max_blocks_per_seq, num_blocks, seq_len, scale)
+        check(lib.granite_cuda_batched_paged_attention_decode(self._h, C.byref(a)))
+
+    def paged_attention_decode(self, Q, K_cache, V_cache, block_table, output, num_heads,
+                               num_kv_heads, seq_len, head_dim, block_size, scale, *, num_blocks,
+                               num_logical_blocks=None) -> None:
+        nlb = num_logical_blocks or (seq_len + block_size - 1) // block_size
+        self.batched_paged_attention_decode(Q, K_cache, V_cache, block_table, None, output, 1,
+                                            num_heads, num_kv_heads, head_dim, block_size, max(nlb, 1),
+                                            scale, num_blocks=num_blocks, seq_len=seq_len)
+
+    def multihead_attention(self, Q, K, V, output, num_heads, num_kv_heads, seq_q, seq_kv, head_dim,
+                            scale, max_seq=0, *, q_dtype=0, out_dtype=0) -> None:
+        a = AttentionArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), num_heads, num_kv_heads, seq_q,
+                          seq_kv, head_dim, max_seq, q_dtype, out_dtype, scale)
+        check(lib.granite_cuda_multihead_attention(self._h, C.byref(a)))

@@ -1,0 +1,270 @@
+// extern "C" entry points declared in include/granite_cuda.h: compute-object lifecycle, raw
+// buffers, and the attention calls.  Errors are values (granite::ErrorCode numbers), never
+// exceptions; there is no CPU fallback anywhere below this boundary.
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "compute_internal.h"
+
+namespace gb200 {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is fetched at run time so that the library links (and loads) on
+// machines without libcuda; it simply cannot compute there.
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return (EncodeTiledFn) nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+}  // namespace gb200
+
+using namespace gb200;
+
+int granite_cuda_compute::ensure_scratch(size_t bytes) {
+    if (bytes <= scratch_bytes) return GRANITE_CUDA_SUCCESS;
+    // growing: make sure nothing in flight still uses the old arena
+    GB_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (scratch) cudaFree(scratch);
+    scratch = nullptr;
+    scratch_bytes = 0;
+    size_t want = bytes + bytes / 4;
+    cudaError_t e = cudaMalloc(&scratch, want);
+    if (e != cudaSuccess) return fail(GRANITE_CUDA_OUT_OF_MEMORY, "scratch arena: cudaMalloc failed");
+    scratch_bytes = want;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
+                                                       uint64_t stride1_bytes, uint32_t box0,
+                                                       uint32_t box1, int swizzle_bytes) {
+    TensorMapKey key{base, dim0, dim1, 0, stride1_bytes, 0, box0, box1, 0, swizzle_bytes, 2};
+    auto it = tensor_maps.find(key);
+    if (it != tensor_maps.end()) return &it->second;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return nullptr;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (stride1_bytes & 15) != 0) {
+        set_error("tensor map: base address and row pitch must be 16-byte aligned");
+        return nullptr;
+    }
+    CUtensorMap map;
+    cuuint64_t dims[2] = {dim0, dim1};
+    cuuint64_t strides[1] = {stride1_bytes};
+    cuuint32_t box[2] = {box0, box1};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+        return nullptr;
+    }
+    if (tensor_maps.size() > 256) tensor_maps.clear();  // callers re-create what they need
+    auto ins = tensor_maps.emplace(key, map);
+    return &ins.first->second;
+}
+
+extern "C" {
+
+const char* granite_cuda_last_error_message(void) { return g_last_error.c_str(); }
+
+int granite_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int granite_cuda_compute_create(int device, void* stream, granite_cuda_compute_t** out) {
+    if (!out) return fail(GRANITE_CUDA_NULL_POINTER, "compute_create: out is null");
+    *out = nullptr;
+    int n = granite_cuda_device_count();
+    if (n <= 0) return fail(GRANITE_CUDA_BACKEND_NOT_INITIALIZED, "no CUDA device is visible; this backend has no CPU fallback");
+    if (device < 0 || device >= n) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "compute_create: device index out of range");
+    GB_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    GB_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(GRANITE_CUDA_BACKEND_NOT_SUPPORTED,
+                    std::string("this library is built for sm_100a only; device is ") + prop.name);
+    auto* c = new (std::nothrow) granite_cuda_compute();
+    if (!c) return fail(GRANITE_CUDA_OUT_OF_MEMORY, "compute_create: host allocation failed");
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (stream) {
+        c->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete c;
+            return fail(GRANITE_CUDA_EXECUTION_FAILED, "compute_create: cudaStreamCreate failed");
+        }
+        c->owns_stream = true;
+    }
+    if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
+        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream) != cudaSuccess) {
+        granite_cuda_compute_destroy(c);
+        return fail(GRANITE_CUDA_OUT_OF_MEMORY, "compute_create: status word allocation failed");
+    }
+    *c->h_status = 0;
+    *out = c;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+void granite_cuda_compute_destroy(granite_cuda_compute_t* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->scratch) cudaFree(c->scratch);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->h_status) cudaFreeHost(c->h_status);
+    if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+void* granite_cuda_compute_stream(granite_cuda_compute_t* c) { return c ? c->stream : nullptr; }
+int granite_cuda_compute_sm_count(granite_cuda_compute_t* c) { return c ? c->sm_count : 0; }
+
+int granite_cuda_sync(granite_cuda_compute_t* c) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "sync: compute object is null");
+    c->syncs++;
+    GB_CUDA_TRY(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    GB_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    int st = *c->h_status;
+    if (st == 0) return GRANITE_CUDA_SUCCESS;
+    GB_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
+    if (st & kStatusTimeout) return fail(GRANITE_CUDA_TIMEOUT, "a device-side wait ran out (status " + std::to_string(st) + ")");
+    if (st & kStatusBadTable) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a block-table entry was outside the pool");
+    if (st & kStatusBadSeqLen) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a sequence length was negative or exceeded its block table");
+    if (st & kStatusBadParent) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a tree parent index was out of range");
+    return fail(GRANITE_CUDA_EXECUTION_FAILED, "device status " + std::to_string(st));
+}
+
+void granite_cuda_get_profiling_stats(granite_cuda_compute_t* c, uint64_t* dispatches, uint64_t* syncs) {
+    if (dispatches) *dispatches = c ? c->dispatches : 0;
+    if (syncs) *syncs = c ? c->syncs : 0;
+}
+
+int granite_cuda_malloc(granite_cuda_compute_t* c, size_t bytes, void** dev_ptr) {
+    if (!c || !dev_ptr) return fail(GRANITE_CUDA_NULL_POINTER, "malloc: null argument");
+    *dev_ptr = nullptr;
+    if (bytes == 0) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "malloc: zero bytes");
+    cudaSetDevice(c->device);
+    if (cudaMalloc(dev_ptr, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(GRANITE_CUDA_OUT_OF_MEMORY, "cudaMalloc of " + std::to_string(bytes) + " bytes failed");
+    }
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_free(granite_cuda_compute_t* c, void* dev_ptr) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "free: compute object is null");
+    if (!dev_ptr) return GRANITE_CUDA_SUCCESS;
+    // tensor maps that point into the buffer are dropped with it
+    for (auto it = c->tensor_maps.begin(); it != c->tensor_maps.end();)
+        it = (it->first.base == dev_ptr) ? c->tensor_maps.erase(it) : std::next(it);
+    GB_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    GB_CUDA_TRY(cudaFree(dev_ptr));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_malloc_host(size_t bytes, void** host_ptr) {
+    if (!host_ptr) return fail(GRANITE_CUDA_NULL_POINTER, "malloc_host: null argument");
+    *host_ptr = nullptr;
+    if (cudaMallocHost(host_ptr, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(GRANITE_CUDA_OUT_OF_MEMORY, "cudaMallocHost failed");
+    }
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_free_host(void* host_ptr) {
+    if (host_ptr) GB_CUDA_TRY(cudaFreeHost(host_ptr));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_write_buffer(granite_cuda_compute_t* c, void* dev_dst, const void* host_src, size_t bytes) {
+    if (!c || !dev_dst || !host_src) return fail(GRANITE_CUDA_NULL_POINTER, "write_buffer: null argument");
+    GB_CUDA_TRY(cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, c->stream));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_read_buffer(granite_cuda_compute_t* c, void* host_dst, const void* dev_src, size_t bytes) {
+    if (!c || !host_dst || !dev_src) return fail(GRANITE_CUDA_NULL_POINTER, "read_buffer: null argument");
+    GB_CUDA_TRY(cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, c->stream));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_copy_buffer(granite_cuda_compute_t* c, void* dev_dst, const void* dev_src, size_t bytes) {
+    if (!c || !dev_dst || !dev_src) return fail(GRANITE_CUDA_NULL_POINTER, "copy_buffer: null argument");
+    GB_CUDA_TRY(cudaMemcpyAsync(dev_dst, dev_src, bytes, cudaMemcpyDeviceToDevice, c->stream));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_memset(granite_cuda_compute_t* c, void* dev_dst, int byte, size_t bytes) {
+    if (!c || !dev_dst) return fail(GRANITE_CUDA_NULL_POINTER, "memset: null argument");
+    GB_CUDA_TRY(cudaMemsetAsync(dev_dst, byte, bytes, c->stream));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c, const GraniteCudaPagedDecodeArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "paged decode: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_paged_decode(c, *args, false, 0);
+}
+
+int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCudaAttentionArgs* a) {
+    if (!c || !a) return fail(GRANITE_CUDA_NULL_POINTER, "multihead_attention: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    const uint32_t max_seq = a->max_seq ? a->max_seq : a->seq_kv;
+    if (a->seq_q == 1) {
+        if (a->q_dtype != 0 || a->out_dtype != 0)
+            return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode takes fp32 Q and writes fp32");
+        if (a->seq_kv > max_seq) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "seq_kv exceeds max_seq");
+        GraniteCudaPagedDecodeArgs d{};
+        d.q = static_cast<const float*>(a->q);
+        d.k_cache = a->k;
+        d.v_cache = a->v;
+        d.output = static_cast<float*>(a->output);
+        d.batch_size = 1;
+        d.num_heads = a->num_heads;
+        d.num_kv_heads = a->num_kv_heads;
+        d.head_dim = a->head_dim;
+        d.block_size = 16;
+        d.seq_len = a->seq_kv;
+        d.scale = a->scale;
+        return launch_paged_decode(c, d, true, max_seq);
+    }
+    return fail(GRANITE_CUDA_NOT_IMPLEMENTED, "prefill is not built into this library yet");
+}
+
+}  // extern "C"

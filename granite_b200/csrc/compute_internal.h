@@ -1,0 +1,78 @@
+// Internal state behind the opaque granite_cuda_compute_t handle: device, stream, the device
+// status word, cached TMA tensor maps and the scratch arena that the split-KV decode and the
+// tensor-core kernels carve their partials from.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <tuple>
+
+#include "../../include/granite_cuda.h"
+
+namespace gb200 {
+
+// Bits of the device status word.
+enum : int {
+    kStatusTimeout = 1,      // a bounded device-side wait ran out
+    kStatusBadTable = 2,     // a block-table entry outside [0, num_blocks)
+    kStatusBadSeqLen = 4,    // a sequence length outside [0, max_blocks*block_size]
+    kStatusBadParent = 8,    // a tree parent index outside [-1, num_nodes)
+};
+
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+
+#define GB_CUDA_TRY(expr)                                                                  \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return ::gb200::fail(_e == cudaErrorMemoryAllocation ? GRANITE_CUDA_OUT_OF_MEMORY \
+                                                                 : GRANITE_CUDA_EXECUTION_FAILED, \
+                                 std::string(#expr) + ": " + cudaGetErrorString(_e));      \
+    } while (0)
+
+struct TensorMapKey {
+    const void* base;
+    uint64_t dim0, dim1, dim2;
+    uint64_t stride1, stride2;
+    uint32_t box0, box1, box2;
+    int swizzle;
+    int rank;
+    bool operator<(const TensorMapKey& o) const {
+        return std::tie(base, dim0, dim1, dim2, stride1, stride2, box0, box1, box2, swizzle, rank) <
+               std::tie(o.base, o.dim0, o.dim1, o.dim2, o.stride1, o.stride2, o.box0, o.box1, o.box2,
+                        o.swizzle, o.rank);
+    }
+};
+
+}  // namespace gb200
+
+struct granite_cuda_compute {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int* d_status = nullptr;  // device status word
+    int* h_status = nullptr;  // pinned mirror
+    uint64_t dispatches = 0;
+    uint64_t syncs = 0;
+    // scratch arena (grown on demand, never shrunk)
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    std::map<gb200::TensorMapKey, CUtensorMap> tensor_maps;
+
+    int ensure_scratch(size_t bytes);
+    // fp16 tensor maps; returns nullptr (and sets the error message) on failure.
+    const CUtensorMap* tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
+                                     uint64_t stride1_bytes, uint32_t box0, uint32_t box1,
+                                     int swizzle_bytes);
+};
+
+namespace gb200 {
+int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
+                        bool contiguous, uint32_t max_seq);
+}  // namespace gb200

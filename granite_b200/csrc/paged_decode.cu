@@ -1,0 +1,628 @@
+// Split-KV flash-decode over the block-table KV cache (and, with an identity table, over the
+// contiguous cache).  HBM-bound: every K/V byte of a sequence is read exactly once for all the
+// query heads that share it.
+//
+// Replaces paged_flash_attention_decode_d128 / batched_paged_attention_decode
+// (src/backend/metal/kernels/metal_shaders_attention.h:3660, :2186) and
+// flash_attention_decode_d128 (:2982); the arithmetic it must match is the CPU loop
+// src/llm/transformer.mm:1779-1840 applied to rows fetched by the paged addressing rule
+// (include/granite/metal_compute.h:853-861).
+//
+// Shape of the work.  All pages of all sequences form one linear list (head-tile major, then
+// sequence, then page).  The list is cut into one equal contiguous range per CTA (one CTA per
+// SM), so the load is balanced to a page whatever the length distribution.  A range that holds
+// a whole sequence writes its output directly; a sequence cut by a range boundary leaves
+// un-normalised partials (m, l, o) that decode_merge_kernel combines.
+//
+// Inside a CTA: one producer warp walks the block table and has TMA copy each page - 16 rows of
+// up to 8 KV heads, one contiguous 32 KB piece of the pool - into a ring of shared-memory slots
+// (128-byte swizzle, mbarrier full/empty pairs).  Eight consumer warps each own one KV head of
+// the tile: S^T = K * Q^T and O^T += V^T * P^T on mma.sync m16n8k16 with the group's query heads
+// as the 8-wide N dimension, online softmax across the warp by shuffles, fp32 state.  Q and P
+// are split into fp16 hi + lo parts so the fp32 inputs of the reference are not rounded.
+#include "compute_internal.h"
+#include "ptx.cuh"
+
+namespace gb200 {
+
+constexpr int kHeadDim = 128;
+constexpr int kPageTokens = 16;
+constexpr int kConsumerWarps = 8;
+constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
+constexpr int kHeadPageBytes = kPageTokens * kHeadDim * 2;  // 4096: one head's K (or V) page
+constexpr int kMaxSlots = 16;
+
+struct DecodeParams {
+    const float* q;
+    const int32_t* tables;
+    const int32_t* seq_lens;
+    float* out;
+    int batch, num_heads, num_kv_heads, group;
+    int max_blocks, num_blocks;
+    int uniform_len;      // used when seq_lens == nullptr
+    int tile_heads;       // KV heads per CTA tile (<= 8)
+    int n_head_tiles;     // num_kv_heads / tile_heads
+    int heads_per_warp;   // query heads of the group owned by one consumer warp
+    int active_warps;     // consumer warps that own at least one query head
+    int slots;            // ring depth
+    int n_ctas;
+    int contiguous;       // 1: k/v are [batch, Hkv, max_seq, D], table is the identity
+    int max_seq;
+    float scale_log2;     // scale * log2(e)
+    int* status;
+    int* page_prefix;     // [batch + 1]
+    int* cta_first_seq;   // [n_ctas]
+    float* part_o;        // [2 * n_ctas][num_heads][128]
+    float2* part_ml;      // [2 * n_ctas][num_heads]
+};
+
+__device__ __forceinline__ long long range_start(long long total, int n_ctas, int c) {
+    return (total * c) / n_ctas;
+}
+
+// ------------------------------------------------------------------------------------ plan
+// One block.  Builds the page prefix sum, validates lengths, zeroes the rows of empty
+// sequences and finds the first sequence of every CTA's range.
+__global__ void __launch_bounds__(1024) decode_plan_kernel(DecodeParams p) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        carry = 0;
+        p.page_prefix[0] = 0;
+    }
+    __syncthreads();
+    const int max_len = p.contiguous ? p.max_seq : p.max_blocks * kPageTokens;
+    for (int base = 0; base < p.batch; base += 1024) {
+        int b = base + tid;
+        int pages = 0;
+        if (b < p.batch) {
+            int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;
+            if (len < 0 || len > max_len) {
+                atomicOr(p.status, kStatusBadSeqLen);
+                len = 0;
+            }
+            pages = (len + kPageTokens - 1) / kPageTokens;
+        }
+        int incl = pages;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int v = __shfl_up_sync(0xffffffffu, w, o);
+                if (lane >= o) w += v;
+            }
+            warp_sums[lane] = w;
+        }
+        __syncthreads();
+        int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0);
+        if (b < p.batch) p.page_prefix[b + 1] = before + incl;
+        __syncthreads();
+        if (tid == 1023) carry = before + incl;
+        __syncthreads();
+    }
+    __threadfence_block();
+    __syncthreads();
+    const int total = p.page_prefix[p.batch];
+    // rows of empty sequences are defined to be zero (rare: one thread per such row)
+    for (int b = tid; b < p.batch; b += 1024) {
+        if (p.page_prefix[b + 1] == p.page_prefix[b]) {
+            float* o = p.out + (size_t)b * p.num_heads * kHeadDim;
+            for (int i = 0; i < p.num_heads * kHeadDim; i++) o[i] = 0.f;
+        }
+    }
+    const long long T = (long long)total * p.n_head_tiles;
+    for (int c = tid; c < p.n_ctas; c += 1024) {
+        int first = 0;
+        if (total > 0) {
+            long long P0 = range_start(T, p.n_ctas, c);
+            int p0 = (int)(P0 % total);
+            // largest b with prefix[b] <= p0 and prefix[b+1] > p0
+            int lo = 0, hi = p.batch;  // invariant: prefix[lo] <= p0 < prefix[hi]
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (p.page_prefix[mid] <= p0) lo = mid; else hi = mid;
+            }
+            first = lo;
+        }
+        p.cta_first_seq[c] = first;
+    }
+}
+
+// ------------------------------------------------------------------------------------ main
+struct Segment {
+    int seq;         // sequence index
+    int head_tile;   // which tile of KV heads
+    int page_begin;  // first logical page of the segment inside the sequence
+    int npages;      // pages in the segment
+    int seq_pages;   // pages of the whole sequence
+    int slot;        // partial slot (2*cta or 2*cta+1); -1 when the segment is the whole sequence
+};
+
+// Walks the CTA's range; every role calls it with the same arguments and sees the same segments.
+struct SegmentWalker {
+    long long P, P1;
+    int total, batch, b, cta, index;
+    const int* prefix;
+    __device__ SegmentWalker(const DecodeParams& p, int cta_) {
+        prefix = p.page_prefix;
+        batch = p.batch;
+        total = prefix[batch];
+        cta = cta_;
+        long long T = (long long)total * p.n_head_tiles;
+        P = range_start(T, p.n_ctas, cta);
+        P1 = range_start(T, p.n_ctas, cta + 1);
+        b = p.cta_first_seq[cta];
+        index = 0;
+    }
+    __device__ bool next(Segment& s) {
+        if (P >= P1) return false;
+        int ht = (int)(P / total);
+        int pg = (int)(P - (long long)ht * total);
+        if (pg == 0) b = 0;
+        while (prefix[b + 1] <= pg) b++;  // skips empty sequences; prefix[batch] == total > pg
+        int seq_begin = prefix[b], seq_end = prefix[b + 1];
+        long long room = P1 - P;
+        int end = seq_end;
+        if ((long long)(end - pg) > room) end = pg + (int)room;
+        s.seq = b;
+        s.head_tile = ht;
+        s.page_begin = pg - seq_begin;
+        s.npages = end - pg;
+        s.seq_pages = seq_end - seq_begin;
+        bool whole = (pg == seq_begin) && (end == seq_end);
+        s.slot = whole ? -1 : 2 * cta + (index == 0 ? 0 : 1);
+        index++;
+        P += s.npages;
+        return true;
+    }
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle wants 1024-byte aligned slots
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int slot_bytes = p.tile_heads * kHeadPageBytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)p.slots * slot_bytes);
+    uint64_t* empty = full + kMaxSlots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxSlots);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < p.slots; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], p.active_warps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (p.page_prefix[p.batch] == 0) return;
+
+    SegmentWalker walk(p, blockIdx.x);
+    Segment seg;
+    int slot = 0;
+    uint32_t phase = 0;
+    auto advance = [&]() {
+        if (++slot == p.slots) {
+            slot = 0;
+            phase ^= 1;
+        }
+    };
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer warp
+        if (lane == 0) {
+            tma_prefetch_desc(&kmap);
+            tma_prefetch_desc(&vmap);
+        }
+        const int nbox = p.tile_heads * 2;  // (head, 64-half chunk) boxes per page per tensor
+        const bool is_v = lane >= 16;
+        const int box = lane & 15;
+        const CUtensorMap* map = is_v ? &vmap : &kmap;
+        while (walk.next(seg)) {
+            const int head0 = seg.head_tile * p.tile_heads;
+            for (int j0 = 0; j0 < seg.npages; j0 += 32) {
+                int e = 0;
+                if (j0 + lane < seg.npages) {
+                    int logical = seg.page_begin + j0 + lane;
+                    if (p.contiguous) {
+                        e = logical;
+                    } else {
+                        e = p.tables[(size_t)seg.seq * p.max_blocks + logical];
+                        if (e < 0 || e >= p.num_blocks) {
+                            atomicOr(p.status, kStatusBadTable);
+                            e = 0;
+                        }
+                    }
+                }
+                const int n = min(32, seg.npages - j0);
+                for (int jj = 0; jj < n; jj++) {
+                    const int entry = __shfl_sync(0xffffffffu, e, jj);
+                    int slot_k = slot; uint32_t ph_k = phase; advance();
+                    int slot_v = slot; uint32_t ph_v = phase; advance();
+                    int ok = 1;
+                    if (lane == 0) {
+                        ok = mbar_wait(&empty[slot_k], ph_k ^ 1, abort_flag) &&
+                             mbar_wait(&empty[slot_v], ph_v ^ 1, abort_flag);
+                        if (ok) {
+                            mbar_arrive_expect_tx(&full[slot_k], slot_bytes);
+                            mbar_arrive_expect_tx(&full[slot_v], slot_bytes);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) {
+                        if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                        return;
+                    }
+                    if (box < nbox) {
+                        const int h = box >> 1, chunk = box & 1;
+                        const int my_slot = is_v ? slot_v : slot_k;
+                        uint8_t* dst = smem + (size_t)my_slot * slot_bytes + h * kHeadPageBytes + chunk * 2048;
+                        int x, y;
+                        if (p.contiguous) {
+                            x = chunk * 64;
+                            y = (seg.seq * p.num_kv_heads + head0 + h) * p.max_seq + entry * kPageTokens;
+                        } else {
+                            x = (head0 + h) * kHeadDim + chunk * 64;
+                            y = entry * kPageTokens;
+                        }
+                        tma_load_2d(dst, map, &full[my_slot], x, y);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps
+    const int kvh_local = warp % p.tile_heads;
+    const int sub = warp / p.tile_heads;
+    const int first_q = sub * p.heads_per_warp;  // first query head of the group owned here
+    if (first_q >= p.group) return;              // idle warp (not counted in active_warps)
+    const int n_q = min(p.heads_per_warp, p.group - first_q);
+    const int g = lane >> 2, t = lane & 3;
+
+    // per-lane shared-memory offsets of the ldmatrix rows
+    const int k_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int k_unit = lane >> 4;
+    const int v_row = (lane & 7) + ((lane >> 4) & 1) * 8;
+    const int v_unit = (lane >> 3) & 1;
+    const uint32_t smem_base = smem_u32(smem) + kvh_local * kHeadPageBytes;
+
+    while (walk.next(seg)) {
+        const int kvh = seg.head_tile * p.tile_heads + kvh_local;
+        const int hq0 = kvh * p.group + first_q;
+        const int len = p.seq_lens ? p.seq_lens[seg.seq] : p.uniform_len;
+
+        // Q^T as the B operand: lane (g,t) holds head nt*8+g, dims ks*16 + {2t,2t+1, 2t+8,2t+9}
+        uint32_t qhi[NT][8][2], qlo[NT][8][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int n = nt * 8 + g;
+            const bool valid = n < n_q;
+            const float* qp = p.q + ((size_t)seg.seq * p.num_heads + hq0 + (valid ? n : 0)) * kHeadDim;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    float2 v = make_float2(0.f, 0.f);
+                    if (valid) v = *reinterpret_cast<const float2*>(qp + ks * 16 + half * 8 + 2 * t);
+                    v.x *= p.scale_log2;
+                    v.y *= p.scale_log2;
+                    __half2 hi = __floats2half2_rn(v.x, v.y);
+                    float2 back = __half22float2(hi);
+                    __half2 lo = __floats2half2_rn(v.x - back.x, v.y - back.y);
+                    qhi[nt][ks][half] = *reinterpret_cast<uint32_t*>(&hi);
+                    qlo[nt][ks][half] = *reinterpret_cast<uint32_t*>(&lo);
+                }
+            }
+        }
+
+        float m_run[NT][2], l_run[NT][2], o[NT][8][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            m_run[nt][0] = m_run[nt][1] = -INFINITY;
+            l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) o[nt][mt][i] = 0.f;
+        }
+
+        for (int j = 0; j < seg.npages; j++) {
+            const int logical = seg.page_begin + j;
+            const int ntok = min(kPageTokens, len - logical * kPageTokens);
+            const int slot_k = slot; const uint32_t ph_k = phase; advance();
+            const int slot_v = slot; const uint32_t ph_v = phase; advance();
+
+            // ---- S^T = K Q^T
+            if (!mbar_wait(&full[slot_k], ph_k, abort_flag)) {
+                if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                return;
+            }
+            float sa[NT][4], sb[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) sa[nt][i] = sb[nt][i] = 0.f;
+            const uint32_t kbase = smem_base + slot_k * slot_bytes + k_row * 128;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                uint32_t a[4];
+                const int unit = (ks & 3) * 2 + k_unit;
+                ldmatrix_x4(a, kbase + (ks >> 2) * 2048 + ((unit ^ (k_row & 7)) << 4));
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    mma_16816(sa[nt], a, qhi[nt][ks][0], qhi[nt][ks][1]);
+                    mma_16816(sb[nt], a, qlo[nt][ks][0], qlo[nt][ks][1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot_k]);
+
+            // ---- online softmax (lane holds tokens g, g+8 for heads 2t, 2t+1 of each n-tile)
+            uint32_t phi[NT][2], plo[NT][2];
+            float alpha[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float s0 = sa[nt][0] + sb[nt][0], s1 = sa[nt][1] + sb[nt][1];
+                float s2 = sa[nt][2] + sb[nt][2], s3 = sa[nt][3] + sb[nt][3];
+                if (g >= ntok) s0 = s1 = -INFINITY;
+                if (g + 8 >= ntok) s2 = s3 = -INFINITY;
+                float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+                for (int sh = 4; sh < 32; sh <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+                }
+                const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+                alpha[nt][0] = fast_exp2(m_run[nt][0] - mn0);
+                alpha[nt][1] = fast_exp2(m_run[nt][1] - mn1);
+                m_run[nt][0] = mn0;
+                m_run[nt][1] = mn1;
+                const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1);
+                const float p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
+                l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + p0 + p2;
+                l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + p1 + p3;
+                __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+                float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+                __half2 l01 = __floats2half2_rn(p0 - b01.x, p1 - b01.y);
+                __half2 l23 = __floats2half2_rn(p2 - b23.x, p3 - b23.y);
+                // C-fragment layout -> B-fragment layout: transpose the 8x8 (token, head) blocks
+                phi[nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h01));
+                phi[nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h23));
+                plo[nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l01));
+                plo[nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l23));
+#pragma unroll
+                for (int mt = 0; mt < 8; mt++) {
+                    o[nt][mt][0] *= alpha[nt][0];
+                    o[nt][mt][1] *= alpha[nt][1];
+                    o[nt][mt][2] *= alpha[nt][0];
+                    o[nt][mt][3] *= alpha[nt][1];
+                }
+            }
+
+            // ---- O^T += V^T P^T
+            if (!mbar_wait(&full[slot_v], ph_v, abort_flag)) {
+                if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                return;
+            }
+            const uint32_t vslot = smem_base + slot_v * slot_bytes;
+            if (ntok < kPageTokens) {
+                // rows past the sequence end may hold anything (even NaN): zero them so that
+                // 0 * garbage cannot poison the accumulators
+                uint8_t* vptr = smem + (size_t)slot_v * slot_bytes + kvh_local * kHeadPageBytes;
+                for (int i = lane; i < (kPageTokens - ntok) * 16; i += 32) {
+                    int r = ntok + (i >> 4), u = i & 15;  // 16 units of 16 B per 256-byte row
+                    int chunk = u >> 3, unit = u & 7;
+                    *reinterpret_cast<uint4*>(vptr + chunk * 2048 + r * 128 + ((unit ^ (r & 7)) << 4)) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+            const uint32_t vbase = vslot + v_row * 128;
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++) {
+                uint32_t a[4];
+                const int unit = (mt & 3) * 2 + v_unit;
+                ldmatrix_x4_trans(a, vbase + (mt >> 2) * 2048 + ((unit ^ (v_row & 7)) << 4));
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    mma_16816(o[nt][mt], a, phi[nt][0], phi[nt][1]);
+                    mma_16816(o[nt][mt], a, plo[nt][0], plo[nt][1]);
+                }
+            }
+            __syncwarp();
+            if (ntok < kPageTokens) fence_proxy_async_smem();
+            if (lane == 0) mbar_arrive(&empty[slot_v]);
+        }
+
+        // ---- segment result
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                l_run[nt][0] += __shfl_xor_sync(0xffffffffu, l_run[nt][0], sh);
+                l_run[nt][1] += __shfl_xor_sync(0xffffffffu, l_run[nt][1], sh);
+            }
+#pragma unroll
+            for (int jx = 0; jx < 2; jx++) {
+                const int n = nt * 8 + 2 * t + jx;
+                if (n >= n_q) continue;
+                const int hq = hq0 + n;
+                if (seg.slot < 0) {
+                    const float inv = 1.0f / l_run[nt][jx];
+                    float* dst = p.out + ((size_t)seg.seq * p.num_heads + hq) * kHeadDim;
+#pragma unroll
+                    for (int mt = 0; mt < 8; mt++) {
+                        dst[mt * 16 + g] = o[nt][mt][jx] * inv;
+                        dst[mt * 16 + g + 8] = o[nt][mt][2 + jx] * inv;
+                    }
+                } else {
+                    float* dst = p.part_o + ((size_t)seg.slot * p.num_heads + hq) * kHeadDim;
+#pragma unroll
+                    for (int mt = 0; mt < 8; mt++) {
+                        dst[mt * 16 + g] = o[nt][mt][jx];
+                        dst[mt * 16 + g + 8] = o[nt][mt][2 + jx];
+                    }
+                    if (g == 0)
+                        p.part_ml[(size_t)seg.slot * p.num_heads + hq] = make_float2(m_run[nt][jx], l_run[nt][jx]);
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ merge
+// grid (batch, n_head_tiles), 128 threads (one per output dim).  Combines the partials of a
+// sequence that was cut by CTA range boundaries:  out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c.
+__global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
+    const int b = blockIdx.x, ht = blockIdx.y, d = threadIdx.x;
+    const int total = p.page_prefix[p.batch];
+    if (total == 0) return;
+    const int s0 = p.page_prefix[b], s1 = p.page_prefix[b + 1];
+    if (s1 == s0) return;
+    const long long T = (long long)total * p.n_head_tiles;
+    const long long A = (long long)ht * total + s0, B = (long long)ht * total + s1;  // [A, B)
+    auto cta_of = [&](long long P) {
+        int c = (int)((P * p.n_ctas) / T);
+        if (c >= p.n_ctas) c = p.n_ctas - 1;
+        while (c + 1 < p.n_ctas && range_start(T, p.n_ctas, c + 1) <= P) c++;
+        while (c > 0 && range_start(T, p.n_ctas, c) > P) c--;
+        return c;
+    };
+    const int c_lo = cta_of(A), c_hi = cta_of(B - 1);
+    if (c_lo == c_hi) return;  // whole sequence inside one range: already final
+    const int heads_in_tile = p.tile_heads * p.group;
+    for (int hh = 0; hh < heads_in_tile; hh++) {
+        const int hq = ht * heads_in_tile + hh;
+        float M = -INFINITY;
+        for (int c = c_lo; c <= c_hi; c++) {
+            if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;  // empty range
+            const int slot = 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1);
+            M = fmaxf(M, p.part_ml[(size_t)slot * p.num_heads + hq].x);
+        }
+        float acc = 0.f, L = 0.f;
+        for (int c = c_lo; c <= c_hi; c++) {
+            if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
+            const int slot = 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1);
+            const float2 ml = p.part_ml[(size_t)slot * p.num_heads + hq];
+            const float w = fast_exp2(ml.x - M);
+            acc += w * p.part_o[((size_t)slot * p.num_heads + hq) * kHeadDim + d];
+            L += w * ml.y;
+        }
+        p.out[((size_t)b * p.num_heads + hq) * kHeadDim + d] = acc / L;
+    }
+}
+
+// ------------------------------------------------------------------------------------ host
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
+                        bool contiguous, uint32_t max_seq) {
+    if (!a.q || !a.k_cache || !a.v_cache || !a.output || (!contiguous && !a.block_tables))
+        return fail(GRANITE_CUDA_NULL_POINTER, "paged decode: null buffer");
+    if (a.head_dim != kHeadDim)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: head_dim must be 128");
+    if (!contiguous && a.block_size != kPageTokens)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: block_size must be 16");
+    if (a.batch_size == 0) return GRANITE_CUDA_SUCCESS;
+    if (a.num_kv_heads == 0 || a.num_heads == 0 || a.num_heads % a.num_kv_heads != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_heads must be a multiple of num_kv_heads");
+    const int hkv = (int)a.num_kv_heads;
+    int tile_heads;
+    if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
+    else if (hkv % 8 == 0) tile_heads = 8;
+    else return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_kv_heads must be 1, 2, 4 or a multiple of 8");
+    const int group = (int)(a.num_heads / a.num_kv_heads);
+    const int warps_per_head = kConsumerWarps / tile_heads;
+    const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
+    if (heads_per_warp > 16)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: more than 16 query heads per consumer warp");
+    const int nt = heads_per_warp <= 8 ? 1 : 2;
+    const int subs_active = (group + heads_per_warp - 1) / heads_per_warp;
+    if (contiguous) {
+        if (max_seq == 0) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode: max_seq must be positive");
+    } else if (a.num_blocks == 0 || a.max_blocks_per_seq == 0) {
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: empty pool or table");
+    }
+
+    DecodeParams p{};
+    p.q = a.q;
+    p.tables = a.block_tables;
+    p.seq_lens = a.seq_lens;
+    p.out = a.output;
+    p.batch = (int)a.batch_size;
+    p.num_heads = (int)a.num_heads;
+    p.num_kv_heads = hkv;
+    p.group = group;
+    p.max_blocks = (int)a.max_blocks_per_seq;
+    p.num_blocks = (int)a.num_blocks;
+    p.uniform_len = (int)a.seq_len;
+    p.tile_heads = tile_heads;
+    p.n_head_tiles = hkv / tile_heads;
+    p.heads_per_warp = heads_per_warp;
+    p.active_warps = subs_active * tile_heads;
+    p.n_ctas = c->sm_count;
+    p.contiguous = contiguous ? 1 : 0;
+    p.max_seq = (int)max_seq;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = c->d_status;
+
+    const int slot_bytes = tile_heads * kHeadPageBytes;
+    const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
+    int slots = (int)((c->smem_optin - 1024 - tail) / slot_bytes);
+    if (slots > kMaxSlots) slots = kMaxSlots;
+    if (slots < 2) return fail(GRANITE_CUDA_INTERNAL_ERROR, "paged decode: not enough shared memory");
+    p.slots = slots;
+    const size_t smem_bytes = 1024 + (size_t)slots * slot_bytes + tail;
+
+    // scratch: prefix | first_seq | part_ml | part_o
+    size_t off = 0;
+    const size_t off_prefix = off; off = align_up(off + (size_t)(p.batch + 1) * 4, 256);
+    const size_t off_first = off;  off = align_up(off + (size_t)p.n_ctas * 4, 256);
+    const size_t off_ml = off;     off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * sizeof(float2), 256);
+    const size_t off_o = off;      off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * kHeadDim * 4, 256);
+    int rc = c->ensure_scratch(off);
+    if (rc) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(c->scratch);
+    p.page_prefix = reinterpret_cast<int*>(ws + off_prefix);
+    p.cta_first_seq = reinterpret_cast<int*>(ws + off_first);
+    p.part_ml = reinterpret_cast<float2*>(ws + off_ml);
+    p.part_o = reinterpret_cast<float*>(ws + off_o);
+
+    const CUtensorMap *kmap, *vmap;
+    if (contiguous) {
+        const uint64_t rows = (uint64_t)a.batch_size * hkv * max_seq;
+        kmap = c->tensor_map_2d(a.k_cache, kHeadDim, rows, kHeadDim * 2, 64, kPageTokens, 128);
+        vmap = c->tensor_map_2d(a.v_cache, kHeadDim, rows, kHeadDim * 2, 64, kPageTokens, 128);
+    } else {
+        const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens;
+        const uint64_t width = (uint64_t)hkv * kHeadDim;
+        kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageTokens, 128);
+        vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageTokens, 128);
+    }
+    if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
+
+    decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
+    auto kern = nt == 1 ? paged_decode_kernel<1> : paged_decode_kernel<2>;
+    GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    kern<<<p.n_ctas, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
+    decode_merge_kernel<<<dim3(p.batch, p.n_head_tiles), 128, 0, c->stream>>>(p);
+    GB_CUDA_TRY(cudaGetLastError());
+    c->dispatches += 3;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+}  // namespace gb200

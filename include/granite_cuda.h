@@ -1,0 +1,150 @@
+/*
+ * granite_cuda.h - C ABI of the B200 (sm_100a) attention backend for Granite.
+ *
+ * This is the drop-in boundary: a CUDA compute class / backend / operator inside Granite binds
+ * exactly these entry points (see INTEGRATION.md for the binding a maintainer adds).  Plain
+ * pointers and sizes only; no C++ or torch types cross it.
+ *
+ * Conventions (following the reference):
+ *   - every function returns an int equal to a granite::ErrorCode value
+ *     (include/granite/error.h:16-57); 0 is Success;
+ *   - work is enqueued asynchronously on the compute object's single in-order stream; only
+ *     granite_cuda_sync() blocks (include/granite/metal_compute.h:36-40,
+ *     src/backend/metal/metal_compute.mm:2721-2745 for the one-object-one-queue model);
+ *   - device-side problems (a wait that ran out, a block-table entry outside the pool) never
+ *     trap: kernels clamp, raise a status word and return; granite_cuda_sync() reports it;
+ *   - there is no CPU fallback: on a machine without a usable GPU every compute call fails
+ *     with GRANITE_CUDA_BACKEND_NOT_INITIALIZED.
+ */
+#ifndef GRANITE_CUDA_H
+#define GRANITE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Values of granite::ErrorCode (include/granite/error.h:16-57), by position. */
+enum {
+    GRANITE_CUDA_SUCCESS = 0,
+    GRANITE_CUDA_OUT_OF_MEMORY = 4,
+    GRANITE_CUDA_ALLOCATION_FAILED = 5,
+    GRANITE_CUDA_BUFFER_TOO_SMALL = 6,
+    GRANITE_CUDA_BACKEND_NOT_SUPPORTED = 7,
+    GRANITE_CUDA_BACKEND_NOT_INITIALIZED = 8,
+    GRANITE_CUDA_OPERATOR_NOT_IMPLEMENTED = 9,
+    GRANITE_CUDA_EXECUTION_FAILED = 11,
+    GRANITE_CUDA_TIMEOUT = 12,
+    GRANITE_CUDA_INVALID_SHAPE = 13,
+    GRANITE_CUDA_INVALID_ARGUMENT = 16,
+    GRANITE_CUDA_NULL_POINTER = 17,
+    GRANITE_CUDA_INVALID_STATE = 20,
+    GRANITE_CUDA_INTERNAL_ERROR = 24,
+    GRANITE_CUDA_NOT_IMPLEMENTED = 25
+};
+
+/* Opaque compute object: one device, one stream, cached tensor maps and scratch memory.
+ * Replaces the MetalCompute singleton (include/granite/metal_compute.h:20-66); one per GPU. */
+typedef struct granite_cuda_compute granite_cuda_compute_t;
+
+/* Message of the last failing call on this thread (never NULL). */
+const char* granite_cuda_last_error_message(void);
+
+/* Number of visible CUDA devices (0 when there is no driver/GPU). */
+int granite_cuda_device_count(void);
+
+/* MetalCompute::initialize (metal_compute.h:30).  `stream` may be NULL (the object creates its
+ * own non-blocking stream) or an existing cudaStream_t to enqueue on; to name the default
+ * stream pass cudaStreamLegacy or cudaStreamPerThread, since its plain handle is NULL. */
+int granite_cuda_compute_create(int device, void* stream, granite_cuda_compute_t** out);
+/* MetalCompute::shutdown (metal_compute.h:31). */
+void granite_cuda_compute_destroy(granite_cuda_compute_t* c);
+/* The cudaStream_t the object enqueues on. */
+void* granite_cuda_compute_stream(granite_cuda_compute_t* c);
+/* Number of SMs of the object's device. */
+int granite_cuda_compute_sm_count(granite_cuda_compute_t* c);
+/* MetalCompute::sync (metal_compute.h:36): blocks until the stream drains, then maps the device
+ * status word to Timeout / InvalidArgument / ExecutionFailed and clears it. */
+int granite_cuda_sync(granite_cuda_compute_t* c);
+/* MetalCompute::get_profiling_stats (metal_compute.h:48-52): kernels launched and syncs so far. */
+void granite_cuda_get_profiling_stats(granite_cuda_compute_t* c, uint64_t* dispatches,
+                                      uint64_t* syncs);
+
+/* ---- raw buffers: MetalCompute::create_buffer (metal_compute.h:944) and the
+ * IComputeBackend buffer calls (include/granite/backend.h:62-115) ------------------------- */
+int granite_cuda_malloc(granite_cuda_compute_t* c, size_t bytes, void** dev_ptr);
+int granite_cuda_free(granite_cuda_compute_t* c, void* dev_ptr);
+int granite_cuda_malloc_host(size_t bytes, void** host_ptr); /* pinned */
+int granite_cuda_free_host(void* host_ptr);
+/* Asynchronous on the object's stream; pair with granite_cuda_sync(). */
+int granite_cuda_write_buffer(granite_cuda_compute_t* c, void* dev_dst, const void* host_src,
+                              size_t bytes);
+int granite_cuda_read_buffer(granite_cuda_compute_t* c, void* host_dst, const void* dev_src,
+                             size_t bytes);
+int granite_cuda_copy_buffer(granite_cuda_compute_t* c, void* dev_dst, const void* dev_src,
+                             size_t bytes);
+int granite_cuda_memset(granite_cuda_compute_t* c, void* dev_dst, int byte, size_t bytes);
+
+/* ---- paged decode attention ---------------------------------------------------------------
+ * MetalCompute::batched_paged_attention_decode (metal_compute.h:906-920,
+ * metal_compute.mm:2658-2696) and, with batch_size 1 and seq_lens NULL,
+ * MetalCompute::paged_attention_decode (metal_compute.h:869-881, metal_compute.mm:2535-2621).
+ * Addressing rule (metal_compute.h:853-861): token pos of a sequence lives at pool row
+ * block_table[pos / block_size] * block_size + pos % block_size.
+ * Supported: head_dim 128, block_size 16, num_heads % num_kv_heads == 0, num_kv_heads in
+ * {1,2,4} or a multiple of 8; anything else returns InvalidArgument as the reference does for an
+ * unsupported head_dim (metal_compute.mm:2556-2559).  A sequence of length 0 gets a zero row. */
+typedef struct {
+    const float* q;              /* [batch, num_heads, head_dim] fp32, device */
+    const void* k_cache;         /* [num_blocks*block_size, num_kv_heads, head_dim] fp16, device */
+    const void* v_cache;         /* same layout */
+    const int32_t* block_tables; /* [batch, max_blocks_per_seq] int32, device */
+    const int32_t* seq_lens;     /* [batch] int32, device; NULL: every sequence has seq_len */
+    float* output;               /* [batch, num_heads, head_dim] fp32, device */
+    uint32_t batch_size;
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t block_size;
+    uint32_t max_blocks_per_seq;
+    uint32_t num_blocks; /* capacity of the pool in blocks (the MTL::Buffer length upstream) */
+    uint32_t seq_len;    /* used only when seq_lens is NULL */
+    float scale;
+} GraniteCudaPagedDecodeArgs;
+
+int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c,
+                                                const GraniteCudaPagedDecodeArgs* args);
+
+/* ---- contiguous-cache attention -------------------------------------------------------------
+ * MetalCompute::multihead_attention (metal_compute.h:804-816, metal_compute.mm:2253-2378).
+ * seq_q == 1: decode. q/out [num_heads, head_dim] fp32; k/v [num_kv_heads, max_seq, head_dim]
+ *             fp16 of which the first seq_kv rows per head are live.
+ * seq_q  > 1: causal prefill with start_pos 0 (metal_compute.mm:2352). q/out
+ *             [seq_q, num_heads, head_dim]; k/v [num_kv_heads, max_seq, head_dim] fp16.
+ *             q_dtype / out_dtype: 0 = fp32 (the reference's layout), 1 = fp16.
+ * max_seq == 0 means seq_kv, as in the reference (metal_compute.mm:2260). */
+typedef struct {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* output;
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t seq_q;
+    uint32_t seq_kv;
+    uint32_t head_dim;
+    uint32_t max_seq;
+    uint32_t q_dtype;   /* 0 fp32, 1 fp16 (prefill only) */
+    uint32_t out_dtype; /* 0 fp32, 1 fp16 (prefill only) */
+    float scale;
+} GraniteCudaAttentionArgs;
+
+int granite_cuda_multihead_attention(granite_cuda_compute_t* c,
+                                     const GraniteCudaAttentionArgs* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRANITE_CUDA_H */

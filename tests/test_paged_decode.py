@@ -1,0 +1,142 @@
+"""Paged / contiguous decode attention on the GPU against the CPU checker (through the C ABI).
+
+Shapes follow tools/test_paged_flash_attention.mm:158-174 (Hq 32, Hkv 8|4, D 128, block 16,
+shuffled block table) plus the edge cases the reference kernels special-case: one token, a
+length that is not a multiple of the block, an empty sequence, ragged batches.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_attention_close
+from granite_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_paged(compute, case, poison_unused=False):
+    import torch
+    dev = "cuda:0"
+    k_np = case.k_pool.view(np.uint16).copy()
+    v_np = case.v_pool.view(np.uint16).copy()
+    if poison_unused:
+        # every row that no live token maps to becomes NaN: the kernel must never let it leak
+        live = np.zeros(case.num_blocks * synth.PAGE, bool)
+        for b, n in enumerate(case.seq_lens):
+            for pos in range(int(n)):
+                live[case.tables[b, pos // synth.PAGE] * synth.PAGE + pos % synth.PAGE] = True
+        k_np[~live] = 0x7E00
+        v_np[~live] = 0x7E00
+    q = torch.from_numpy(case.q).to(dev)
+    k = torch.from_numpy(k_np.view(np.float16)).to(dev)
+    v = torch.from_numpy(v_np.view(np.float16)).to(dev)
+    tables = torch.from_numpy(case.tables).to(dev)
+    lens = torch.from_numpy(case.seq_lens).to(dev)
+    out = torch.full((case.batch, case.num_heads, case.head_dim), float("nan"), device=dev)
+    scale = 1.0 / np.sqrt(case.head_dim)
+    compute.batched_paged_attention_decode(q, k, v, tables, lens, out, case.batch, case.num_heads,
+                                           case.num_kv_heads, case.head_dim, synth.PAGE,
+                                           case.max_blocks, scale, num_blocks=case.num_blocks)
+    compute.sync()
+    return out.cpu().numpy(), k_np, v_np
+
+
+def _oracle(case, k_np, v_np):
+    from oracle import pyoracle
+    tables = np.where(case.tables < 0, 0, case.tables)
+    ref, bad = pyoracle.paged_decode_batch(case.q, k_np, v_np, tables, case.seq_lens, synth.PAGE)
+    assert bad == 0
+    return ref
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (32, 4), (64, 8), (8, 8), (16, 2), (8, 1), (32, 16)])
+def test_paged_decode_matches_cpu(compute, hq, hkv):
+    case = synth.paged_case(seed=7 + hq + hkv, batch=5, len_lo=1, len_hi=700, num_heads=hq, num_kv_heads=hkv)
+    got, k_np, v_np = _run_paged(compute, case)
+    assert_attention_close(got, _oracle(case, k_np, v_np), f"Hq={hq} Hkv={hkv}")
+
+
+@pytest.mark.parametrize("lens", [[1], [15], [16], [17], [512], [4097], [1, 16, 33, 2048, 5], [0, 40, 0], [3000] * 3])
+def test_paged_decode_edge_lengths(compute, lens):
+    case = synth.paged_case(seed=11, batch=len(lens), len_lo=0, len_hi=0, seq_lens=np.array(lens, np.int32),
+                            spare_blocks=3)
+    got, k_np, v_np = _run_paged(compute, case, poison_unused=True)
+    ref = _oracle(case, k_np, v_np)
+    assert_attention_close(got, ref, f"lens={lens}")
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert not got[b].any()
+
+
+def test_paged_decode_many_short_sequences(compute):
+    rng = np.random.default_rng(5)
+    lens = rng.integers(1, 40, size=600).astype(np.int32)
+    case = synth.paged_case(seed=12, batch=len(lens), len_lo=0, len_hi=0, seq_lens=lens)
+    got, k_np, v_np = _run_paged(compute, case)
+    assert_attention_close(got, _oracle(case, k_np, v_np), "600 short sequences")
+
+
+def test_single_sequence_paged_decode(compute):
+    import torch
+    case = synth.paged_case(seed=13, batch=1, len_lo=0, len_hi=0, seq_lens=np.array([777], np.int32))
+    dev = "cuda:0"
+    q = torch.from_numpy(case.q).to(dev)
+    k = torch.from_numpy(case.k_pool).to(dev)
+    v = torch.from_numpy(case.v_pool).to(dev)
+    table = torch.from_numpy(case.tables[0]).to(dev)
+    out = torch.zeros((case.num_heads, case.head_dim), device=dev)
+    compute.paged_attention_decode(q, k, v, table, out, case.num_heads, case.num_kv_heads, 777,
+                                   case.head_dim, synth.PAGE, 1.0 / np.sqrt(128.0), num_blocks=case.num_blocks)
+    compute.sync()
+    ref = _oracle(case, case.k_pool.view(np.uint16), case.v_pool.view(np.uint16))
+    assert_attention_close(out.cpu().numpy()[None], ref, "single sequence")
+
+
+def test_bad_table_entry_is_reported_not_fatal(compute):
+    import granite_b200 as g
+    case = synth.paged_case(seed=14, batch=2, len_lo=100, len_hi=200)
+    case.tables[1, 2] = case.num_blocks + 5
+    with pytest.raises(g.GraniteCudaError) as ei:
+        _run_paged(compute, case)
+    assert ei.value.code == g.ErrorCode.InvalidArgument
+    compute.sync()  # status word was cleared; the context is still usable
+    case.tables[1, 2] = 0
+    _run_paged(compute, case)
+
+
+def test_unsupported_shapes_are_rejected(compute):
+    import torch
+    import granite_b200 as g
+    t = torch.zeros(16, device="cuda:0")
+    for kw in (dict(head_dim=64), dict(block_size=32), dict(num_kv_heads=3)):
+        args = dict(batch_size=1, num_heads=32, num_kv_heads=8, head_dim=128, block_size=16)
+        args.update(kw)
+        with pytest.raises(g.GraniteCudaError) as ei:
+            compute.batched_paged_attention_decode(t, t, t, t, t, t, args["batch_size"], args["num_heads"],
+                                                   args["num_kv_heads"], args["head_dim"], args["block_size"],
+                                                   4, 0.1, num_blocks=4)
+        assert ei.value.code == g.ErrorCode.InvalidArgument
+
+
+@pytest.mark.parametrize("seq_kv,max_seq", [(512, 512), (1, 64), (100, 256), (2048, 4096), (333, 333)])
+def test_contiguous_decode_matches_cpu(compute, seq_kv, max_seq):
+    """multihead_attention with seq_q == 1 (config: batch 1, Hq 32, Hkv 8, D 128, ctx 512)."""
+    import torch
+    from oracle import pyoracle
+    hq, hkv, d = 32, 8, 128
+    rng = np.random.default_rng(1001 + seq_kv)
+    q = rng.standard_normal((hq, d), np.float32)
+    k = rng.standard_normal((hkv, max_seq, d), np.float32).astype(np.float16)
+    v = rng.standard_normal((hkv, max_seq, d), np.float32).astype(np.float16)
+    # rows past seq_kv are stale cache contents: make them hostile
+    k.view(np.uint16)[:, seq_kv:] = 0x7E00
+    v.view(np.uint16)[:, seq_kv:] = 0x7E00
+    dev = "cuda:0"
+    out = torch.zeros((hq, d), device=dev)
+    compute.multihead_attention(torch.from_numpy(q).to(dev), torch.from_numpy(k).to(dev),
+                                torch.from_numpy(v).to(dev), out, hq, hkv, 1, seq_kv, d,
+                                1.0 / np.sqrt(d), max_seq)
+    compute.sync()
+    kf = pyoracle.cache_to_fp32(k.view(np.uint16), seq_kv)
+    vf = pyoracle.cache_to_fp32(v.view(np.uint16), seq_kv)
+    ref = pyoracle.attention(q[None, None], kf, vf, start_pos=seq_kv - 1)[0, 0]
+    assert_attention_close(out.cpu().numpy(), ref, f"contiguous seq_kv={seq_kv}")
