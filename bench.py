@@ -1,0 +1,383 @@
+"""Benchmark of the attention hot path: batched paged decode attention over the block-table KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one batched paged decode call (plan + split-KV kernel + merge) over one batch of
+synthetic sequences whose K/V pages already live in HBM.  Workload at N = 1: 64 sequences, context
+lengths uniform in [1024, 32768], page 16, shuffled block table, Hq 32 / Hkv 8 / D 128, fp16 K/V,
+fp32 Q and output.  At N > 1 every rank owns its own batch of that shape (sequences are
+independent: sharded by sequence, no collective inside attention); the per-rank outputs are
+all-gathered with NCCL each step.  Prints ONE JSON line (rank 0).
+
+--impl reference times Granite's CPU attention arithmetic (oracle/, a restatement of
+src/llm/transformer.mm:1779-1840 over pages fetched by the rule of metal_compute.h:853-861, with
+the reference's thread policy) on a bounded sample of the same workload, on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = "paged_decode_b64"
+METRIC = "paged decode attention GB/s"
+UNIT = "GB/s"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs
+    (read-only queries; nothing is set)."""
+
+    def __init__(self, index: int, period_s: float = 0.003):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_baseline_sample(case_np, stride: int, repeats: int = 1):
+    """Times the CPU checker on every `stride`-th sequence; returns (GB/s, seconds, bytes)."""
+    from oracle import pyoracle
+    from granite_b200 import synth
+    sel = np.arange(0, case_np["seq_lens"].shape[0], stride)
+    lens = case_np["seq_lens"][sel]
+    hkv, d, hq = case_np["num_kv_heads"], case_np["head_dim"], case_np["num_heads"]
+    pages = int(((lens + synth.PAGE - 1) // synth.PAGE).sum())
+    nbytes = int(lens.sum()) * hkv * d * 2 * 2 + pages * 4 + len(sel) * 4 + len(sel) * hq * d * 4 * 2
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        pyoracle.paged_decode_batch(case_np["q"], case_np["k_pool"], case_np["v_pool"], case_np["tables"],
+                                    case_np["seq_lens"], synth.PAGE, stride=stride)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return nbytes / best / 1e9, best, nbytes, len(sel)
+
+
+def host_case_for_cpu(seed: int, cfg: dict, sel):
+    """The sequences `sel` of the workload, rebuilt on the host with a compact pool that holds only
+    their pages (the CPU arm never needs the other sequences' K/V)."""
+    from granite_b200 import synth
+    rng = np.random.default_rng(seed)
+    lens_all = synth.draw_lengths(rng, cfg["batch"], cfg["len_lo"], cfg["len_hi"], cfg["dist"])
+    lens = lens_all[np.asarray(sel)]
+    case = synth.paged_case(seed, len(lens), 0, 0, cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"],
+                            seq_lens=lens)
+    return dict(q=case.q, k_pool=case.k_pool.view(np.uint16), v_pool=case.v_pool.view(np.uint16),
+                tables=np.where(case.tables < 0, 0, case.tables), seq_lens=case.seq_lens,
+                num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, head_dim=case.head_dim)
+
+
+def workload_lengths(cfg: dict) -> np.ndarray:
+    from granite_b200 import synth
+    return synth.draw_lengths(np.random.default_rng(cfg["seed"]), cfg["batch"], cfg["len_lo"], cfg["len_hi"],
+                              cfg["dist"])
+
+
+def run_reference(args):
+    """Reference arm: CPU attention on the host cores.  Each step is a bounded sample of the
+    workload - whole sequences taken from every 16th position - sized from a calibration run so
+    that all steps together take about two minutes."""
+    from granite_b200 import synth
+    from oracle import pyoracle
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cfg = dict(synth.CONFIGS[WORKLOAD])
+    lens_all = workload_lengths(cfg)
+    shortest = int(np.argmin(lens_all))
+    calib = host_case_for_cpu(cfg["seed"], cfg, [shortest])
+    _, secs, _, _ = cpu_baseline_sample(calib, 1)
+    tok_per_s = float(lens_all[shortest]) / secs
+    budget_tokens = tok_per_s * 120.0 / max(args.steps + args.warmup, 1)
+    sel, tokens = [], 0
+    for b in range(0, cfg["batch"], 16):
+        if tokens + int(lens_all[b]) <= budget_tokens:
+            sel.append(b)
+            tokens += int(lens_all[b])
+    if not sel:
+        sel = [shortest]
+    hc = host_case_for_cpu(cfg["seed"], cfg, sel)
+    for _ in range(args.warmup):
+        cpu_baseline_sample(hc, 1)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        _, _, b, nseq = cpu_baseline_sample(hc, 1)
+        nbytes += b
+    dt = time.perf_counter() - t0
+    value = nbytes / dt / 1e9
+    cores = pyoracle.num_threads()
+    sample = (f"sequences {sel} of the workload's {cfg['batch']} ({int(hc['seq_lens'].sum())} tokens) per step")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample, "page": 16, "num_heads": cfg["num_heads"],
+                   "num_kv_heads": cfg["num_kv_heads"], "head_dim": cfg["head_dim"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="granite_b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sequences", type=int, default=0,
+                    help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import granite_b200 as g
+    from granite_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        torch.cuda.set_device(0)
+    dev = torch.device("cuda", local_rank if world > 1 else 0)
+    n_gpus = world
+
+    cfg = dict(synth.CONFIGS[WORKLOAD])
+    if args.sequences > 0:
+        cfg["batch"] = args.sequences
+    seed = cfg["seed"] + 7919 * rank  # every rank owns its own batch of the same shape
+    case = synth.paged_case(seed, cfg["batch"], cfg["len_lo"], cfg["len_hi"], cfg["num_heads"],
+                            cfg["num_kv_heads"], cfg["head_dim"], cfg["dist"], device=dev)
+    B, Hq, Hkv, D = case.batch, case.num_heads, case.num_kv_heads, case.head_dim
+    scale = 1.0 / float(np.sqrt(D))
+    stream = torch.cuda.current_stream()
+    compute = g.CudaCompute(dev.index, stream.cuda_stream)
+
+    tables_h = torch.from_numpy(case.tables).pin_memory()
+    lens_h = torch.from_numpy(case.seq_lens).pin_memory()
+    q_h = case.q.cpu().pin_memory()
+    out_h = torch.empty((B, Hq, D), dtype=torch.float32).pin_memory()
+    tables_d = tables_h.to(dev)
+    lens_d = lens_h.to(dev)
+    q_d = case.q
+    outs = [torch.zeros((B, Hq, D), device=dev) for _ in range(2)]
+    gathered = [torch.empty((world * B, Hq, D), device=dev) for _ in range(2)] if world > 1 else None
+
+    def decode(q, tables, lens, out):
+        compute.batched_paged_attention_decode(q, case.k_pool, case.v_pool, tables, lens, out, B, Hq, Hkv,
+                                               D, synth.PAGE, case.max_blocks, scale,
+                                               num_blocks=case.num_blocks)
+
+    pending = []
+
+    def step(i):
+        out = outs[i & 1]
+        decode(q_d, tables_d, lens_d, out)
+        if world > 1:
+            pending.append(dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True))
+            if len(pending) > 2:
+                pending.pop(0).wait()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- resident-input throughput ("value")
+    for i in range(args.warmup):
+        step(i)
+    for w in pending:
+        w.wait()
+    pending.clear()
+    barrier()
+    compute.enable_kernel_timing(True)
+    compute.reset_kernel_timing()
+    sampler = ClockSampler(dev.index)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    for w in pending:
+        w.wait()
+    pending.clear()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    compute.sync()
+    ms_total = e0.elapsed_time(e1)
+    kstats = compute.get_kernel_timing_stats()
+    compute.enable_kernel_timing(False)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    local_bytes = case.algorithmic_bytes()
+    if world > 1:
+        tb = torch.tensor([local_bytes], device=dev, dtype=torch.float64)
+        dist.all_reduce(tb)
+        total_bytes = float(tb.item())
+    else:
+        total_bytes = float(local_bytes)
+    ms_per_step = ms_total / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the C ABI with host buffers
+    e2e_steps = max(3, min(args.steps, 200))
+
+    def e2e_step():
+        compute.write_buffer(q_d, q_h, q_h.numel() * 4)
+        compute.write_buffer(tables_d, tables_h, tables_h.numel() * 4)
+        compute.write_buffer(lens_d, lens_h, lens_h.numel() * 4)
+        decode(q_d, tables_d, lens_d, outs[0])
+        compute.read_buffer(out_h, outs[0], out_h.numel() * 4)
+        compute.sync()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
+    h2d = q_h.numel() * 4 + tables_h.numel() * 4 + lens_h.numel() * 4
+    d2h = out_h.numel() * 4
+
+    # ---- roofline of the dominant kernel (rank 0's launches)
+    peak, peak_kind = measured_peaks()
+    main_ms, main_n = kstats.get("paged_decode_splitkv", (0.0, 0))
+    kernel_ms = main_ms / max(main_n, 1)
+    achieved = local_bytes / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else None
+    roofline = {
+        "bound": "hbm", "kernel": "paged_decode_splitkv", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
+        "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": local_bytes,
+        "traffic": int(local_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE),
+        "other_kernels_ms": {k: v[0] / max(v[1], 1) for k, v in kstats.items() if k != "paged_decode_splitkv"},
+    }
+
+    # ---- CPU baseline (rank 0, N = 1 only): bounded sample
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import pyoracle
+        sel = list(range(0, cfg["batch"], 8))
+        hc = host_case_for_cpu(cfg["seed"], cfg, sel)
+        gbs, secs, nb, nseq = cpu_baseline_sample(hc, 1, repeats=2)
+        cpu = {"value": gbs, "unit": UNIT, "cores": pyoracle.num_threads(), "kind": "port",
+               "sample": f"every 8th sequence ({nseq} of {cfg['batch']}, {int(hc['seq_lens'].sum())} tokens), "
+                         f"best of 2, {secs:.2f} s each"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sequences_per_gpu": B, "context": "uniform[1024,32768]",
+                       "page": synth.PAGE, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
+                       "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
+                       "l2": "inputs larger than L2 (4.4 GB of K/V per step, no reuse)",
+                       "sharding": "by sequence; NCCL all-gather of outputs per step" if world > 1 else "single GPU"},
+            "hbm_frac_of_measured_peak": value / n_gpus / peak,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "note": "host Q, block tables and lengths copied in, output copied out, sync per step; "
+                            "K/V pages are cache state resident in HBM"},
+            "gpu_launches": 3 * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    compute.shutdown()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one paged_decode_splitkv
+# launch, from the ncu capture of the 16-sequence case summarised in
+# profiles/paged_decode_splitkv_b64.md; DRAM traffic grows in proportion to the tokens read.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -85,6 +85,10 @@ class AttentionArgs(C.Structure):
     ]
 
 
+class KernelTiming(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("gpu_time_ms", C.c_double), ("dispatches", C.c_uint64)]
+
+
 def _sig(name, restype, *argtypes):
     fn = getattr(lib, name)
     fn.restype = restype
@@ -100,6 +104,9 @@ _sig("granite_cuda_compute_stream", C.c_void_p, C.c_void_p)
 _sig("granite_cuda_compute_sm_count", C.c_int, C.c_void_p)
 _sig("granite_cuda_sync", C.c_int, C.c_void_p)
 _sig("granite_cuda_get_profiling_stats", None, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64))
+_sig("granite_cuda_enable_kernel_timing", None, C.c_void_p, C.c_int)
+_sig("granite_cuda_reset_kernel_timing", None, C.c_void_p)
+_sig("granite_cuda_get_kernel_timing_stats", C.c_int, C.c_void_p, C.POINTER(KernelTiming), C.c_int)
 _sig("granite_cuda_malloc", C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p))
 _sig("granite_cuda_free", C.c_int, C.c_void_p, C.c_void_p)
 _sig("granite_cuda_malloc_host", C.c_int, C.c_size_t, C.POINTER(C.c_void_p))
@@ -182,6 +189,18 @@ class CudaCompute:
         d, s = C.c_uint64(), C.c_uint64()
         lib.granite_cuda_get_profiling_stats(self._h, C.byref(d), C.byref(s))
         return d.value, s.value
+
+    def enable_kernel_timing(self, enable: bool) -> None:
+        lib.granite_cuda_enable_kernel_timing(self._h, int(enable))
+
+    def reset_kernel_timing(self) -> None:
+        lib.granite_cuda_reset_kernel_timing(self._h)
+
+    def get_kernel_timing_stats(self) -> dict[str, tuple[float, int]]:
+        """{kernel name: (total GPU ms, dispatches)}; drains the stream first."""
+        buf = (KernelTiming * 32)()
+        n = lib.granite_cuda_get_kernel_timing_stats(self._h, buf, 32)
+        return {buf[i].name.decode(): (buf[i].gpu_time_ms, buf[i].dispatches) for i in range(min(n, 32))}
 
     # ---- raw buffers
     def create_buffer(self, size: int) -> int:

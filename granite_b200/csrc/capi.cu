@@ -90,6 +90,33 @@ const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_
     return &ins.first->second;
 }
 
+cudaEvent_t granite_cuda_compute::take_event() {
+    if (!event_pool.empty()) {
+        cudaEvent_t e = event_pool.back();
+        event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+void granite_cuda_compute::resolve_timings() {
+    for (auto& t : pending_timings) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, t.begin, t.end) == cudaSuccess) {
+            auto& st = kernel_stats[t.name];
+            st.ms += ms;
+            st.dispatches++;
+        } else {
+            cudaGetLastError();
+        }
+        event_pool.push_back(t.begin);
+        event_pool.push_back(t.end);
+    }
+    pending_timings.clear();
+}
+
 extern "C" {
 
 const char* granite_cuda_last_error_message(void) { return g_last_error.c_str(); }
@@ -144,6 +171,8 @@ void granite_cuda_compute_destroy(granite_cuda_compute_t* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    c->resolve_timings();
+    for (cudaEvent_t e : c->event_pool) cudaEventDestroy(e);
     if (c->scratch) cudaFree(c->scratch);
     if (c->d_status) cudaFree(c->d_status);
     if (c->h_status) cudaFreeHost(c->h_status);
@@ -159,6 +188,7 @@ int granite_cuda_sync(granite_cuda_compute_t* c) {
     c->syncs++;
     GB_CUDA_TRY(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     GB_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->resolve_timings();
     int st = *c->h_status;
     if (st == 0) return GRANITE_CUDA_SUCCESS;
     GB_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
@@ -172,6 +202,34 @@ int granite_cuda_sync(granite_cuda_compute_t* c) {
 void granite_cuda_get_profiling_stats(granite_cuda_compute_t* c, uint64_t* dispatches, uint64_t* syncs) {
     if (dispatches) *dispatches = c ? c->dispatches : 0;
     if (syncs) *syncs = c ? c->syncs : 0;
+}
+
+void granite_cuda_enable_kernel_timing(granite_cuda_compute_t* c, int enable) {
+    if (c) c->kernel_timing = enable != 0;
+}
+
+void granite_cuda_reset_kernel_timing(granite_cuda_compute_t* c) {
+    if (!c) return;
+    cudaStreamSynchronize(c->stream);
+    c->resolve_timings();
+    c->kernel_stats.clear();
+}
+
+int granite_cuda_get_kernel_timing_stats(granite_cuda_compute_t* c, GraniteCudaKernelTiming* out, int capacity) {
+    if (!c) return 0;
+    cudaStreamSynchronize(c->stream);
+    c->resolve_timings();
+    int n = 0;
+    for (auto& kv : c->kernel_stats) {
+        if (out && n < capacity) {
+            std::strncpy(out[n].name, kv.first.c_str(), sizeof(out[n].name) - 1);
+            out[n].name[sizeof(out[n].name) - 1] = 0;
+            out[n].gpu_time_ms = kv.second.ms;
+            out[n].dispatches = kv.second.dispatches;
+        }
+        n++;
+    }
+    return n;
 }
 
 int granite_cuda_malloc(granite_cuda_compute_t* c, size_t bytes, void** dev_ptr) {

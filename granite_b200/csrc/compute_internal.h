@@ -9,6 +9,7 @@
 #include <map>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "../../include/granite_cuda.h"
 
@@ -65,6 +66,16 @@ struct granite_cuda_compute {
     size_t scratch_bytes = 0;
     std::map<gb200::TensorMapKey, CUtensorMap> tensor_maps;
 
+    // per-kernel GPU timing (MetalCompute::enable_kernel_timing, metal_compute.h:54-60)
+    struct TimedLaunch { const char* name; cudaEvent_t begin, end; };
+    struct KernelStat { double ms = 0.0; uint64_t dispatches = 0; };
+    bool kernel_timing = false;
+    std::vector<TimedLaunch> pending_timings;
+    std::vector<cudaEvent_t> event_pool;
+    std::map<std::string, KernelStat> kernel_stats;
+    cudaEvent_t take_event();
+    void resolve_timings();  // call only after the stream has drained
+
     int ensure_scratch(size_t bytes);
     // fp16 tensor maps; returns nullptr (and sets the error message) on failure.
     const CUtensorMap* tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
@@ -73,6 +84,23 @@ struct granite_cuda_compute {
 };
 
 namespace gb200 {
+// Brackets one kernel launch with events when kernel timing is on; counts the dispatch always.
+struct LaunchScope {
+    granite_cuda_compute* c;
+    cudaEvent_t end = nullptr;
+    LaunchScope(granite_cuda_compute* c_, const char* name) : c(c_) {
+        c->dispatches++;
+        if (c->kernel_timing) {
+            cudaEvent_t b = c->take_event();
+            end = c->take_event();
+            cudaEventRecord(b, c->stream);
+            c->pending_timings.push_back({name, b, end});
+        }
+    }
+    ~LaunchScope() {
+        if (end) cudaEventRecord(end, c->stream);
+    }
+};
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
                         bool contiguous, uint32_t max_seq);
 }  // namespace gb200

@@ -485,14 +485,15 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
 }
 
 // ------------------------------------------------------------------------------------ merge
-// grid (batch, n_head_tiles), 128 threads (one per output dim).  Combines the partials of a
+// grid (batch, num_heads), 128 threads (one per output dim).  Combines the partials of a
 // sequence that was cut by CTA range boundaries:  out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c.
 __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
-    const int b = blockIdx.x, ht = blockIdx.y, d = threadIdx.x;
+    const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
     const int total = p.page_prefix[p.batch];
     if (total == 0) return;
     const int s0 = p.page_prefix[b], s1 = p.page_prefix[b + 1];
     if (s1 == s0) return;
+    const int ht = hq / (p.tile_heads * p.group);
     const long long T = (long long)total * p.n_head_tiles;
     const long long A = (long long)ht * total + s0, B = (long long)ht * total + s1;  // [A, B)
     auto cta_of = [&](long long P) {
@@ -504,26 +505,25 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
     };
     const int c_lo = cta_of(A), c_hi = cta_of(B - 1);
     if (c_lo == c_hi) return;  // whole sequence inside one range: already final
-    const int heads_in_tile = p.tile_heads * p.group;
-    for (int hh = 0; hh < heads_in_tile; hh++) {
-        const int hq = ht * heads_in_tile + hh;
-        float M = -INFINITY;
-        for (int c = c_lo; c <= c_hi; c++) {
-            if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;  // empty range
-            const int slot = 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1);
-            M = fmaxf(M, p.part_ml[(size_t)slot * p.num_heads + hq].x);
-        }
-        float acc = 0.f, L = 0.f;
-        for (int c = c_lo; c <= c_hi; c++) {
-            if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
-            const int slot = 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1);
-            const float2 ml = p.part_ml[(size_t)slot * p.num_heads + hq];
-            const float w = fast_exp2(ml.x - M);
-            acc += w * p.part_o[((size_t)slot * p.num_heads + hq) * kHeadDim + d];
-            L += w * ml.y;
-        }
-        p.out[((size_t)b * p.num_heads + hq) * kHeadDim + d] = acc / L;
+    // The first contributing range may hold the sequence as its second partial (slot 1); every
+    // later one starts inside the sequence, so the sequence is its first segment (slot 0).
+    // Ranges in between can be empty when there are fewer pages than CTAs: those wrote nothing.
+    const int slot_lo = 2 * c_lo + (range_start(T, p.n_ctas, c_lo) >= A ? 0 : 1);
+    float M = p.part_ml[(size_t)slot_lo * p.num_heads + hq].x;
+    for (int c = c_lo + 1; c <= c_hi; c++) {
+        if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
+        M = fmaxf(M, p.part_ml[(size_t)(2 * c) * p.num_heads + hq].x);
     }
+    float acc = 0.f, L = 0.f;
+    for (int c = c_lo; c <= c_hi; c++) {
+        if (c != c_lo && range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
+        const int slot = c == c_lo ? slot_lo : 2 * c;
+        const float2 ml = p.part_ml[(size_t)slot * p.num_heads + hq];
+        const float w = fast_exp2(ml.x - M);
+        acc += w * p.part_o[((size_t)slot * p.num_heads + hq) * kHeadDim + d];
+        L += w * ml.y;
+    }
+    p.out[((size_t)b * p.num_heads + hq) * kHeadDim + d] = acc / L;
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -615,13 +615,21 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     }
     if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
-    decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
     auto kern = nt == 1 ? paged_decode_kernel<1> : paged_decode_kernel<2>;
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    kern<<<p.n_ctas, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
-    decode_merge_kernel<<<dim3(p.batch, p.n_head_tiles), 128, 0, c->stream>>>(p);
+    {
+        LaunchScope t(c, "decode_plan");
+        decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
+    }
+    {
+        LaunchScope t(c, contiguous ? "contiguous_decode_splitkv" : "paged_decode_splitkv");
+        kern<<<p.n_ctas, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
+    }
+    {
+        LaunchScope t(c, "decode_merge");
+        decode_merge_kernel<<<dim3(p.batch, p.num_heads), 128, 0, c->stream>>>(p);
+    }
     GB_CUDA_TRY(cudaGetLastError());
-    c->dispatches += 3;
     return GRANITE_CUDA_SUCCESS;
 }
 

@@ -72,6 +72,20 @@ int granite_cuda_sync(granite_cuda_compute_t* c);
 void granite_cuda_get_profiling_stats(granite_cuda_compute_t* c, uint64_t* dispatches,
                                       uint64_t* syncs);
 
+/* MetalCompute::enable_kernel_timing / reset_kernel_timing / get_kernel_timing_stats
+ * (metal_compute.h:54-60): when enabled every kernel launch is bracketed by CUDA events on the
+ * object's stream; the getter drains the stream and returns one row per kernel name (the number
+ * of rows available; at most `capacity` are written). */
+typedef struct {
+    char name[64];
+    double gpu_time_ms;
+    uint64_t dispatches;
+} GraniteCudaKernelTiming;
+void granite_cuda_enable_kernel_timing(granite_cuda_compute_t* c, int enable);
+void granite_cuda_reset_kernel_timing(granite_cuda_compute_t* c);
+int granite_cuda_get_kernel_timing_stats(granite_cuda_compute_t* c, GraniteCudaKernelTiming* out,
+                                         int capacity);
+
 /* ---- raw buffers: MetalCompute::create_buffer (metal_compute.h:944) and the
  * IComputeBackend buffer calls (include/granite/backend.h:62-115) ------------------------- */
 int granite_cuda_malloc(granite_cuda_compute_t* c, size_t bytes, void** dev_ptr);

@@ -179,6 +179,7 @@ class Ref:
         r.ref_fp16_to_fp32.argtypes = [C.c_uint16]
         r.ref_fp32_to_fp16.restype = C.c_uint16
         r.ref_fp32_to_fp16.argtypes = [C.c_float]
+        r.ref_fp16_to_fp32_bits.argtypes = [_u16p, np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS"), C.c_size_t]
         r.ref_num_threads.restype = C.c_int
         r.ref_paged_pool_script.restype = C.c_int
         r.ref_paged_pool_script.argtypes = [C.c_int, C.c_int, C.c_int, _i32p, C.c_int, _i32p, _i32p,
@@ -195,6 +196,12 @@ class Ref:
 
     def fp32_to_fp16(self, f: float) -> int:
         return int(self._r.ref_fp32_to_fp16(f))
+
+    def fp16_to_fp32_bits(self, codes: np.ndarray) -> np.ndarray:
+        codes = np.ascontiguousarray(codes, np.uint16)
+        out = np.empty(codes.shape, np.uint32)
+        self._r.ref_fp16_to_fp32_bits(codes.reshape(-1), out.reshape(-1), codes.size)
+        return out
 
     def num_threads(self) -> int:
         return int(self._r.ref_num_threads())

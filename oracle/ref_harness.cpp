@@ -48,6 +48,13 @@ extern "C" {
 
 float ref_fp16_to_fp32(uint16_t h) { return fp16_to_fp32(h); }
 uint16_t ref_fp32_to_fp16(float f) { return fp32_to_fp16(f); }
+// Bit patterns of fp16_to_fp32 for n codes (keeps NaN payloads, which a float return would quiet).
+void ref_fp16_to_fp32_bits(const uint16_t* h, uint32_t* bits, size_t n) {
+    for (size_t i = 0; i < n; i++) {
+        float f = fp16_to_fp32(h[i]);
+        std::memcpy(&bits[i], &f, 4);
+    }
+}
 int ref_num_threads(void) { return static_cast<int>(get_num_threads()); }
 
 // Runs `fn(i, user)` for i in [0, n) through the reference's parallel_for with its own thread

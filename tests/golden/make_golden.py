@@ -1,0 +1,187 @@
+"""Regenerates the golden fixtures in this directory.  Run where the reference checkout exists:
+
+    python tests/golden/make_golden.py
+
+Sources of truth, per file:
+  ref_fp16.npz            reference fp16_to_fp32 / fp32_to_fp16 (src/llm/math_ops.cpp:18-54) through
+                          oracle/_ref (the reference's own compiled sources)
+  ref_paged_pool.npz      reference PagedKVPool / PagedKVCache / BlockManager replaying a seeded
+                          script of operations (src/llm/paged_kv_cache.cpp)
+  ref_kvcache_append.npz  reference KVCache::append layout (src/llm/kv_cache.cpp:52-107)
+  ref_spec_tree.npz       reference SpeculationTree parents / depths / BFS order
+                          (src/llm/speculation_tree.cpp:13-84)
+  kat_sdpa_2x3x4.npz      the one attention known-answer test the reference holds
+                          (tests/test_vulkan.cpp:353-482): inputs and expected values recomputed
+                          here in numpy float32 in the test's own order, independently of oracle/
+  oracle_small_cases.npz  small seeded decode / causal prefill / tree cases evaluated by oracle/
+                          (guards the checker itself against drift; not a reference output)
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent.parent))
+
+from oracle import pyoracle  # noqa: E402
+from granite_b200 import synth  # noqa: E402
+
+
+def ref_fp16(ref):
+    codes = np.arange(65536, dtype=np.uint16)
+    widened = ref.fp16_to_fp32_bits(codes)
+    rng = np.random.default_rng(42)
+    floats = np.concatenate([
+        rng.standard_normal(4000).astype(np.float32),
+        (rng.standard_normal(2000) * 1e-6).astype(np.float32),
+        (rng.standard_normal(2000) * 1e5).astype(np.float32),
+        np.array([0.0, -0.0, 1.0, -1.0, 65504.0, 65520.0, 1e-8, 6.1e-5, 5.9e-8, np.inf, -np.inf, np.nan,
+                  0.333251953125, 0.3333740234375], np.float32),
+    ])
+    narrowed = np.array([ref.fp32_to_fp16(float(f)) for f in floats], np.uint16)
+    np.savez_compressed(HERE / "ref_fp16.npz", widened_bits=widened, floats=floats.view(np.uint32), narrowed=narrowed)
+
+
+def paged_script(seed, n_ops, max_sequences, max_total_tokens, block_size):
+    """A seeded walk over the page-manager operations, biased towards exhaustion and reuse."""
+    rng = np.random.default_rng(seed)
+    ops = []
+    live = []
+    for _ in range(n_ops):
+        r = rng.random()
+        if r < 0.15 or not live:
+            ops.append((0, 0, 0))
+            live.append(len(live))  # optimistic; replays are deterministic anyway
+        elif r < 0.60:
+            ops.append((1, int(rng.integers(0, max_sequences)), int(rng.integers(1, 3 * block_size))))
+        elif r < 0.75:
+            ops.append((2, int(rng.integers(0, max_sequences)), int(rng.integers(0, 4 * block_size))))
+        elif r < 0.85:
+            ops.append((3, int(rng.integers(-1, max_sequences + 1)), 0))
+        elif r < 0.90:
+            ops.append((4, 0, 0))
+        elif r < 0.95:
+            ops.append((5, int(rng.integers(-2, max_total_tokens // block_size + 2)), 0))
+        else:
+            ops.append((6 if rng.random() < 0.5 else 7, int(rng.integers(0, max_sequences)), int(rng.integers(0, 5 * block_size))))
+    return np.array(ops, np.int32)
+
+
+def ref_paged_pool(ref):
+    out = {}
+    for i, (seed, n_ops, ms, mt, bs) in enumerate([(1, 400, 4, 256, 16), (2, 600, 8, 100, 16), (3, 300, 3, 64, 4)]):
+        ops = paged_script(seed, n_ops, ms, mt, bs)
+        max_blocks = (mt + bs - 1) // bs
+        r = ref.paged_pool_script(ms, mt, bs, ops, max_blocks)
+        out[f"cfg{i}"] = np.array([ms, mt, bs, max_blocks], np.int32)
+        out[f"ops{i}"] = ops
+        for k in ("results", "seq_lens", "table_lens", "tables"):
+            out[f"{k}{i}"] = r[k]
+        out[f"free{i}"] = np.array([r["num_free"], r["num_total"]], np.int32)
+    np.savez_compressed(HERE / "ref_paged_pool.npz", **out)
+
+
+def ref_kvcache(ref):
+    rng = np.random.default_rng(7)
+    hkv, d, max_seq = 3, 8, 20
+    steps = np.array([5, 1, 1, 7, 2], np.int32)
+    ks = [rng.integers(0, 65536, size=(hkv, int(n), d)).astype(np.uint16) for n in steps]
+    vs = [rng.integers(0, 65536, size=(hkv, int(n), d)).astype(np.uint16) for n in steps]
+    k_out, v_out, final_len = ref.kvcache_append(hkv, d, max_seq, steps,
+                                                 np.concatenate([k.reshape(-1) for k in ks]),
+                                                 np.concatenate([v.reshape(-1) for v in vs]))
+    np.savez_compressed(HERE / "ref_kvcache_append.npz", shape=np.array([hkv, d, max_seq], np.int32), steps=steps,
+                        k_chunks=np.concatenate([k.reshape(-1) for k in ks]),
+                        v_chunks=np.concatenate([v.reshape(-1) for v in vs]),
+                        k_out=k_out, v_out=v_out, final_len=np.array([final_len], np.int32))
+
+
+def ref_spec_tree(ref):
+    out = {}
+    for i, (seed, n) in enumerate([(1004, 64), (5, 16), (6, 1), (8, 33)]):
+        parents = synth.tree_parents(seed, n)
+        r = ref.speculation_tree(parents)
+        out[f"parents{i}"] = parents
+        out[f"parents_out{i}"] = r["parents"]
+        out[f"depths{i}"] = r["depths"]
+        out[f"bfs{i}"] = r["bfs"]
+        out[f"max_depth{i}"] = np.array([r["max_depth"]], np.int32)
+    np.savez_compressed(HERE / "ref_spec_tree.npz", **out)
+
+
+def kat_sdpa():
+    """tests/test_vulkan.cpp:366-474, recomputed in the test's own order with float32 steps."""
+    f = np.float32
+    sq, skv, d = 2, 3, 4
+    q = np.array([f(i + 1) for i in range(sq * d)], f).reshape(sq, d)
+    kt = np.array([f(i + 1) * f(0.5) for i in range(d * skv)], f).reshape(d, skv)
+    v = np.array([f(i + 1) * f(0.25) for i in range(skv * d)], f).reshape(skv, d)
+    scale = 1.0 / np.sqrt(float(d))
+    expected = np.zeros((sq, d), f)
+    for i in range(sq):
+        scores = np.zeros(skv, f)
+        for j in range(skv):
+            s = f(0)
+            for dd in range(d):
+                s = f(s + f(f(i * d + dd + 1) * f(f(dd * skv + j + 1) * f(0.5))))
+            scores[j] = f(s * f(scale))
+        mx = scores.max()
+        probs = np.zeros(skv, f)
+        se = f(0)
+        for j in range(skv):
+            probs[j] = np.exp(f(scores[j] - mx), dtype=f)
+            se = f(se + probs[j])
+        inv = f(f(1) / se)
+        probs = (probs * inv).astype(f)
+        for dd in range(d):
+            s = f(0)
+            for j in range(skv):
+                s = f(s + f(probs[j] * f(f(j * d + dd + 1) * f(0.25))))
+            expected[i, dd] = s
+    np.savez_compressed(HERE / "kat_sdpa_2x3x4.npz", q=q, kt=kt, v=v, scale=np.array([scale], np.float64),
+                        expected=expected, tol=np.array([1e-4]))
+
+
+def oracle_small_cases():
+    out = {}
+    rng = np.random.default_rng(99)
+    # decode over a contiguous cache
+    hq, hkv, d, seq, max_seq = 8, 2, 16, 37, 48
+    q = rng.standard_normal((1, 1, hq, d)).astype(np.float32)
+    kc = rng.standard_normal((hkv, max_seq, d)).astype(np.float16)
+    vc = rng.standard_normal((hkv, max_seq, d)).astype(np.float16)
+    k_all = pyoracle.cache_to_fp32(kc.view(np.uint16), seq)
+    v_all = pyoracle.cache_to_fp32(vc.view(np.uint16), seq)
+    out.update(dec_q=q, dec_k=kc.view(np.uint16), dec_v=vc.view(np.uint16), dec_seq=np.array([seq]),
+               dec_out=pyoracle.attention(q, k_all, v_all, start_pos=seq - 1, threads=1))
+    # causal prefill
+    s = 19
+    q = rng.standard_normal((1, s, hq, d)).astype(np.float32)
+    k = rng.standard_normal((s, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((s, hkv, d)).astype(np.float32)
+    out.update(pre_q=q, pre_k=k, pre_v=v, pre_out=pyoracle.attention(q, k, v, start_pos=0, threads=1))
+    # tree
+    n, prefix = 12, 21
+    parents = synth.tree_parents(3, n)
+    q = rng.standard_normal((1, n, hq, d)).astype(np.float32)
+    kp = rng.standard_normal((prefix, hkv, d)).astype(np.float32)
+    vp = rng.standard_normal((prefix, hkv, d)).astype(np.float32)
+    kt = rng.standard_normal((1, n, hkv, d)).astype(np.float32)
+    vt = rng.standard_normal((1, n, hkv, d)).astype(np.float32)
+    out.update(tree_parents=parents, tree_q=q, tree_kp=kp, tree_vp=vp, tree_kt=kt, tree_vt=vt,
+               tree_mask=pyoracle.tree_mask(parents),
+               tree_out=pyoracle.attention_tree(q, kp, vp, kt, vt, parents, threads=1))
+    np.savez_compressed(HERE / "oracle_small_cases.npz", **out)
+
+
+if __name__ == "__main__":
+    ref = pyoracle.Ref()
+    ref_fp16(ref)
+    ref_paged_pool(ref)
+    ref_kvcache(ref)
+    ref_spec_tree(ref)
+    kat_sdpa()
+    oracle_small_cases()
+    for p in sorted(HERE.glob("*.npz")):
+        print(p.name, p.stat().st_size)

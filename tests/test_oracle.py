@@ -1,0 +1,140 @@
+"""Pins the CPU checker (oracle/) before anything trusts it: against the reference's own
+compiled objects (golden files written by tests/golden/make_golden.py, and live against
+oracle/_ref when that library is present), and against the one attention known-answer test the
+reference holds (tests/test_vulkan.cpp:353-482)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import pyoracle
+from granite_b200 import synth
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def test_fp16_widening_matches_reference_for_every_code():
+    g = np.load(GOLD / "ref_fp16.npz")
+    mine = pyoracle.f16_bits_to_f32(np.arange(65536, dtype=np.uint16)).view(np.uint32)
+    assert np.array_equal(mine, g["widened_bits"])
+
+
+def test_fp16_truncating_narrowing_matches_reference():
+    g = np.load(GOLD / "ref_fp16.npz")
+    floats = g["floats"].view(np.float32)
+    mine = np.array([pyoracle.fp32_to_fp16(float(f)) for f in floats], np.uint16)
+    assert np.array_equal(mine, g["narrowed"])
+    # truncation, not rounding: 0.33337402 sits just below the next fp16 step
+    assert pyoracle.fp32_to_fp16(0.3333740234375 - 1e-7) == pyoracle.fp32_to_fp16(0.333251953125)
+    # flush of subnormal results and clamp to infinity (math_ops.cpp:51-52)
+    assert pyoracle.fp32_to_fp16(5.9e-8) == 0
+    assert pyoracle.fp32_to_fp16(70000.0) == 0x7C00
+    assert pyoracle.fp32_to_fp16(float("nan")) == 0x7C00
+
+
+def test_known_answer_2x3x4():
+    g = np.load(GOLD / "kat_sdpa_2x3x4.npz")
+    got = pyoracle.sdpa_kt(g["q"], g["kt"], g["v"], float(g["scale"][0]))
+    assert np.abs(got - g["expected"]).max() <= 1e-4  # the reference test's own bound
+    # the LLM-path loop gives the same numbers on the same problem (K given row-major)
+    k = np.ascontiguousarray(g["kt"].T)[:, None, :]
+    v = g["v"][:, None, :]
+    q = g["q"][None, :, None, :]
+    got2 = pyoracle.attention(q, k, v, start_pos=10, scale=float(g["scale"][0]), threads=1)[0, :, 0, :]
+    assert np.abs(got2 - g["expected"]).max() <= 1e-4
+
+
+def test_oracle_small_cases_are_stable():
+    g = np.load(GOLD / "oracle_small_cases.npz")
+    seq = int(g["dec_seq"][0])
+    k_all = pyoracle.cache_to_fp32(g["dec_k"], seq)
+    v_all = pyoracle.cache_to_fp32(g["dec_v"], seq)
+    for threads in (1, 4):
+        assert np.array_equal(pyoracle.attention(g["dec_q"], k_all, v_all, start_pos=seq - 1, threads=threads), g["dec_out"])
+        assert np.array_equal(pyoracle.attention(g["pre_q"], g["pre_k"], g["pre_v"], start_pos=0, threads=threads), g["pre_out"])
+        assert np.array_equal(pyoracle.attention_tree(g["tree_q"], g["tree_kp"], g["tree_vp"], g["tree_kt"], g["tree_vt"],
+                                                      g["tree_parents"], threads=threads), g["tree_out"])
+    assert np.array_equal(pyoracle.tree_mask(g["tree_parents"]), g["tree_mask"])
+
+
+def test_attention_against_float64_softmax():
+    rng = np.random.default_rng(3)
+    s, hq, hkv, d = 23, 4, 2, 32
+    q = rng.standard_normal((1, s, hq, d)).astype(np.float32)
+    k = rng.standard_normal((s, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((s, hkv, d)).astype(np.float32)
+    got = pyoracle.attention(q, k, v, start_pos=0)
+    for h in range(hq):
+        sc = (q[0, :, h].astype(np.float64) @ k[:, h // 2].astype(np.float64).T) / np.sqrt(d)
+        sc[np.triu_indices(s, 1)] = -np.inf
+        p = np.exp(sc - sc.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        assert np.abs(p @ v[:, h // 2].astype(np.float64) - got[0, :, h]).max() < 1e-5
+
+
+def test_causal_rule_uses_start_pos():
+    """k_pos > start_pos + q_pos is masked (transformer.mm:1805-1806)."""
+    rng = np.random.default_rng(4)
+    q = rng.standard_normal((1, 2, 2, 8)).astype(np.float32)
+    k = rng.standard_normal((6, 1, 8)).astype(np.float32)
+    v = rng.standard_normal((6, 1, 8)).astype(np.float32)
+    got = pyoracle.attention(q, k, v, start_pos=3)
+    # query 0 sees keys 0..3, query 1 sees 0..4
+    a = pyoracle.attention(q[:, :1], k[:4], v[:4], start_pos=3)
+    b = pyoracle.attention(q[:, 1:], k[:5], v[:5], start_pos=4)
+    assert np.array_equal(got[:, :1], a) and np.array_equal(got[:, 1:], b)
+
+
+def test_paged_gather_follows_addressing_rule():
+    case = synth.paged_case(seed=21, batch=3, len_lo=1, len_hi=90, num_heads=4, num_kv_heads=2, head_dim=8)
+    pool = case.k_pool.view(np.uint16)
+    for b in range(case.batch):
+        n = int(case.seq_lens[b])
+        rows, bad = pyoracle.paged_gather(pool, case.tables[b], n, synth.PAGE)
+        assert bad == 0
+        for pos in (0, n // 2, n - 1):
+            phys = case.tables[b, pos // 16] * 16 + pos % 16  # metal_compute.h:857-861
+            assert np.array_equal(rows[pos], pool[phys])
+    _, bad = pyoracle.paged_gather(pool, np.array([case.num_blocks], np.int32), 3, synth.PAGE)
+    assert bad == 3
+
+
+def test_tree_mask_matches_definition_and_reference_tree():
+    g = np.load(GOLD / "ref_spec_tree.npz")
+    for i in range(4):
+        parents = g[f"parents{i}"]
+        assert np.array_equal(g[f"parents_out{i}"], parents)  # get_parent_indices keeps insertion order
+        m = pyoracle.tree_mask(parents)
+        depths = g[f"depths{i}"]
+        n = len(parents)
+        for a in range(n):
+            anc = {a}
+            c = parents[a]
+            while c >= 0:
+                anc.add(int(c))
+                c = parents[c]
+            assert set(np.flatnonzero(m[a])) == anc
+            assert m[a].sum() == depths[a] + 1  # self + one ancestor per level
+        assert pyoracle.tree_validate(parents)
+    assert not pyoracle.tree_validate(np.array([-1, 2, 7], np.int32))
+    assert not pyoracle.tree_validate(np.array([-2], np.int32))
+
+
+def test_synthetic_tree_respects_limits():
+    p = synth.tree_parents(1004, 64, max_children=4, max_depth=8)
+    assert p[0] == -1 and (p[1:] < np.arange(1, 64)).all() and (p[1:] >= 0).all()
+    assert np.bincount(p[1:], minlength=64).max() <= 4
+    assert pyoracle.tree_mask(p).sum(1).max() - 1 <= 8
+
+
+@pytest.mark.skipif(not pyoracle.ref_available(), reason="oracle/_ref not built (needs the reference checkout)")
+def test_live_reference_objects_agree_with_goldens():
+    ref = pyoracle.Ref()
+    g = np.load(GOLD / "ref_paged_pool.npz")
+    for i in range(3):
+        ms, mt, bs, mb = (int(x) for x in g[f"cfg{i}"])
+        r = ref.paged_pool_script(ms, mt, bs, g[f"ops{i}"], mb)
+        assert np.array_equal(r["results"], g[f"results{i}"])
+        assert np.array_equal(r["tables"], g[f"tables{i}"])
+    for h in (0, 1, 0x3FF, 0x400, 0x7BFF, 0x7C00, 0x7E00, 0x8001, 0xFC00):
+        assert np.float32(ref.fp16_to_fp32(h)).tobytes() == np.float32(pyoracle.fp16_to_fp32(h)).tobytes()
