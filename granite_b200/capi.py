@@ -117,6 +117,8 @@ _sig("granite_cuda_copy_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.
 _sig("granite_cuda_memset", C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t)
 _sig("granite_cuda_batched_paged_attention_decode", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs))
 _sig("granite_cuda_multihead_attention", C.c_int, C.c_void_p, C.POINTER(AttentionArgs))
+_sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
+     C.c_void_p)
 
 
 def last_error() -> str:
@@ -239,3 +241,18 @@ class CudaCompute:
         a = AttentionArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), num_heads, num_kv_heads, seq_q,
                           seq_kv, head_dim, max_seq, q_dtype, out_dtype, scale)
         check(lib.granite_cuda_multihead_attention(self._h, C.byref(a)))
+
+
+def batched_paged_attention_decode_static(Q, K_cache, V_cache, block_tables, seq_lens, output, batch_size,
+                                          num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                                          scale, *, num_blocks, stream: int = 0, device_status=None,
+                                          seq_len: int = 0) -> None:
+    """The allocation-free paged decode: for hosts that own all device memory themselves or cannot
+    tolerate cudaMalloc's device-wide synchronisation.  Needs no compute object; runs on the current
+    device and on `stream`; scratch is a fixed array inside the library (batch <= 4096, heads <= 64).
+    Calls that overlap on one GPU race on that array - serialise them."""
+    a = PagedDecodeArgs(_ptr(Q), _ptr(K_cache), _ptr(V_cache), _ptr(block_tables), _ptr(seq_lens),
+                        _ptr(output), batch_size, num_heads, num_kv_heads, head_dim, block_size,
+                        max_blocks_per_seq, num_blocks, seq_len, scale)
+    check(lib.granite_cuda_batched_paged_attention_decode_static(C.byref(a), C.c_void_p(stream),
+                                                                 C.c_void_p(_ptr(device_status))))

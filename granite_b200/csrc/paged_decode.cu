@@ -20,6 +20,8 @@
 // the tile: S^T = K * Q^T and O^T += V^T * P^T on mma.sync m16n8k16 with the group's query heads
 // as the 8-wide N dimension, online softmax across the warp by shuffles, fp32 state.  Q and P
 // are split into fp16 hi + lo parts so the fp32 inputs of the reference are not rounded.
+#include <mutex>
+
 #include "compute_internal.h"
 #include "ptx.cuh"
 
@@ -634,3 +636,195 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
 }
 
 }  // namespace gb200
+
+// =====================================================================================
+// Allocation-free variant of the batched paged decode.
+//
+// Some hosts cannot let this library allocate: a serving process whose own arena already owns
+// all of HBM (a cudaMalloc from a plug-in would fail or fragment it), and latency-critical
+// loops where the implicit device-wide synchronisation of cudaMalloc/cudaFree is not
+// acceptable.  For them the scratch that the split-KV decode needs (page prefix sums, the first
+// sequence of every CTA range, and the partial (m, l, o) of sequences cut by a range boundary)
+// lives in the fixed device array below instead of the compute object's growable arena.
+// Every GPU that loads the library carries these ~12.7 MB until the process exits.
+// =====================================================================================
+namespace gb200 {
+
+constexpr int kStaticMaxBatch = 4096;   // sequences per call
+constexpr int kStaticMaxHeads = 64;     // query heads
+constexpr int kStaticMaxCtas = 192;     // SMs of the device
+constexpr size_t kStaticOffStatus = 0;
+constexpr size_t kStaticOffPrefix = 256;
+constexpr size_t kStaticOffFirst = kStaticOffPrefix + ((size_t)(kStaticMaxBatch + 1) * 4 + 255) / 256 * 256;
+constexpr size_t kStaticOffMl = kStaticOffFirst + ((size_t)kStaticMaxCtas * 4 + 255) / 256 * 256;
+constexpr size_t kStaticOffO = kStaticOffMl + (size_t)2 * kStaticMaxCtas * kStaticMaxHeads * sizeof(float2);
+constexpr size_t kStaticScratchBytes = kStaticOffO + (size_t)2 * kStaticMaxCtas * kStaticMaxHeads * kHeadDim * 4;
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+struct StaticDeviceSetup {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // device address of g_static_decode_scratch on this device
+    int sm_count = 0;
+    int smem_optin = 0;
+};
+constexpr int kMaxDevices = 64;
+static StaticDeviceSetup g_static_setup[kMaxDevices];
+static std::mutex g_static_setup_mutex;
+
+// Once per device, with that device current: resolves the device address of the scratch array
+// and raises the kernels' dynamic shared-memory limit.  Allocates nothing.
+static int static_decode_setup(int device, StaticDeviceSetup** out) {
+    if (device < 0 || device >= kMaxDevices)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: device index out of range");
+    std::lock_guard<std::mutex> lock(g_static_setup_mutex);
+    StaticDeviceSetup& s = g_static_setup[device];
+    if (!s.ready) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return fail(GRANITE_CUDA_BACKEND_NOT_INITIALIZED,
+                        std::string("static decode: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        }
+        int major = 0;
+        GB_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        if (major != 10) return fail(GRANITE_CUDA_BACKEND_NOT_SUPPORTED, "static decode: built for sm_100a only");
+        GB_CUDA_TRY(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, device));
+        GB_CUDA_TRY(cudaDeviceGetAttribute(&s.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
+        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
+        s.scratch = static_cast<unsigned char*>(ptr);
+        s.ready = true;
+    }
+    *out = &s;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+// A tensor map built on the stack (the compute object's cache would allocate host memory).
+static int encode_pool_map(CUtensorMap* map, const void* base, uint64_t width_elems, uint64_t rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn enc = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    if (!enc) return fail(GRANITE_CUDA_BACKEND_NOT_INITIALIZED, "static decode: cuTensorMapEncodeTiled unavailable");
+    if (reinterpret_cast<uintptr_t>(base) & 15)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: K/V pools must be 16-byte aligned");
+    cuuint64_t dims[2] = {width_elems, rows};
+    cuuint64_t strides[1] = {width_elems * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)kPageTokens};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(GRANITE_CUDA_EXECUTION_FAILED, "static decode: cuTensorMapEncodeTiled failed with " + std::to_string((int)r));
+    return GRANITE_CUDA_SUCCESS;
+}
+
+}  // namespace gb200
+
+extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteCudaPagedDecodeArgs* args,
+                                                                  void* stream, int32_t* device_status) {
+    using namespace gb200;
+    if (!args) return fail(GRANITE_CUDA_NULL_POINTER, "static decode: args is null");
+    const GraniteCudaPagedDecodeArgs& a = *args;
+    if (!a.q || !a.k_cache || !a.v_cache || !a.output || !a.block_tables)
+        return fail(GRANITE_CUDA_NULL_POINTER, "static decode: null buffer");
+    if (a.head_dim != kHeadDim || a.block_size != kPageTokens)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: head_dim must be 128 and block_size 16");
+    if (a.batch_size == 0) return GRANITE_CUDA_SUCCESS;
+    if (a.batch_size > (uint32_t)kStaticMaxBatch)
+        return fail(GRANITE_CUDA_BUFFER_TOO_SMALL, "static decode: batch_size " + std::to_string(a.batch_size) +
+                    " exceeds the fixed scratch (max " + std::to_string(kStaticMaxBatch) + " sequences per call)");
+    if (a.num_heads > (uint32_t)kStaticMaxHeads)
+        return fail(GRANITE_CUDA_BUFFER_TOO_SMALL, "static decode: num_heads " + std::to_string(a.num_heads) +
+                    " exceeds the fixed scratch (max " + std::to_string(kStaticMaxHeads) + " query heads)");
+    if (a.num_kv_heads == 0 || a.num_heads == 0 || a.num_heads % a.num_kv_heads != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: num_heads must be a multiple of num_kv_heads");
+    if (a.num_blocks == 0 || a.max_blocks_per_seq == 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: empty pool or table");
+    const int hkv = (int)a.num_kv_heads;
+    int tile_heads;
+    if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
+    else if (hkv % 8 == 0) tile_heads = 8;
+    else return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: num_kv_heads must be 1, 2, 4 or a multiple of 8");
+    const int group = (int)(a.num_heads / a.num_kv_heads);
+    const int warps_per_head = kConsumerWarps / tile_heads;
+    const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
+    if (heads_per_warp > 16)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: more than 16 query heads per consumer warp");
+
+    int device = 0;
+    GB_CUDA_TRY(cudaGetDevice(&device));
+    StaticDeviceSetup* setup = nullptr;
+    int rc = static_decode_setup(device, &setup);
+    if (rc) return rc;
+    if (setup->sm_count > kStaticMaxCtas)
+        return fail(GRANITE_CUDA_BUFFER_TOO_SMALL, "static decode: device has more SMs than the fixed scratch covers");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    DecodeParams p{};
+    p.q = a.q;
+    p.tables = a.block_tables;
+    p.seq_lens = a.seq_lens;
+    p.out = a.output;
+    p.batch = (int)a.batch_size;
+    p.num_heads = (int)a.num_heads;
+    p.num_kv_heads = hkv;
+    p.group = group;
+    p.max_blocks = (int)a.max_blocks_per_seq;
+    p.num_blocks = (int)a.num_blocks;
+    p.uniform_len = (int)a.seq_len;
+    p.tile_heads = tile_heads;
+    p.n_head_tiles = hkv / tile_heads;
+    p.heads_per_warp = heads_per_warp;
+    p.active_warps = ((group + heads_per_warp - 1) / heads_per_warp) * tile_heads;
+    p.n_ctas = setup->sm_count;
+    p.contiguous = 0;
+    p.max_seq = 0;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    const int slot_bytes = tile_heads * kHeadPageBytes;
+    const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
+    int slots = (int)((setup->smem_optin - 1024 - tail) / slot_bytes);
+    if (slots > kMaxSlots) slots = kMaxSlots;
+    if (slots < 2) return fail(GRANITE_CUDA_INTERNAL_ERROR, "static decode: not enough shared memory");
+    p.slots = slots;
+    const size_t smem_bytes = 1024 + (size_t)slots * slot_bytes + tail;
+
+    unsigned char* ws = setup->scratch;
+    p.page_prefix = reinterpret_cast<int*>(ws + kStaticOffPrefix);
+    p.cta_first_seq = reinterpret_cast<int*>(ws + kStaticOffFirst);
+    p.part_ml = reinterpret_cast<float2*>(ws + kStaticOffMl);
+    p.part_o = reinterpret_cast<float*>(ws + kStaticOffO);
+    if (device_status) {
+        p.status = device_status;  // the caller owns and clears it
+    } else {
+        // the array keeps the previous call's contents: the status word must start at zero
+        p.status = reinterpret_cast<int*>(ws + kStaticOffStatus);
+        GB_CUDA_TRY(cudaMemsetAsync(p.status, 0, sizeof(int), st));
+    }
+    // prefix sums, first-sequence table and partials are fully rewritten before they are read
+
+    CUtensorMap kmap, vmap;
+    const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens, width = (uint64_t)hkv * kHeadDim;
+    if ((rc = encode_pool_map(&kmap, a.k_cache, width, rows)) != 0) return rc;
+    if ((rc = encode_pool_map(&vmap, a.v_cache, width, rows)) != 0) return rc;
+
+    decode_plan_kernel<<<1, 1024, 0, st>>>(p);
+    if (heads_per_warp <= 8)
+        paged_decode_kernel<1><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
+    else
+        paged_decode_kernel<2><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
+    decode_merge_kernel<<<dim3(p.batch, p.num_heads), 128, 0, st>>>(p);
+    GB_CUDA_TRY(cudaGetLastError());
+    return GRANITE_CUDA_SUCCESS;
+}

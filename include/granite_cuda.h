@@ -131,6 +131,30 @@ typedef struct {
 int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c,
                                                 const GraniteCudaPagedDecodeArgs* args);
 
+/* Allocation-free batched paged decode.  This entry point has no counterpart in the reference.
+ * It exists for hosts that cannot let a plug-in allocate device memory: a serving process whose
+ * own arena already owns the GPU's memory, or a latency-critical loop that cannot afford the
+ * device-wide synchronisation hidden in cudaMalloc/cudaFree.  Same arguments, layouts, limits and
+ * results as granite_cuda_batched_paged_attention_decode, but it needs no compute object and
+ * calls no cudaMalloc, cudaFree or other allocating routine: its scratch (prefix sums and the
+ * partials of sequences split across SMs) is a fixed ~12.7 MB array that every GPU which loads
+ * this library holds until the process exits.
+ *   - Limits: batch_size <= 4096, num_heads <= 64, at most 192 SMs; beyond them the call returns
+ *     GRANITE_CUDA_BUFFER_TOO_SMALL and launches nothing.
+ *   - Runs on the CURRENT device, on `stream` (a cudaStream_t; NULL is the default stream),
+ *     asynchronously.
+ *   - The first call on each device also does a one-time set-up (it resolves the array's device
+ *     address and raises the kernels' shared-memory limit), so make that first call before any
+ *     stream capture begins.
+ *   - All calls share the one array and it keeps the previous call's contents; the call clears
+ *     the only part that must start at zero.  Two calls that overlap on the same GPU (different
+ *     streams, or different threads) race on it: serialise them.
+ *   - device_status: optional device int32 that receives the status bits (2 = block-table entry
+ *     outside the pool, 4 = bad sequence length, 1 = a bounded wait ran out); the caller zeroes
+ *     and reads it.  NULL: the bits go to a word inside the array and are not reported. */
+int granite_cuda_batched_paged_attention_decode_static(const GraniteCudaPagedDecodeArgs* args,
+                                                       void* stream, int32_t* device_status);
+
 /* ---- contiguous-cache attention -------------------------------------------------------------
  * MetalCompute::multihead_attention (metal_compute.h:804-816, metal_compute.mm:2253-2378).
  * seq_q == 1: decode. q/out [num_heads, head_dim] fp32; k/v [num_kv_heads, max_seq, head_dim]
