@@ -322,7 +322,7 @@ int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCud
         d.scale = a->scale;
         return launch_paged_decode(c, d, true, max_seq);
     }
-    return fail(GRANITE_CUDA_NOT_IMPLEMENTED, "prefill is not built into this library yet");
+    return launch_prefill(c, *a);
 }
 
 }  // extern "C"

@@ -103,4 +103,5 @@ struct LaunchScope {
 };
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
                         bool contiguous, uint32_t max_seq);
+int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a);
 }  // namespace gb200

@@ -159,9 +159,11 @@ int granite_cuda_batched_paged_attention_decode_static(const GraniteCudaPagedDec
  * MetalCompute::multihead_attention (metal_compute.h:804-816, metal_compute.mm:2253-2378).
  * seq_q == 1: decode. q/out [num_heads, head_dim] fp32; k/v [num_kv_heads, max_seq, head_dim]
  *             fp16 of which the first seq_kv rows per head are live.
- * seq_q  > 1: causal prefill with start_pos 0 (metal_compute.mm:2352). q/out
- *             [seq_q, num_heads, head_dim]; k/v [num_kv_heads, max_seq, head_dim] fp16.
- *             q_dtype / out_dtype: 0 = fp32 (the reference's layout), 1 = fp16.
+ * seq_q  > 1: causal prefill (metal_compute.mm:2333-2375). q/out [seq_q, num_heads, head_dim];
+ *             k/v [num_kv_heads, max_seq, head_dim] fp16, keys [0, seq_kv) live.
+ *             q_dtype / out_dtype: 0 = fp32 (the reference's layout), 1 = fp16.  fp32 Q is
+ *             rounded to fp16 once for the tensor cores, as the Metal kernel does
+ *             (metal_shaders_attention.h:1505-1507); accumulation is fp32.
  * max_seq == 0 means seq_kv, as in the reference (metal_compute.mm:2260). */
 typedef struct {
     const void* q;
@@ -177,6 +179,9 @@ typedef struct {
     uint32_t q_dtype;   /* 0 fp32, 1 fp16 (prefill only) */
     uint32_t out_dtype; /* 0 fp32, 1 fp16 (prefill only) */
     float scale;
+    uint32_t start_pos; /* prefill only: query i sits at position start_pos + i and sees keys
+                           <= that position (chunked prefill, src/llm/transformer.mm:3682-3692);
+                           the reference wrapper passes 0 */
 } GraniteCudaAttentionArgs;
 
 int granite_cuda_multihead_attention(granite_cuda_compute_t* c,
