@@ -86,6 +86,18 @@ class AttentionArgs(C.Structure):
     ]
 
 
+class TreeAttentionArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_tree", C.c_void_p),
+        ("v_tree", C.c_void_p), ("parent_indices", C.c_void_p), ("block_tables", C.c_void_p),
+        ("cache_lens", C.c_void_p), ("output", C.c_void_p),
+        ("batch_size", C.c_uint32), ("num_heads", C.c_uint32), ("num_kv_heads", C.c_uint32),
+        ("num_nodes", C.c_uint32), ("cache_len", C.c_uint32), ("head_dim", C.c_uint32),
+        ("cache_stride", C.c_uint32), ("block_size", C.c_uint32), ("max_blocks_per_seq", C.c_uint32),
+        ("num_blocks", C.c_uint32), ("q_dtype", C.c_uint32), ("scale", C.c_float),
+    ]
+
+
 class KernelTiming(C.Structure):
     _fields_ = [("name", C.c_char * 64), ("gpu_time_ms", C.c_double), ("dispatches", C.c_uint64)]
 
@@ -118,6 +130,8 @@ _sig("granite_cuda_copy_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.
 _sig("granite_cuda_memset", C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t)
 _sig("granite_cuda_batched_paged_attention_decode", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs))
 _sig("granite_cuda_multihead_attention", C.c_int, C.c_void_p, C.POINTER(AttentionArgs))
+_sig("granite_cuda_attention_tree", C.c_int, C.c_void_p, C.POINTER(TreeAttentionArgs))
+_sig("granite_cuda_build_tree_mask", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32)
 _sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
      C.c_void_p)
 
@@ -242,6 +256,20 @@ class CudaCompute:
         a = AttentionArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), num_heads, num_kv_heads, seq_q,
                           seq_kv, head_dim, max_seq, q_dtype, out_dtype, scale, start_pos)
         check(lib.granite_cuda_multihead_attention(self._h, C.byref(a)))
+
+    def attention_tree(self, Q, K_cache, V_cache, K_tree, V_tree, parent_indices, output, num_heads,
+                       num_kv_heads, num_nodes, cache_len, head_dim, scale, *, batch_size=1,
+                       block_tables=None, cache_lens=None, cache_stride=0, block_size=16,
+                       max_blocks_per_seq=0, num_blocks=0, q_dtype=0) -> None:
+        a = TreeAttentionArgs(_ptr(Q), _ptr(K_cache), _ptr(V_cache), _ptr(K_tree), _ptr(V_tree),
+                              _ptr(parent_indices), _ptr(block_tables), _ptr(cache_lens), _ptr(output),
+                              batch_size, num_heads, num_kv_heads, num_nodes, cache_len, head_dim,
+                              cache_stride, block_size, max_blocks_per_seq, num_blocks, q_dtype, scale)
+        check(lib.granite_cuda_attention_tree(self._h, C.byref(a)))
+
+    def build_tree_mask(self, parent_indices, masks, batch_size, num_nodes) -> None:
+        check(lib.granite_cuda_build_tree_mask(self._h, C.c_void_p(_ptr(parent_indices)),
+                                               C.c_void_p(_ptr(masks)), batch_size, num_nodes))
 
 
 def batched_paged_attention_decode_static(Q, K_cache, V_cache, block_tables, seq_lens, output, batch_size,

@@ -54,10 +54,7 @@ int granite_cuda_compute::ensure_scratch(size_t bytes) {
     return GRANITE_CUDA_SUCCESS;
 }
 
-const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
-                                                       uint64_t stride1_bytes, uint32_t box0,
-                                                       uint32_t box1, int swizzle_bytes) {
-    TensorMapKey key{base, dim0, dim1, 0, stride1_bytes, 0, box0, box1, 0, swizzle_bytes, 2};
+const CUtensorMap* granite_cuda_compute::encode_map(const TensorMapKey& key) {
     auto it = tensor_maps.find(key);
     if (it != tensor_maps.end()) return &it->second;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -65,21 +62,21 @@ const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_
         set_error("cuTensorMapEncodeTiled is not available from the driver");
         return nullptr;
     }
-    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (stride1_bytes & 15) != 0) {
-        set_error("tensor map: base address and row pitch must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(key.base) & 15) != 0 || (key.stride1 & 15) != 0 || (key.stride2 & 15) != 0) {
+        set_error("tensor map: base address and strides must be 16-byte aligned");
         return nullptr;
     }
     CUtensorMap map;
-    cuuint64_t dims[2] = {dim0, dim1};
-    cuuint64_t strides[1] = {stride1_bytes};
-    cuuint32_t box[2] = {box0, box1};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
-                            : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                            : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
-                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides,
-                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    cuuint64_t dims[3] = {key.dim0, key.dim1, key.dim2};
+    cuuint64_t strides[2] = {key.stride1, key.stride2};
+    cuuint32_t box[3] = {key.box0, key.box1, key.box2};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMapSwizzle sw = key.swizzle == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : key.swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : key.swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)key.rank, const_cast<void*>(key.base), dims,
+                     strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
@@ -88,6 +85,20 @@ const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_
     if (tensor_maps.size() > 256) tensor_maps.clear();  // callers re-create what they need
     auto ins = tensor_maps.emplace(key, map);
     return &ins.first->second;
+}
+
+const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
+                                                       uint64_t stride1_bytes, uint32_t box0,
+                                                       uint32_t box1, int swizzle_bytes) {
+    return encode_map(TensorMapKey{base, dim0, dim1, 0, stride1_bytes, 0, box0, box1, 0, swizzle_bytes, 2});
+}
+
+const CUtensorMap* granite_cuda_compute::tensor_map_3d(const void* base, uint64_t dim0, uint64_t dim1,
+                                                       uint64_t dim2, uint64_t stride1_bytes,
+                                                       uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
+                                                       uint32_t box2, int swizzle_bytes) {
+    return encode_map(TensorMapKey{base, dim0, dim1, dim2, stride1_bytes, stride2_bytes, box0, box1, box2,
+                                   swizzle_bytes, 3});
 }
 
 cudaEvent_t granite_cuda_compute::take_event() {
@@ -323,6 +334,19 @@ int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCud
         return launch_paged_decode(c, d, true, max_seq);
     }
     return launch_prefill(c, *a);
+}
+
+int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTreeAttentionArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_tree_verify(c, *args);
+}
+
+int granite_cuda_build_tree_mask(granite_cuda_compute_t* c, const int32_t* parent_indices, uint64_t* masks,
+                                 uint32_t batch_size, uint32_t num_nodes) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "build_tree_mask: compute object is null");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_tree_mask(c, parent_indices, masks, batch_size, num_nodes);
 }
 
 }  // extern "C"

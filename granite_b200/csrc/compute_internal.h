@@ -81,6 +81,10 @@ struct granite_cuda_compute {
     const CUtensorMap* tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,
                                      uint64_t stride1_bytes, uint32_t box0, uint32_t box1,
                                      int swizzle_bytes);
+    const CUtensorMap* tensor_map_3d(const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                                     uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
+                                     uint32_t box1, uint32_t box2, int swizzle_bytes);
+    const CUtensorMap* encode_map(const gb200::TensorMapKey& key);
 };
 
 namespace gb200 {
@@ -104,4 +108,6 @@ struct LaunchScope {
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
                         bool contiguous, uint32_t max_seq);
 int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a);
+int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a);
+int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* masks, uint32_t batch, uint32_t n);
 }  // namespace gb200

@@ -187,6 +187,53 @@ typedef struct {
 int granite_cuda_multihead_attention(granite_cuda_compute_t* c,
                                      const GraniteCudaAttentionArgs* args);
 
+/* ---- tree attention for speculative-decoding verification -----------------------------------
+ * MetalCompute::attention_tree (metal_compute.h:830-844, metal_compute.mm:2463-2529): every tree
+ * node attends to the whole committed prefix and, among the tree nodes, to itself and its
+ * ancestors (mask rule of src/llm/transformer.mm:823-840; parents must lie in [-1, num_nodes),
+ * :806-813 - a parent outside that range is treated as "no parent" and reported by sync as
+ * InvalidArgument).  With batch_size 1, block_tables NULL, cache_lens NULL and cache_stride 0
+ * the layouts are exactly the reference's:
+ *   q, output      [num_heads, num_nodes, head_dim] fp32
+ *   k_cache/v_cache [num_kv_heads, cache_len, head_dim] fp16 (row stride cache_len)
+ *   k_tree/v_tree  [num_kv_heads, num_nodes, head_dim] fp16, parent_indices [num_nodes] int32
+ * Extensions for the batched configurations: a leading batch dimension on every buffer,
+ * per-sequence prefix lengths (cache_lens, device), a contiguous cache whose row stride exceeds
+ * the live length (cache_stride), and a prefix that lives in the paged pool (block_tables
+ * non-NULL: k_cache/v_cache are then the pools [num_blocks*block_size, num_kv_heads, head_dim]).
+ * q_dtype 1 takes fp16 queries (no hi/lo split needed).  num_nodes <= 64 (the reference caps the
+ * tree at 64 nodes, src/llm/speculative_runner.cpp:579); head_dim 128; block_size 16. */
+typedef struct {
+    const void* q;                 /* [batch, num_heads, num_nodes, head_dim] fp32 (or fp16) */
+    const void* k_cache;           /* may be NULL when there is no prefix */
+    const void* v_cache;
+    const void* k_tree;            /* [batch, num_kv_heads, num_nodes, head_dim] fp16 */
+    const void* v_tree;
+    const int32_t* parent_indices; /* [batch, num_nodes] int32, device */
+    const int32_t* block_tables;   /* [batch, max_blocks_per_seq] or NULL (contiguous cache) */
+    const int32_t* cache_lens;     /* [batch] int32, device, or NULL (use cache_len) */
+    float* output;                 /* [batch, num_heads, num_nodes, head_dim] fp32 */
+    uint32_t batch_size;
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t num_nodes;
+    uint32_t cache_len;
+    uint32_t head_dim;
+    uint32_t cache_stride;         /* contiguous cache: rows per (sequence, KV head); 0 = cache_len */
+    uint32_t block_size;
+    uint32_t max_blocks_per_seq;
+    uint32_t num_blocks;
+    uint32_t q_dtype;              /* 0 fp32, 1 fp16 */
+    float scale;
+} GraniteCudaTreeAttentionArgs;
+
+int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTreeAttentionArgs* args);
+
+/* The ancestor mask on its own (src/llm/transformer.mm:823-840): masks[b*num_nodes + i] gets a
+ * 64-bit word whose bit j is set when node i of sequence b may attend to tree node j. */
+int granite_cuda_build_tree_mask(granite_cuda_compute_t* c, const int32_t* parent_indices,
+                                 uint64_t* masks, uint32_t batch_size, uint32_t num_nodes);
+
 #ifdef __cplusplus
 }
 #endif
