@@ -98,6 +98,20 @@ class TreeAttentionArgs(C.Structure):
     ]
 
 
+class KvAppendArgs(C.Structure):
+    _fields_ = [("cache_k", C.c_void_p), ("cache_v", C.c_void_p), ("new_k", C.c_void_p), ("new_v", C.c_void_p),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("current_len", C.c_uint32),
+                ("new_len", C.c_uint32), ("max_seq_len", C.c_uint32)]
+
+
+class PagedKvAppendArgs(C.Structure):
+    _fields_ = [("new_k", C.c_void_p), ("new_v", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("block_table", C.c_void_p), ("positions", C.c_void_p),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("start_pos", C.c_uint32),
+                ("new_len", C.c_uint32), ("block_size", C.c_uint32), ("num_blocks", C.c_uint32),
+                ("table_len", C.c_uint32), ("batch_size", C.c_uint32)]
+
+
 class KernelTiming(C.Structure):
     _fields_ = [("name", C.c_char * 64), ("gpu_time_ms", C.c_double), ("dispatches", C.c_uint64)]
 
@@ -130,6 +144,8 @@ _sig("granite_cuda_copy_buffer", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.
 _sig("granite_cuda_memset", C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t)
 _sig("granite_cuda_batched_paged_attention_decode", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs))
 _sig("granite_cuda_multihead_attention", C.c_int, C.c_void_p, C.POINTER(AttentionArgs))
+_sig("granite_cuda_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(KvAppendArgs))
+_sig("granite_cuda_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(PagedKvAppendArgs))
 _sig("granite_cuda_attention_tree", C.c_int, C.c_void_p, C.POINTER(TreeAttentionArgs))
 _sig("granite_cuda_build_tree_mask", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32)
 _sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
@@ -266,6 +282,20 @@ class CudaCompute:
                               batch_size, num_heads, num_kv_heads, num_nodes, cache_len, head_dim,
                               cache_stride, block_size, max_blocks_per_seq, num_blocks, q_dtype, scale)
         check(lib.granite_cuda_attention_tree(self._h, C.byref(a)))
+
+    def kv_cache_append(self, cache_k, cache_v, new_k, new_v, num_kv_heads, head_dim, current_len,
+                        new_len, max_seq_len) -> None:
+        a = KvAppendArgs(_ptr(cache_k), _ptr(cache_v), _ptr(new_k), _ptr(new_v), num_kv_heads, head_dim,
+                         current_len, new_len, max_seq_len)
+        check(lib.granite_cuda_kv_cache_append(self._h, C.byref(a)))
+
+    def paged_kv_cache_append(self, new_k, new_v, K_cache, V_cache, block_table, num_kv_heads, head_dim,
+                              start_pos, new_len, block_size, *, num_blocks, table_len, positions=None,
+                              batch_size=0) -> None:
+        a = PagedKvAppendArgs(_ptr(new_k), _ptr(new_v), _ptr(K_cache), _ptr(V_cache), _ptr(block_table),
+                              _ptr(positions), num_kv_heads, head_dim, start_pos, new_len, block_size,
+                              num_blocks, table_len, batch_size)
+        check(lib.granite_cuda_paged_kv_cache_append(self._h, C.byref(a)))
 
     def build_tree_mask(self, parent_indices, masks, batch_size, num_nodes) -> None:
         check(lib.granite_cuda_build_tree_mask(self._h, C.c_void_p(_ptr(parent_indices)),

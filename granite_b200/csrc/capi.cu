@@ -336,6 +336,24 @@ int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCud
     return launch_prefill(c, *a);
 }
 
+int granite_cuda_sdpa(granite_cuda_compute_t* c, const GraniteCudaSdpaArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "sdpa: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_sdpa_operator(c, *args);
+}
+
+int granite_cuda_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaKvAppendArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "kv_cache_append: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_kv_cache_append(c, *args);
+}
+
+int granite_cuda_paged_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaPagedKvAppendArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "paged_kv_cache_append: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_paged_kv_cache_append(c, *args);
+}
+
 int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTreeAttentionArgs* args) {
     if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null argument");
     GB_CUDA_TRY(cudaSetDevice(c->device));

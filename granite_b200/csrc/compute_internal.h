@@ -109,5 +109,8 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
                         bool contiguous, uint32_t max_seq);
 int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a);
 int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a);
+int launch_kv_cache_append(granite_cuda_compute* c, const GraniteCudaKvAppendArgs& a);
+int launch_paged_kv_cache_append(granite_cuda_compute* c, const GraniteCudaPagedKvAppendArgs& a);
+int launch_sdpa_operator(granite_cuda_compute* c, const GraniteCudaSdpaArgs& a);
 int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* masks, uint32_t batch, uint32_t n);
 }  // namespace gb200

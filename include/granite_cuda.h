@@ -187,6 +187,76 @@ typedef struct {
 int granite_cuda_multihead_attention(granite_cuda_compute_t* c,
                                      const GraniteCudaAttentionArgs* args);
 
+/* ---- operator-level attention -----------------------------------------------------------------
+ * The computation behind OpType::ScaledDotProductAttention (include/granite/operators.h:71):
+ * out = softmax(scale * Q K^T) V for one head, any head_dim; q/out [seq_q, head_dim],
+ * v [seq_kv, head_dim].  k_transposed = 1: k is [head_dim, seq_kv] (the Vulkan operator,
+ * src/operators/vulkan/vulkan_operators.cpp:345-434); 0: k is [seq_kv, head_dim].  causal = 1
+ * limits row i to keys < i + start_pos + 1 (the Metal operator,
+ * src/operators/metal/metal_operators.mm:619-690).  dtype 0 = fp32, 1 = fp16 (all four buffers). */
+typedef struct {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* output;
+    uint32_t seq_q;
+    uint32_t seq_kv;
+    uint32_t head_dim;
+    uint32_t dtype;
+    uint32_t k_transposed;
+    uint32_t causal;
+    uint32_t start_pos;
+    float scale;
+} GraniteCudaSdpaArgs;
+
+int granite_cuda_sdpa(granite_cuda_compute_t* c, const GraniteCudaSdpaArgs* args);
+
+/* ---- K/V cache writes ---------------------------------------------------------------------------
+ * MetalCompute::kv_cache_append (metal_compute.h:787-797; kernel kv_cache_append_f16,
+ * metal_shaders_attention.h:102-132): new_k/new_v [new_len, num_kv_heads, head_dim] fp32 are
+ * written at rows [current_len, current_len + new_len) of cache_k/cache_v
+ * [num_kv_heads, max_seq_len, head_dim] fp16.  Overflow is InvalidArgument as in
+ * KVCache::append (src/llm/kv_cache.cpp:60-64).
+ * fp32 -> fp16 follows Granite's CPU path bit for bit (truncation, src/llm/math_ops.cpp:45-54). */
+typedef struct {
+    void* cache_k;
+    void* cache_v;
+    const void* new_k;
+    const void* new_v;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t current_len;
+    uint32_t new_len;
+    uint32_t max_seq_len;
+} GraniteCudaKvAppendArgs;
+
+int granite_cuda_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaKvAppendArgs* args);
+
+/* MetalCompute::paged_kv_cache_append (metal_compute.h:887-898; kernel
+ * metal_shaders_attention.h:2142-2176): new_k/new_v [num_kv_heads, new_len, head_dim] fp32 go to
+ * positions [start_pos, start_pos + new_len) of one sequence through block_table
+ * [table_len] int32.  With `positions` non-NULL it is the batched decode-step form instead:
+ * new_k/new_v [batch_size, num_kv_heads, head_dim], token b goes to position positions[b] of
+ * sequence b through row b of block_table [batch_size, table_len]. */
+typedef struct {
+    const void* new_k;
+    const void* new_v;
+    void* k_cache;               /* pool [num_blocks*block_size, num_kv_heads, head_dim] fp16 */
+    void* v_cache;
+    const int32_t* block_table;  /* device */
+    const int32_t* positions;    /* device [batch_size] or NULL */
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t start_pos;
+    uint32_t new_len;
+    uint32_t block_size;
+    uint32_t num_blocks;
+    uint32_t table_len;          /* entries per block-table row */
+    uint32_t batch_size;         /* used only with positions */
+} GraniteCudaPagedKvAppendArgs;
+
+int granite_cuda_paged_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaPagedKvAppendArgs* args);
+
 /* ---- tree attention for speculative-decoding verification -----------------------------------
  * MetalCompute::attention_tree (metal_compute.h:830-844, metal_compute.mm:2463-2529): every tree
  * node attends to the whole committed prefix and, among the tree nodes, to itself and its

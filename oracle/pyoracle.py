@@ -189,6 +189,8 @@ class Ref:
                                          _u16p, _u16p, _i32p]
         r.ref_speculation_tree.restype = C.c_int
         r.ref_speculation_tree.argtypes = [_i32p, C.c_int, _i32p, _i32p, _i32p, _i32p, _i32p]
+        r.ref_find_accepted_path.restype = C.c_int
+        r.ref_find_accepted_path.argtypes = [_i32p, _i32p, C.c_int, _i32p, C.c_int, _i32p, _i32p]
         self._r = r
 
     def fp16_to_fp32(self, h: int) -> float:
@@ -245,3 +247,12 @@ class Ref:
         md = np.zeros(1, np.int32)
         self._r.ref_speculation_tree(parents, n, po, dep, bfs, nb, md)
         return dict(parents=po, depths=dep, bfs=bfs[: int(nb[0])], max_depth=int(md[0]))
+
+    def find_accepted_path(self, parents, tokens, targets):
+        parents = np.ascontiguousarray(parents, np.int32)
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        targets = np.ascontiguousarray(targets, np.int32)
+        out = np.zeros(len(targets) + 1, np.int32)
+        n = np.zeros(1, np.int32)
+        self._r.ref_find_accepted_path(parents, tokens, len(parents), targets, len(targets), out, n)
+        return out[: int(n[0])]

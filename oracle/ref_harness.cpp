@@ -177,4 +177,16 @@ int ref_speculation_tree(const int32_t* parents, int n, int32_t* parents_out, in
     return 0;
 }
 
+// SpeculationTree::find_accepted_path (src/llm/speculation_tree.cpp:85-143) on a tree built from
+// (token, parent) pairs.
+int ref_find_accepted_path(const int32_t* parents, const int32_t* tokens, int n, const int32_t* targets,
+                           int n_targets, int32_t* out, int32_t* n_out) {
+    SpeculationTree tree;
+    for (int i = 0; i < n; i++) tree.add_node(tokens[i], parents[i], 0.0f);
+    auto path = tree.find_accepted_path(std::vector<int32_t>(targets, targets + n_targets));
+    *n_out = static_cast<int32_t>(path.size());
+    for (size_t i = 0; i < path.size(); i++) out[i] = path[i];
+    return 0;
+}
+
 }  // extern "C"

@@ -107,6 +107,18 @@ def ref_spec_tree(ref):
         out[f"depths{i}"] = r["depths"]
         out[f"bfs{i}"] = r["bfs"]
         out[f"max_depth{i}"] = np.array([r["max_depth"]], np.int32)
+    # accepted-path search (speculation_tree.cpp:85-143) on small-vocabulary trees
+    rng = np.random.default_rng(11)
+    for i in range(6):
+        n = int(rng.integers(1, 40))
+        parents = synth.tree_parents(200 + i, n)
+        tokens = rng.integers(0, 4, size=n).astype(np.int32)
+        targets = rng.integers(0, 4, size=int(rng.integers(1, 10))).astype(np.int32)
+        targets[0] = tokens[0] if i % 3 else targets[0]
+        out[f"ap_parents{i}"] = parents
+        out[f"ap_tokens{i}"] = tokens
+        out[f"ap_targets{i}"] = targets
+        out[f"ap_path{i}"] = ref.find_accepted_path(parents, tokens, targets)
     np.savez_compressed(HERE / "ref_spec_tree.npz", **out)
 
 

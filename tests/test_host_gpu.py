@@ -1,0 +1,199 @@
+"""The C++ faces (CudaBackend, CudaAttentionOp, KVCache, PagedKVPool + CudaCompute) on a GPU, driven
+through their extern "C" test drivers, plus the K/V append kernels through the C ABI."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from conftest import assert_attention_close
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+
+
+def _lib():
+    import granite_b200 as g
+    lib = g.lib
+    lib.granite_host_last_error.restype = C.c_char_p
+    lib.granite_host_backend_selftest.argtypes = [C.c_int]
+    lib.granite_host_operator_attention.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                    C.c_int, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int64]
+    lib.granite_host_kvcache_append.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, _u16p, _u16p,
+                                                _u16p, _u16p, _i32p, _i32p]
+    lib.granite_host_paged_flow.argtypes = [C.c_int, C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            _f32p, _f32p, _f32p, _f32p, _i32p, C.c_int, _u16p, _u16p, C.c_int]
+    return lib
+
+
+def test_backend_buffer_semantics():
+    lib = _lib()
+    rc = lib.granite_host_backend_selftest(0)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+
+
+def test_operator_known_answer_2x3x4():
+    """The reference's one attention test (tests/test_vulkan.cpp:353-482), same flow, CUDA backend."""
+    lib = _lib()
+    g = np.load(GOLD / "kat_sdpa_2x3x4.npz")
+    q, kt, v = (np.ascontiguousarray(g[k], np.float32) for k in ("q", "kt", "v"))
+    out = np.zeros_like(q)
+    rc = lib.granite_host_operator_attention(0, 0, q.ctypes.data, kt.ctypes.data, v.ctypes.data, out.ctypes.data,
+                                             2, 3, 4, 1, float(g["scale"][0]), 0)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+    assert np.abs(out - g["expected"]).max() <= 1e-4  # the reference test's bound
+
+
+@pytest.mark.parametrize("dtype,sq,skv,d,start_pos", [(0, 7, 33, 16, 0), (0, 50, 300, 128, 0), (1, 5, 9, 64, 0),
+                                                      (1, 6, 40, 32, 11)])
+def test_operator_layouts(dtype, sq, skv, d, start_pos):
+    """fp32: K pre-transposed, no mask (Vulkan contract); fp16: K row-major with the causal limit
+    q + start_pos + 1 (Metal contract); default scale 1/sqrt(D)."""
+    from oracle import pyoracle
+    lib = _lib()
+    rng = np.random.default_rng(sq * 100 + skv)
+    q = rng.standard_normal((sq, d), np.float32)
+    k = rng.standard_normal((skv, d), np.float32)
+    v = rng.standard_normal((skv, d), np.float32)
+    if dtype == 0:
+        kt = np.ascontiguousarray(k.T)
+        out = np.zeros((sq, d), np.float32)
+        rc = lib.granite_host_operator_attention(0, 0, q.ctypes.data, kt.ctypes.data, v.ctypes.data, out.ctypes.data,
+                                                 sq, skv, d, 0, 0.0, 0)
+        ref = pyoracle.sdpa_kt(q, kt, v, 1.0 / np.sqrt(d))
+        got = out
+    else:
+        qh, kh, vh = q.astype(np.float16), k.astype(np.float16), v.astype(np.float16)
+        out = np.zeros((sq, d), np.float16)
+        rc = lib.granite_host_operator_attention(0, 1, qh.ctypes.data, kh.ctypes.data, vh.ctypes.data,
+                                                 out.ctypes.data, sq, skv, d, 0, 0.0, start_pos)
+        ref = pyoracle.sdpa_kt(qh.astype(np.float32), np.ascontiguousarray(kh.astype(np.float32).T),
+                               vh.astype(np.float32), 1.0 / np.sqrt(d), causal_start_pos=start_pos)
+        got = out.astype(np.float32)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+    assert_attention_close(got, ref, f"operator dtype={dtype}")
+
+
+def test_kvcache_append_layout_matches_reference():
+    """Device KVCache against the bytes the reference KVCache produced (src/llm/kv_cache.cpp:52-107)."""
+    lib = _lib()
+    g = np.load(GOLD / "ref_kvcache_append.npz")
+    hkv, d, max_seq = (int(x) for x in g["shape"])
+    steps = np.ascontiguousarray(g["steps"], np.int32)
+    k_out = np.zeros((hkv, max_seq, d), np.uint16)
+    v_out = np.zeros_like(k_out)
+    fl, oc = np.zeros(1, np.int32), np.zeros(1, np.int32)
+    rc = lib.granite_host_kvcache_append(0, hkv, d, max_seq, steps, len(steps), np.ascontiguousarray(g["k_chunks"]),
+                                         np.ascontiguousarray(g["v_chunks"]), k_out.reshape(-1), v_out.reshape(-1),
+                                         fl, oc)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+    assert np.array_equal(k_out, g["k_out"]) and np.array_equal(v_out, g["v_out"])
+    assert int(fl[0]) == int(g["final_len"][0])
+    assert int(oc[0]) == 16  # InvalidArgument: "KV cache overflow"
+
+
+@pytest.mark.parametrize("lens,hq,hkv,step", [([40, 7, 129, 16], 32, 8, 24), ([300], 8, 2, 300), ([5, 5, 5], 16, 4, 1)])
+def test_page_manager_in_hbm_end_to_end(lens, hq, hkv, step):
+    """PagedKVPool on the CUDA backend: ragged growth through BlockManager, fp32 K/V appended into
+    the HBM pool by paged_kv_cache_append, tables mirrored to the device, one batched decode.
+    Checks: every row read back through the block table is bit-identical to the reference's
+    truncating fp32->fp16 of what was appended; the decode output matches the CPU attention."""
+    from oracle import pyoracle
+    lib = _lib()
+    d, bs = 128, 16
+    lens_a = np.array(lens, np.int32)
+    batch = len(lens)
+    num_blocks = int(((lens_a + bs - 1) // bs).sum()) + 3
+    max_blocks = int(((lens_a + bs - 1) // bs).max())
+    rng = np.random.default_rng(sum(lens))
+    k_src = [rng.standard_normal((hkv, L, d), np.float32) for L in lens]
+    v_src = [rng.standard_normal((hkv, L, d), np.float32) for L in lens]
+    q = rng.standard_normal((batch, hq, d), np.float32)
+    out = np.zeros((batch, hq, d), np.float32)
+    tables = np.zeros((batch, max_blocks), np.int32)
+    k_pool = np.zeros((num_blocks * bs, hkv, d), np.uint16)
+    v_pool = np.zeros_like(k_pool)
+    rc = lib.granite_host_paged_flow(0, batch, lens_a, hq, hkv, d, bs, num_blocks,
+                                     np.concatenate([a.reshape(-1) for a in k_src]),
+                                     np.concatenate([a.reshape(-1) for a in v_src]), q.reshape(-1), out.reshape(-1),
+                                     tables.reshape(-1), max_blocks, k_pool.reshape(-1), v_pool.reshape(-1), step)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+    trunc = np.vectorize(pyoracle.fp32_to_fp16, otypes=[np.uint16])
+    used = set()
+    for b, L in enumerate(lens):
+        nb = (L + bs - 1) // bs
+        assert (tables[b, :nb] >= 0).all() and (tables[b, nb:] == -1).all()
+        used.update(int(x) for x in tables[b, :nb])
+        rows, bad = pyoracle.paged_gather(k_pool, tables[b].clip(0), L, bs)
+        vrows, _ = pyoracle.paged_gather(v_pool, tables[b].clip(0), L, bs)
+        assert bad == 0
+        assert np.array_equal(rows, trunc(k_src[b]).transpose(1, 0, 2)), f"K rows of sequence {b}"
+        assert np.array_equal(vrows, trunc(v_src[b]).transpose(1, 0, 2)), f"V rows of sequence {b}"
+    assert len(used) == int(((lens_a + bs - 1) // bs).sum())  # no page shared between sequences
+    ref, bad = pyoracle.paged_decode_batch(q, k_pool, v_pool, tables.clip(0), lens_a, bs)
+    assert bad == 0
+    assert_attention_close(out, ref, "decode through the HBM page manager")
+
+
+def test_kv_cache_append_kernel_is_bit_exact(compute):
+    """kv_cache_append through the C ABI: [new_len, H, D] fp32 -> [H, max_seq, D] fp16 with the
+    reference CPU's truncating cast, including values that flush to zero or clamp to infinity."""
+    import torch
+    from oracle import pyoracle
+    dev = "cuda:0"
+    h, d, max_seq, cur, new = 3, 64, 40, 9, 17
+    rng = np.random.default_rng(8)
+    nk = rng.standard_normal((new, h, d), np.float32)
+    nv = rng.standard_normal((new, h, d), np.float32)
+    nk.reshape(-1)[:6] = [1e-8, -1e-8, 70000.0, -70000.0, 0.333374, 6.0e-5]
+    ck = torch.zeros((h, max_seq, d), dtype=torch.float16, device=dev)
+    cv = torch.zeros_like(ck)
+    compute.kv_cache_append(ck, cv, torch.from_numpy(nk).to(dev), torch.from_numpy(nv).to(dev), h, d, cur, new, max_seq)
+    compute.sync()
+    trunc = np.vectorize(pyoracle.fp32_to_fp16, otypes=[np.uint16])
+    want_k = np.zeros((h, max_seq, d), np.uint16)
+    want_v = np.zeros_like(want_k)
+    want_k[:, cur:cur + new] = trunc(nk).transpose(1, 0, 2)
+    want_v[:, cur:cur + new] = trunc(nv).transpose(1, 0, 2)
+    assert np.array_equal(ck.cpu().numpy().view(np.uint16), want_k)
+    assert np.array_equal(cv.cpu().numpy().view(np.uint16), want_v)
+    import granite_b200 as g
+    with pytest.raises(g.GraniteCudaError) as ei:
+        compute.kv_cache_append(ck, cv, ck, cv, h, d, 30, 17, max_seq)
+    assert ei.value.code == g.ErrorCode.InvalidArgument
+
+
+def test_batched_paged_append_then_decode(compute):
+    """A decode step of a batch: one new token per sequence appended at positions[b], then attended."""
+    import torch
+    from oracle import pyoracle
+    from granite_b200 import synth
+    dev = "cuda:0"
+    case = synth.paged_case(seed=31, batch=5, len_lo=1, len_hi=90, num_heads=16, num_kv_heads=4, spare_blocks=0)
+    lens = case.seq_lens.copy()
+    k = torch.from_numpy(case.k_pool).to(dev)
+    v = torch.from_numpy(case.v_pool).to(dev)
+    tables = torch.from_numpy(case.tables).to(dev)
+    rng = np.random.default_rng(2)
+    nk = rng.standard_normal((case.batch, 4, 128), np.float32)
+    nv = rng.standard_normal((case.batch, 4, 128), np.float32)
+    pos = (lens - 1).astype(np.int32)  # overwrite each sequence's last token
+    compute.paged_kv_cache_append(torch.from_numpy(nk).to(dev), torch.from_numpy(nv).to(dev), k, v, tables, 4, 128, 0,
+                                  0, 16, num_blocks=case.num_blocks, table_len=case.max_blocks,
+                                  positions=torch.from_numpy(pos).to(dev), batch_size=case.batch)
+    out = torch.zeros((case.batch, 16, 128), device=dev)
+    compute.batched_paged_attention_decode(torch.from_numpy(case.q).to(dev), k, v, tables, torch.from_numpy(lens).to(dev),
+                                           out, case.batch, 16, 4, 128, 16, case.max_blocks, 1 / np.sqrt(128.0),
+                                           num_blocks=case.num_blocks)
+    compute.sync()
+    trunc = np.vectorize(pyoracle.fp32_to_fp16, otypes=[np.uint16])
+    kp, vp = case.k_pool.view(np.uint16).copy(), case.v_pool.view(np.uint16).copy()
+    for b in range(case.batch):
+        row = case.tables[b, pos[b] // 16] * 16 + pos[b] % 16
+        kp[row], vp[row] = trunc(nk[b]), trunc(nv[b])
+    assert np.array_equal(k.cpu().numpy().view(np.uint16), kp)
+    ref, _ = pyoracle.paged_decode_batch(case.q, kp, vp, case.tables.clip(0), lens, 16)
+    assert_attention_close(out.cpu().numpy(), ref, "append + decode")
