@@ -191,6 +191,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="granite_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
+                    help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
+                         "across the ranks by sequence (strong scaling); not the default benchmark line")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
     args = ap.parse_args()
@@ -215,12 +218,25 @@ def main():
     dev = torch.device("cuda", local_rank if world > 1 else 0)
     n_gpus = world
 
-    cfg = dict(synth.CONFIGS[WORKLOAD])
+    cfg = dict(synth.CONFIGS[args.workload])
     if args.sequences > 0:
         cfg["batch"] = args.sequences
-    seed = cfg["seed"] + 7919 * rank  # every rank owns its own batch of the same shape
-    case = synth.paged_case(seed, cfg["batch"], cfg["len_lo"], cfg["len_hi"], cfg["num_heads"],
-                            cfg["num_kv_heads"], cfg["head_dim"], cfg["dist"], device=dev)
+    strong = args.workload != WORKLOAD
+    if strong:
+        # one fixed problem, sequences dealt to the ranks longest-first (granite_b200/sharding.py)
+        from granite_b200 import sharding
+        lens_all = synth.draw_lengths(np.random.default_rng(cfg["seed"]), cfg["batch"], cfg["len_lo"],
+                                      cfg["len_hi"], cfg["dist"])
+        plan = sharding.lpt_assign(lens_all, world)
+        case = synth.paged_case(cfg["seed"] + 7919 * rank, len(plan[rank]), 0, 0, cfg["num_heads"],
+                                cfg["num_kv_heads"], cfg["head_dim"], seq_lens=lens_all[plan[rank]], device=dev)
+    else:
+        # every rank owns its own batch of the workload's shape: the same seeded context lengths
+        # (per-GPU work is fixed, as weak scaling requires), its own page permutation and K/V/Q values
+        lens = synth.draw_lengths(np.random.default_rng(cfg["seed"]), cfg["batch"], cfg["len_lo"], cfg["len_hi"],
+                                  cfg["dist"])
+        case = synth.paged_case(cfg["seed"] + 7919 * rank, cfg["batch"], 0, 0, cfg["num_heads"],
+                                cfg["num_kv_heads"], cfg["head_dim"], seq_lens=lens, device=dev)
     B, Hq, Hkv, D = case.batch, case.num_heads, case.num_kv_heads, case.head_dim
     scale = 1.0 / float(np.sqrt(D))
     stream = torch.cuda.current_stream()
@@ -234,7 +250,11 @@ def main():
     lens_d = lens_h.to(dev)
     q_d = case.q
     outs = [torch.zeros((B, Hq, D), device=dev) for _ in range(2)]
-    gathered = [torch.empty((world * B, Hq, D), device=dev) for _ in range(2)] if world > 1 else None
+    rows = B
+    if strong and world > 1:
+        rows = sharding.padded_rows(plan)  # ranks own different numbers of sequences
+        outs = [torch.zeros((rows, Hq, D), device=dev) for _ in range(2)]
+    gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)] if world > 1 else None
 
     def decode(q, tables, lens, out):
         compute.batched_paged_attention_decode(q, case.k_pool, case.v_pool, tables, lens, out, B, Hq, Hkv,
@@ -247,9 +267,9 @@ def main():
         out = outs[i & 1]
         decode(q_d, tables_d, lens_d, out)
         if world > 1:
-            pending.append(dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True))
-            if len(pending) > 2:
-                pending.pop(0).wait()
+            # the gather is ordered after this step's kernels and before the next step's: a
+            # persistent one-CTA-per-SM decode kernel must not share SMs with an NCCL kernel
+            dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True).wait()
 
     def barrier():
         if world > 1:
@@ -339,7 +359,7 @@ def main():
 
     # ---- CPU baseline (rank 0, N = 1 only): bounded sample
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not strong:
         from oracle import pyoracle
         sel = list(range(0, cfg["batch"], 8))
         hc = host_case_for_cpu(cfg["seed"], cfg, sel)
@@ -351,12 +371,14 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sequences_per_gpu": B, "context": "uniform[1024,32768]",
+            "config": {"workload": args.workload, "sequences_per_gpu": B,
+                       "context": f"{cfg['dist']}[{cfg['len_lo']},{cfg['len_hi']}]",
                        "page": synth.PAGE, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
                        "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
-                       "l2": "inputs larger than L2 (4.4 GB of K/V per step, no reuse)",
+                       "l2": f"inputs larger than L2 ({case.total_tokens * Hkv * D * 4 / 1e9:.1f} GB of K/V per GPU per step, no reuse)",
                        "sharding": "by sequence; NCCL all-gather of outputs per step" if world > 1 else "single GPU"},
             "hbm_frac_of_measured_peak": value / n_gpus / peak,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
