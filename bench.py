@@ -184,6 +184,109 @@ def run_reference(args):
     return 0
 
 
+def tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+def measure_prefill(compute, dev, reps: int = 40):
+    """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (BASELINE.json configs[1]); the
+    kernel's own event-timed duration, rotating over 4 input sets."""
+    import torch
+    from granite_b200 import synth
+    cfg = synth.CONFIGS["prefill_causal_s2048"]
+    seq, hq, hkv, d = cfg["seq"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(cfg["seed"])
+    sets = [(torch.randn((seq, hq, d), device=dev, generator=gen).half(),
+             torch.randn((hkv, seq, d), device=dev, generator=gen).half(),
+             torch.randn((hkv, seq, d), device=dev, generator=gen).half()) for _ in range(4)]
+    out = torch.zeros((seq, hq, d), device=dev, dtype=torch.float16)
+
+    def step(i):
+        q, k, v = sets[i % 4]
+        compute.multihead_attention(q, k, v, out, hq, hkv, seq, seq, d, 1.0 / float(np.sqrt(d)), seq,
+                                    q_dtype=1, out_dtype=1)
+
+    for i in range(5):
+        step(i)
+    compute.sync()
+    compute.enable_kernel_timing(True)
+    compute.reset_kernel_timing()
+    for i in range(reps):
+        step(i)
+    st = compute.get_kernel_timing_stats()
+    compute.enable_kernel_timing(False)
+    ms = st["prefill_causal_fa"][0] / st["prefill_causal_fa"][1]
+    flops = 4 * d * hq * seq * (seq + 1) // 2
+    burst, sustained, kind = tensor_peak()
+    tf = flops / ms / 1e9
+    return {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms, "launches": reps,
+            "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst,
+            "frac": tf / burst, "frac_of_sustained": tf / sustained, "peak_kind": kind,
+            "note": "unmasked half of the causal square counted only; P enters the PV product as fp16 hi+lo "
+                    "(two MMAs) to keep the CPU path's precision, which the flop count does not credit"}
+
+
+def measure_tree(compute, dev, reps: int = 30):
+    """Tree verification: 16 sequences x (4096-token paged prefix + 64-node tree), Hq 32, Hkv 8
+    (BASELINE.json configs[3]); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
+    import torch
+    from granite_b200 import synth
+    cfg = synth.CONFIGS["tree_verify_b16"]
+    batch, n, hq, hkv, L, d = cfg["batch"], cfg["nodes"], cfg["num_heads"], cfg["num_kv_heads"], cfg["prefix"], 128
+    cases = [synth.paged_case(cfg["seed"] + i, batch, 0, 0, hq, hkv, seq_lens=np.full(batch, L, np.int32), device=dev)
+             for i in range(3)]
+    tables = [torch.from_numpy(c.tables).to(dev) for c in cases]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(cfg["seed"] + 500)
+    q = torch.randn((batch, hq, n, d), device=dev, generator=gen).half()
+    kt = torch.randn((batch, hkv, n, d), device=dev, generator=gen).half()
+    vt = torch.randn((batch, hkv, n, d), device=dev, generator=gen).half()
+    parents_np = np.stack([synth.tree_parents(cfg["seed"] + 500 + b, n, cfg["max_children"], cfg["max_depth"])
+                           for b in range(batch)])
+    parents = torch.from_numpy(parents_np).to(dev)
+    out = torch.zeros((batch, hq, n, d), device=dev)
+
+    def step(i):
+        c = cases[i % 3]
+        compute.attention_tree(q, c.k_pool, c.v_pool, kt, vt, parents, out, hq, hkv, n, L, d,
+                               1.0 / float(np.sqrt(d)), batch_size=batch, block_tables=tables[i % 3],
+                               max_blocks_per_seq=c.max_blocks, num_blocks=c.num_blocks, q_dtype=1)
+
+    for i in range(4):
+        step(i)
+    compute.sync()
+    compute.enable_kernel_timing(True)
+    compute.reset_kernel_timing()
+    for i in range(reps):
+        step(i)
+    st = compute.get_kernel_timing_stats()
+    compute.enable_kernel_timing(False)
+    ms = st["tree_verify"][0] / st["tree_verify"][1]
+    visible = 0
+    for b in range(batch):  # self + ancestors of every node
+        for i in range(n):
+            c, depth = parents_np[b, i], 1
+            while c >= 0:
+                depth += 1
+                c = parents_np[b, c]
+            visible += depth
+    flops = 4 * d * hq * (batch * n * L + visible)
+    nbytes = batch * L * hkv * d * 4 + batch * (L // 16) * 4 + 2 * batch * hkv * n * d * 2 + batch * hq * n * d * (2 + 4)
+    burst, sustained, kind = tensor_peak()
+    hbm, hkind = measured_peaks()
+    tf = flops / ms / 1e9
+    gbs = nbytes / ms / 1e6
+    return {"workload": "tree_verify_b16", "kernel": "tree_verify", "kernel_ms": ms, "launches": reps,
+            "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
+            "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
+            "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -194,6 +297,8 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
+    ap.add_argument("--only", default="", choices=["", "prefill", "tree"],
+                    help="run just one of the secondary tensor-bound workloads (profiling captures)")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
     args = ap.parse_args()
@@ -217,6 +322,13 @@ def main():
         torch.cuda.set_device(0)
     dev = torch.device("cuda", local_rank if world > 1 else 0)
     n_gpus = world
+
+    if args.only:
+        compute = g.CudaCompute(dev.index, torch.cuda.current_stream().cuda_stream)
+        fn = measure_prefill if args.only == "prefill" else measure_tree
+        print(json.dumps(fn(compute, dev, max(args.steps, 1))), flush=True)
+        compute.shutdown()
+        return 0
 
     cfg = dict(synth.CONFIGS[args.workload])
     if args.sequences > 0:
@@ -368,6 +480,10 @@ def main():
                "sample": f"every 8th sequence ({nseq} of {cfg['batch']}, {int(hc['seq_lens'].sum())} tokens), "
                          f"best of 2, {secs:.2f} s each"}
 
+    secondary = None
+    if world == 1 and not strong and args.sequences == 0:
+        secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev)}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
@@ -387,6 +503,7 @@ def main():
                             "K/V pages are cache state resident in HBM"},
             "gpu_launches": 3 * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+            "secondary": secondary,
         }
         print(json.dumps(line), flush=True)
     compute.shutdown()

@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
     "-Xptxas", "-v",
     f"-I{INCLUDE}",
-]
+] + os.environ.get("GB_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

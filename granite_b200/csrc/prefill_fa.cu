@@ -17,10 +17,22 @@
 //               of O in TMEM), which is exact because l and O always share the same reference
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t aliases the first 64 of S_t.
 // Accumulation is fp32 throughout; P is rounded to fp16 only as the MMA input.
+#include <cstdio>
+#include <cstring>
+
 #include "compute_internal.h"
 #include "ptx.cuh"
 
 namespace gb200 {
+
+// Development aid: built with -DGB_FA_TRACE the first CTA records clock64() at the hand-over points
+// of its roles (slot = role * 64 + step * 4 + event) and the launcher prints the timeline.
+#ifdef GB_FA_TRACE
+#define FA_TRACE(role, step, ev) \
+    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (step) < 16) p.trace[(role) * 64 + (step) * 4 + (ev)] = clock64(); } while (0)
+#else
+#define FA_TRACE(role, step, ev) do {} while (0)
+#endif
 
 constexpr int kFaThreads = 384;
 constexpr int kTile = 128;                    // query rows per tile, keys per KV tile, head_dim
@@ -37,6 +49,7 @@ struct FaParams {
     int start_pos;
     float scale_log2;
     int* status;
+    unsigned long long* trace;  // timeline hook, only used in GB_FA_TRACE builds
 };
 
 struct FaSmem {
@@ -110,6 +123,8 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
 
+    if (warp < 4) {
+    setmaxnreg_dec<56>();  // producer / MMA warpgroup gives registers up
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -154,35 +169,41 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, false, false);
             constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kTile, false, true);
             const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+            // descriptor low words of every operand base; a k-step only adds a constant
+            const uint32_t q_lo[2] = {desc_lo(q_addr, 16), desc_lo(q_addr + kTileBytes, 16)};
+            const uint32_t k_lo[2] = {desc_lo(k_addr, 16), desc_lo(k_addr + kTileBytes, 16)};
+            const uint32_t v_lo[2] = {desc_lo(v_addr, kChunkBytes), desc_lo(v_addr + kTileBytes, kChunkBytes)};
             auto issue_qk = [&](int t, int s) {
-                // S_t = Q_t K^T: K-major operands, 8 steps of 16 along head_dim
+                // S_t = Q_t K^T: K-major operands, 8 steps of 16 along head_dim (32 bytes inside the
+                // swizzled row, the second 64-wide block 16 KB further)
+                const uint32_t d = tmem + t * kTile;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (ks >> 2) * kChunkBytes + (ks & 3) * 32;
-                    umma_ss(tmem + t * kTile, smem_desc_sw128(q_addr + t * kTileBytes + off, 16, 1024),
-                            smem_desc_sw128(k_addr + s * kTileBytes + off, 16, 1024), idesc_qk, ks > 0);
+                    const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                    umma_ss_words(d, q_lo[t] + off, k_lo[s] + off, kDescHiSw128, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 if (kSplitQ) {  // + Q_lo K^T (the low halves sit in the second query slot)
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++) {
-                        const uint32_t off = (ks >> 2) * kChunkBytes + (ks & 3) * 32;
-                        umma_ss(tmem + t * kTile, smem_desc_sw128(q_addr + kTileBytes + off, 16, 1024),
-                                smem_desc_sw128(k_addr + s * kTileBytes + off, 16, 1024), idesc_qk, true);
+                        const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                        umma_ss_words(d, q_lo[1] + off, k_lo[s] + off, kDescHiSw128, idesc_qk, 1u);
                     }
                 }
             };
             auto issue_pv = [&](int t, int s, bool acc) {
                 // O_t += P_t V: P from TMEM (8 columns per 16 keys), V MN-major in shared memory
+                // (16 keys = 2 KB further per step; the second 64-wide block of head_dim via LBO)
+                const uint32_t d = tmem + 2 * kTile + t * kTile;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint64_t vdesc = smem_desc_sw128(v_addr + s * kTileBytes + ks * 2048, kChunkBytes, 1024);
+                    const uint32_t vl = v_lo[s] + ks * (2048 >> 4);
                     if (kSplitP) {
                         // each 64-column half of S_t was replaced by 32 columns of P_hi + 32 of P_lo
                         const uint32_t a_hi = tmem + t * kTile + (ks >> 2) * 64 + (ks & 3) * 8;
-                        umma_ts(tmem + 2 * kTile + t * kTile, a_hi, vdesc, idesc_pv, acc || ks > 0);
-                        umma_ts(tmem + 2 * kTile + t * kTile, a_hi + 32, vdesc, idesc_pv, true);
+                        umma_ts_words(d, a_hi, vl, kDescHiSw128, idesc_pv, (acc || ks > 0) ? 1u : 0u);
+                        umma_ts_words(d, a_hi + 32, vl, kDescHiSw128, idesc_pv, 1u);
                     } else {
-                        umma_ts(tmem + 2 * kTile + t * kTile, tmem + t * kTile + ks * 8, vdesc, idesc_pv, acc || ks > 0);
+                        umma_ts_words(d, tmem + t * kTile + ks * 8, vl, kDescHiSw128, idesc_pv, (acc || ks > 0) ? 1u : 0u);
                     }
                 }
             };
@@ -203,8 +224,10 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 const bool more = j + 1 < n_kv;
                 const int s2 = (j + 1) & 1;
                 const uint32_t ph2 = ((j + 1) >> 1) & 1;
+                FA_TRACE(0, j, 0);
                 ok = mbar_wait(&sh->v_full[s], ph, abort_flag) && mbar_wait(&sh->p_ready[0], j & 1, abort_flag);
                 if (!ok) break;
+                FA_TRACE(0, j, 1);
                 tc_fence_after_sync();
                 issue_pv(0, s, j > 0);
                 if (!more) tc_commit(&sh->o_final[0]);
@@ -216,8 +239,10 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     tc_commit(&sh->s_full[0]);
                 }
                 if (valid1) {
+                    FA_TRACE(0, j, 2);
                     ok = mbar_wait(&sh->p_ready[1], j & 1, abort_flag);
                     if (!ok) break;
+                    FA_TRACE(0, j, 3);
                     tc_fence_after_sync();
                     issue_pv(1, s, j > 0);
                     if (!more) tc_commit(&sh->o_final[1]);
@@ -233,7 +258,9 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             }
             if (!ok) atomicOr(p.status, kStatusTimeout);
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+        setmaxnreg_inc<224>();  // softmax warpgroups hold a whole S row in registers
         // ------------------------------------------------------------------ softmax + epilogue
         const int t = (warp - 4) >> 2;           // which query tile
         const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
@@ -247,27 +274,43 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             float m_used = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_kv; j++) {
+                if (quarter == 0) FA_TRACE(1 + t, j, 0);
                 ok = mbar_wait(&sh->s_full[t], j & 1, abort_flag);
                 if (!ok) break;
+                if (quarter == 0) FA_TRACE(1 + t, j, 1);
                 tc_fence_after_sync();
                 const int k0 = j * kTile;
                 const bool need_mask = (k0 + kTile - 1 > p.start_pos + q0) || (k0 + kTile > p.seq_kv);
                 const int limit = last_visible - k0;  // column c is visible iff c <= limit
-                uint32_t r[32];
-                // pass 1: row maximum
+                // S row (128 fp32) into registers: four loads in flight, one wait
+                uint32_t x0[32], x1[32], x2[32], x3[32];
+                tmem_ld32(s_addr, x0);
+                tmem_ld32(s_addr + 32, x1);
+                tmem_ld32(s_addr + 64, x2);
+                tmem_ld32(s_addr + 96, x3);
+                tmem_wait_ld();
+                if (quarter == 0) FA_TRACE(1 + t, j, 2);
                 float mx = -INFINITY;
-#pragma unroll 1
-                for (int ch = 0; ch < 4; ch++) {
-                    tmem_ld32(s_addr + ch * 32, r);
-                    tmem_wait_ld();
-                    if (need_mask) {
+                if (need_mask) {
 #pragma unroll
-                        for (int c = 0; c < 32; c++)
-                            if (ch * 32 + c <= limit) mx = fmaxf(mx, __uint_as_float(r[c]));
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; c++) mx = fmaxf(mx, __uint_as_float(r[c]));
+                    for (int c = 0; c < 32; c++) {
+                        if (c > limit) x0[c] = 0xFF800000u;        // -inf
+                        if (32 + c > limit) x1[c] = 0xFF800000u;
+                        if (64 + c > limit) x2[c] = 0xFF800000u;
+                        if (96 + c > limit) x3[c] = 0xFF800000u;
                     }
+                }
+                {
+                    // four independent chains (short dependency depth: two warps share a scheduler)
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        m0 = fmaxf(m0, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x0[c + 1])));
+                        m1 = fmaxf(m1, fmaxf(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1])));
+                        m2 = fmaxf(m2, fmaxf(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1])));
+                        m3 = fmaxf(m3, fmaxf(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1])));
+                    }
+                    mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                 }
                 mx *= p.scale_log2;
                 if (j == 0) {
@@ -279,6 +322,7 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
                         if (grow) m_used = mx;
                         l_run *= alpha;
+                        uint32_t r[32];
 #pragma unroll 1
                         for (int ch = 0; ch < 4; ch++) {
                             tmem_ld32(o_addr + ch * 32, r);
@@ -289,41 +333,34 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         }
                     }
                 }
-                // pass 2: P = 2^(s*scale - m) as fp16 (hi, and lo = P - hi when kSplitP), written over S
-                float lsum = 0.f;
-#pragma unroll 1
-                for (int half = 0; half < 2; half++) {
-                    uint32_t pk[32], pl[kSplitP ? 32 : 1];
+                // P = 2^(s*scale - m): fp16 hi (and lo = P - hi when kSplitP) written over S.  Each
+                // 64-column half of S becomes 32 columns of hi followed by 32 columns of lo.
+                float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial sums
+                const float neg_m = -m_used;
+                auto emit = [&](uint32_t (&x)[32], int chunk) {
+                    uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int sub = 0; sub < 2; sub++) {
-                        tmem_ld32(s_addr + half * 64 + sub * 32, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-                            if (need_mask) {
-                                const int col = half * 64 + sub * 32 + c;
-                                if (col > limit) p0 = 0.f;
-                                if (col + 1 > limit) p1 = 0.f;
-                            }
-                            lsum += p0 + p1;
-                            const __half2 h = __floats2half2_rn(p0, p1);
-                            pk[sub * 16 + (c >> 1)] = *reinterpret_cast<const uint32_t*>(&h);
-                            if (kSplitP) {
-                                const float2 b = __half22float2(h);
-                                pl[sub * 16 + (c >> 1)] = pack_half2(p0 - b.x, p1 - b.y);
-                            }
-                        }
+                    for (int c = 0; c < 32; c += 2) {
+                        // masked scores are -inf: exp2 gives exactly 0
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(x[c]), p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(x[c + 1]), p.scale_log2, neg_m));
+                        ls[c & 6] += p0;
+                        ls[(c & 6) + 1] += p1;
+                        if (kSplitP) split_hi_lo(p0, p1, hi[c >> 1], lo[c >> 1]);
+                        else hi[c >> 1] = pack_half2(p0, p1);
                     }
                     if (kSplitP) {
-                        tmem_st32(s_addr + half * 64, pk);
-                        tmem_st32(s_addr + half * 64 + 32, pl);
+                        tmem_st16(s_addr + (chunk >> 1) * 64 + (chunk & 1) * 16, hi);
+                        tmem_st16(s_addr + (chunk >> 1) * 64 + 32 + (chunk & 1) * 16, lo);
                     } else {
-                        tmem_st32(s_addr + half * 32, pk);
+                        tmem_st16(s_addr + chunk * 16, hi);
                     }
-                }
-                l_run += lsum;
+                };
+                emit(x0, 0);
+                emit(x1, 1);
+                emit(x2, 2);
+                emit(x3, 3);
+                l_run += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
                 if (t == 0 && k0 + kTile > p.seq_kv) {
                     // keys past seq_kv carry P = 0, but their V rows may hold anything (even NaN):
                     // zero them in shared memory before the MMA reads the tile
@@ -343,6 +380,7 @@ prefill_fa_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&sh->p_ready[t]);
+                if (quarter == 0) FA_TRACE(1 + t, j, 3);
             }
             if (ok) ok = mbar_wait(&sh->o_final[t], 0, abort_flag);
             if (ok) {
@@ -448,10 +486,28 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     auto kern = split_q ? prefill_fa_kernel<true, true> : prefill_fa_kernel<true, false>;
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     const int grid = p.n_qblocks * p.num_kv_heads * p.pairs;
+#ifdef GB_FA_TRACE
+    static unsigned long long* trace_buf = nullptr;
+    if (!trace_buf) cudaMallocManaged(&trace_buf, 3 * 64 * sizeof(unsigned long long));
+    memset(trace_buf, 0, 3 * 64 * sizeof(unsigned long long));
+    p.trace = trace_buf;
+#endif
     {
         LaunchScope t(c, "prefill_causal_fa");
         kern<<<grid, kFaThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, p);
     }
+#ifdef GB_FA_TRACE
+    cudaStreamSynchronize(c->stream);
+    {
+        unsigned long long t0 = trace_buf[64 + 1];  // softmax 0, step 0, S ready
+        const char* roles[3] = {"mma", "sm0", "sm1"};
+        for (int step = 0; step < 16; step++)
+            for (int r = 0; r < 3; r++)
+                fprintf(stderr, "trace %s step %2d: %8lld %8lld %8lld %8lld\n", roles[r], step,
+                        (long long)(trace_buf[r * 64 + step * 4 + 0] - t0), (long long)(trace_buf[r * 64 + step * 4 + 1] - t0),
+                        (long long)(trace_buf[r * 64 + step * 4 + 2] - t0), (long long)(trace_buf[r * 64 + step * 4 + 3] - t0));
+    }
+#endif
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }

@@ -139,6 +139,8 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
 
+    if (warp < 4) {
+    setmaxnreg_dec<56>();  // producer / MMA warpgroup gives registers up
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (whole warp)
         if (lane == 0) {
@@ -230,30 +232,36 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             constexpr uint32_t idesc_pv = umma_idesc_f16(kTvTile, kTvTile, false, true);
             constexpr uint32_t idesc_qk_tree = umma_idesc_f16(kTvTile, kNodeSlots, false, false);
             const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+            const uint32_t q_lo[2] = {desc_lo(q_addr, 16), desc_lo(q_addr + kTvTileBytes, 16)};
+            const uint32_t k_lo[2] = {desc_lo(k_addr, 16), desc_lo(k_addr + kTvTileBytes, 16)};
+            const uint32_t v_lo[2] = {desc_lo(v_addr, kTvChunkBytes), desc_lo(v_addr + kTvTileBytes, kTvChunkBytes)};
             auto issue_qk = [&](int t, int s, bool tree_step) {
                 const uint32_t idesc = tree_step ? idesc_qk_tree : idesc_qk;
+                const uint32_t d = tmem + t * kTvTile;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (ks >> 2) * kTvChunkBytes + (ks & 3) * 32;
-                    umma_ss(tmem + t * kTvTile, smem_desc_sw128(q_addr + t * kTvTileBytes + off, 16, 1024),
-                            smem_desc_sw128(k_addr + s * kTvTileBytes + off, 16, 1024), idesc, ks > 0);
+                    const uint32_t off = ((ks >> 2) * kTvChunkBytes + (ks & 3) * 32) >> 4;
+                    umma_ss_words(d, q_lo[t] + off, k_lo[s] + off, kDescHiSw128, idesc, ks > 0 ? 1u : 0u);
                 }
                 if (kSplitQ) {
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++) {
-                        const uint32_t off = (ks >> 2) * kTvChunkBytes + (ks & 3) * 32;
-                        umma_ss(tmem + t * kTvTile, smem_desc_sw128(q_addr + kTvTileBytes + off, 16, 1024),
-                                smem_desc_sw128(k_addr + s * kTvTileBytes + off, 16, 1024), idesc, true);
+                        const uint32_t off = ((ks >> 2) * kTvChunkBytes + (ks & 3) * 32) >> 4;
+                        umma_ss_words(d, q_lo[1] + off, k_lo[s] + off, kDescHiSw128, idesc, 1u);
                     }
                 }
             };
             auto issue_pv = [&](int t, int s, bool acc, bool tree_step) {
                 const int nks = tree_step ? 4 : 8;  // 16 keys per step
-                for (int ks = 0; ks < nks; ks++) {
-                    const uint64_t vdesc = smem_desc_sw128(v_addr + s * kTvTileBytes + ks * 2048, kTvChunkBytes, 1024);
-                    const uint32_t a_hi = tmem + t * kTvTile + (ks >> 2) * 64 + (ks & 3) * 8;
-                    umma_ts(tmem + 2 * kTvTile + t * kTvTile, a_hi, vdesc, idesc_pv, acc || ks > 0);
-                    umma_ts(tmem + 2 * kTvTile + t * kTvTile, a_hi + 32, vdesc, idesc_pv, true);
+                const uint32_t d = tmem + 2 * kTvTile + t * kTvTile;
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    if (ks < nks) {
+                        const uint32_t vl = v_lo[s] + ks * (2048 >> 4);
+                        const uint32_t a_hi = tmem + t * kTvTile + (ks >> 2) * 64 + (ks & 3) * 8;
+                        umma_ts_words(d, a_hi, vl, kDescHiSw128, idesc_pv, (acc || ks > 0) ? 1u : 0u);
+                        umma_ts_words(d, a_hi + 32, vl, kDescHiSw128, idesc_pv, 1u);
+                    }
                 }
             };
             bool ok = mbar_wait(&sh->q_full, 0, abort_flag) && mbar_wait(&sh->k_full[0], 0, abort_flag);
@@ -304,7 +312,9 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             }
             if (!ok) atomicOr(p.status, kStatusTimeout);
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+        setmaxnreg_inc<224>();  // softmax warpgroups hold a whole S row in registers
         // ------------------------------------------------------------------ softmax + epilogue
         const int t = (warp - 4) >> 2;
         const int quarter = warp & 3;
@@ -330,21 +340,43 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                 auto visible = [&](int col) {
                     return tree_step ? ((anc >> col) & 1ull) != 0 : col <= limit;
                 };
-                const int nch = tree_step ? 2 : 4;  // 32-column chunks of S
-                uint32_t r[32];
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int ch = 0; ch < nch; ch++) {
-                    tmem_ld32(s_addr + ch * 32, r);
-                    tmem_wait_ld();
-                    if (need_mask) {
+                // S row into registers (128 columns for a prefix tile, 64 for the tree tile)
+                uint32_t x0[32], x1[32], x2[32], x3[32];
+                tmem_ld32(s_addr, x0);
+                tmem_ld32(s_addr + 32, x1);
+                if (!tree_step) {
+                    tmem_ld32(s_addr + 64, x2);
+                    tmem_ld32(s_addr + 96, x3);
+                }
+                tmem_wait_ld();
+                if (tree_step) {
 #pragma unroll
-                        for (int c = 0; c < 32; c++)
-                            if (visible(ch * 32 + c)) mx = fmaxf(mx, __uint_as_float(r[c]));
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; c++) mx = fmaxf(mx, __uint_as_float(r[c]));
+                    for (int c = 0; c < 32; c++) {
+                        if (!((anc >> c) & 1ull)) x0[c] = 0xFF800000u;         // -inf
+                        if (!((anc >> (32 + c)) & 1ull)) x1[c] = 0xFF800000u;
+                        x2[c] = 0xFF800000u;
+                        x3[c] = 0xFF800000u;
                     }
+                } else if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) {
+                        if (c > limit) x0[c] = 0xFF800000u;
+                        if (32 + c > limit) x1[c] = 0xFF800000u;
+                        if (64 + c > limit) x2[c] = 0xFF800000u;
+                        if (96 + c > limit) x3[c] = 0xFF800000u;
+                    }
+                }
+                float mx;
+                {
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        m0 = fmaxf(m0, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x0[c + 1])));
+                        m1 = fmaxf(m1, fmaxf(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1])));
+                        m2 = fmaxf(m2, fmaxf(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1])));
+                        m3 = fmaxf(m3, fmaxf(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1])));
+                    }
+                    mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                 }
                 mx *= p.scale_log2;
                 if (j == 0) {
@@ -355,6 +387,7 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                         const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
                         if (grow) m_used = mx;
                         l_run *= alpha;
+                        uint32_t r[32];
 #pragma unroll 1
                         for (int ch = 0; ch < 4; ch++) {
                             tmem_ld32(o_addr + ch * 32, r);
@@ -365,34 +398,28 @@ tree_verify_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                         }
                     }
                 }
-                float lsum = 0.f;
-#pragma unroll 1
-                for (int half = 0; half < (tree_step ? 1 : 2); half++) {
-                    uint32_t pk[32], pl[32];
+                float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                const float neg_m = -m_used;
+                auto emit = [&](uint32_t (&x)[32], int chunk) {
+                    uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int sub2 = 0; sub2 < 2; sub2++) {
-                        tmem_ld32(s_addr + half * 64 + sub2 * 32, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-                            if (need_mask) {
-                                const int col = half * 64 + sub2 * 32 + c;
-                                if (!visible(col)) p0 = 0.f;
-                                if (!visible(col + 1)) p1 = 0.f;
-                            }
-                            lsum += p0 + p1;
-                            const __half2 h = __floats2half2_rn(p0, p1);
-                            const float2 bk = __half22float2(h);
-                            pk[sub2 * 16 + (c >> 1)] = *reinterpret_cast<const uint32_t*>(&h);
-                            pl[sub2 * 16 + (c >> 1)] = pack_half2(p0 - bk.x, p1 - bk.y);
-                        }
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(x[c]), p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(x[c + 1]), p.scale_log2, neg_m));
+                        ls[c & 6] += p0;
+                        ls[(c & 6) + 1] += p1;
+                        split_hi_lo(p0, p1, hi[c >> 1], lo[c >> 1]);
                     }
-                    tmem_st32(s_addr + half * 64, pk);
-                    tmem_st32(s_addr + half * 64 + 32, pl);
+                    tmem_st16(s_addr + (chunk >> 1) * 64 + (chunk & 1) * 16, hi);
+                    tmem_st16(s_addr + (chunk >> 1) * 64 + 32 + (chunk & 1) * 16, lo);
+                };
+                emit(x0, 0);
+                emit(x1, 1);
+                if (!tree_step) {
+                    emit(x2, 2);
+                    emit(x3, 3);
                 }
-                l_run += lsum;
+                l_run += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
                 if (t == 0 && !tree_step && k0 + kTvTile > cache_len) {
                     // prefix keys past cache_len carry P = 0 but their V rows may hold anything
                     const int s = j & 1;
