@@ -207,6 +207,7 @@ int granite_cuda_sync(granite_cuda_compute_t* c) {
     if (st & kStatusBadTable) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a block-table entry was outside the pool");
     if (st & kStatusBadSeqLen) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a sequence length was negative or exceeded its block table");
     if (st & kStatusBadParent) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a tree parent index was out of range");
+    if (st & kStatusLayout) return fail(GRANITE_CUDA_INTERNAL_ERROR, "a kernel's shared-memory layout did not fit its window");
     return fail(GRANITE_CUDA_EXECUTION_FAILED, "device status " + std::to_string(st));
 }
 

@@ -21,6 +21,7 @@ enum : int {
     kStatusBadTable = 2,     // a block-table entry outside [0, num_blocks)
     kStatusBadSeqLen = 4,    // a sequence length outside [0, max_blocks*block_size]
     kStatusBadParent = 8,    // a tree parent index outside [-1, num_nodes)
+    kStatusLayout = 16,      // a kernel found its shared-memory window smaller than its layout
 };
 
 void set_error(const std::string& msg);
