@@ -192,6 +192,14 @@ def tensor_peak():
     return 1590.0, 1400.0, "fallback"
 
 
+def hold_queue(dev, ms: float = 8.0):
+    """Keeps the GPU busy for a few milliseconds so that the launches enqueued next pile up behind
+    it: short kernels are then timed back to back, without the idle-queue launch latency that a
+    host-bound enqueue loop would add to every event pair."""
+    import torch
+    torch.cuda._sleep(int(ms * 1.9e6))
+
+
 def measure_prefill(compute, dev, reps: int = 40):
     """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (BASELINE.json configs[1]); the
     kernel's own event-timed duration, rotating over 4 input sets."""
@@ -216,6 +224,7 @@ def measure_prefill(compute, dev, reps: int = 40):
     compute.sync()
     compute.enable_kernel_timing(True)
     compute.reset_kernel_timing()
+    hold_queue(dev)
     for i in range(reps):
         step(i)
     st = compute.get_kernel_timing_stats()
@@ -262,6 +271,7 @@ def measure_tree(compute, dev, reps: int = 30):
     compute.sync()
     compute.enable_kernel_timing(True)
     compute.reset_kernel_timing()
+    hold_queue(dev)
     for i in range(reps):
         step(i)
     st = compute.get_kernel_timing_stats()

@@ -1,0 +1,906 @@
+// Tensor-core attention for the two contraction-shaped paths, on tcgen05 + TMEM fed by TMA:
+//
+//   causal prefill        replaces flash_attention_prefill
+//                         (src/backend/metal/kernels/metal_shaders_attention.h:1453, dispatched by
+//                         MetalCompute::multihead_attention with seq_q > 1,
+//                         src/backend/metal/metal_compute.mm:2333-2375); arithmetic to match: the CPU
+//                         loop src/llm/transformer.mm:1779-1840 with k_pos > start_pos + q_pos -> -inf
+//   tree verification     replaces attention_tree_f16kv / attention_tree_nocontext_f16kv
+//                         (metal_shaders_attention.h:1677, :1869, dispatched by
+//                         MetalCompute::attention_tree, metal_compute.mm:2463-2529); arithmetic to
+//                         match: src/llm/transformer.mm:2044-2126 with the ancestor mask of :823-840.
+//                         Beyond the reference: a batch of sequences, and a committed prefix that
+//                         lives in the paged pool (block table) as well as in a contiguous cache.
+//
+// One pipeline serves both.  A work item is one or two 128-row query tiles that share every K/V
+// tile (prefill: the two query heads of a GQA pair at one query block; tree: the four query heads
+// of a group, 2 heads x 64 node slots per tile) and the K/V tiles they may see.  CTAs are
+// persistent, one per SM, and run their items back to back.  A "virtual step" is (K/V tile j,
+// query tile t); S of consecutive virtual steps alternates between two TMEM buffers, so the score
+// MMAs of the next virtual step run while the softmax of the current one is still working.
+// Roles (384 threads):
+//   warp 0      TMA producer: Q once per item, then K_j / V_j into shared-memory rings
+//               (128-byte swizzle; a paged prefix tile is 8 pages = 32 boxes issued by the warp)
+//   warp 1      one thread issues the score MMAs S_b = Q_t K_j^T (operands in shared memory)
+//   warps 2, 3  one thread each issues half of the output MMAs O_t += P_b V_j: warp 2 the fp16
+//               "hi" part of P, warp 3 the "lo" part (P from TMEM, V from shared memory,
+//               MN-major).  A single thread cannot issue 128x128x16 instructions fast enough to
+//               keep the tensor pipe busy; three can.
+//   warps 4-11  softmax: both warpgroups work on the same 128 rows, the first on key columns
+//               0-63 of the tile, the second on 64-127; row maxima and sums are exchanged through
+//               shared memory.  thread = query row; S is read with tcgen05.ld, P is written back
+//               over S as fp16 hi + lo (P keeps ~22 bits, as the fp32 reference does); the
+//               running maximum is only raised when it grows by more than 2^8 (lazy rescale of O)
+// TMEM (512 columns): S[0] | S[1] | O[0] | O[1], 128 fp32 columns each.
+#include <cstdio>
+#include <cstring>
+
+#include "compute_internal.h"
+#include "ptx.cuh"
+
+namespace gb200 {
+
+// Development aid: built with -DGB_FA_TRACE one CTA records clock64() at the hand-over points of
+// its roles (slot = role * 256 + virtual step * 4 + event) and the launcher prints the timeline.
+#ifdef GB_FA_TRACE
+#define FA_TRACE(role, step, ev) \
+    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (step) < 64) p.trace[(role) * 256 + (step) * 4 + (ev)] = clock64(); } while (0)
+#else
+#define FA_TRACE(role, step, ev) do {} while (0)
+#endif
+
+constexpr int kTcThreads = 384;
+constexpr int kT = 128;                      // query rows per tile, keys per K/V tile, head_dim
+constexpr int kTileBytes = kT * kT * 2;      // 32 KB: one [128 x 128] fp16 tile
+constexpr int kChunkBytes = kTileBytes / 2;  // 16 KB: one 64-column (128-byte) swizzle block
+constexpr int kNodeSlots = 64;               // tree nodes per sequence the kernel is laid out for
+constexpr int kPageRows = 16;
+constexpr float kLazyLog2 = 8.0f;
+constexpr int kMaxStages = 3;
+constexpr uint32_t kNegInf = 0xFF800000u;
+
+struct TcParams {
+    int num_heads, num_kv_heads, group;
+    int units_per_kvh;   // items per KV head (prefill: per query block; tree: per sequence)
+    float scale_log2;
+    int* status;
+    // prefill
+    void* out;           // [seq_q, Hq, 128] fp16 or fp32
+    int out_fp16;
+    int seq_q, seq_kv, max_seq, n_qblocks, start_pos;
+    // tree
+    float* tree_out;            // [batch, Hq, N, 128] fp32
+    const int32_t* parents;     // [batch, N]
+    const int32_t* tables;      // [batch, max_blocks] (paged) or nullptr
+    const int32_t* cache_lens;  // [batch] or nullptr
+    int batch, num_nodes, cache_len, cache_stride, max_blocks, num_blocks;
+    unsigned long long* trace;  // timeline hook, only used in GB_FA_TRACE builds
+};
+
+struct TcSmem {
+    uint64_t q_full, q_empty, k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages];
+    uint64_t s_full[2], s_free[2], p_ready[2], o_final;
+    uint32_t tmem_base;
+    int abort_flag;
+    float xchg[2][2][kT];  // [virtual-step parity][warpgroup][row]: row maxima / sums between the warpgroups
+};
+static_assert(sizeof(TcSmem) <= 3072, "barriers and exchange slots must fit beside seven 32 KB tiles");
+
+struct TcItem {
+    int head0;      // first query head of the item
+    int kvh;
+    int b;          // tree: sequence
+    int q0;         // prefill: first query row
+    int rows_here;  // prefill: live rows of the query block
+    int n_steps;    // K/V tiles to walk (tree: prefix tiles + 1)
+    int n_prefix;   // tree: prefix tiles
+    int cache_len;  // tree: prefix length
+    bool valid;
+};
+
+// fp32 -> fp16 hi + fp16 lo (x ~= hi + lo to about 22 bits), so fp32 queries lose nothing.
+__global__ void split_f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ hi,
+                                        __half* __restrict__ lo, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float x = src[i];
+        const __half h = __float2half_rn(x);
+        hi[i] = h;
+        lo[i] = __float2half_rn(x - __half2float(h));
+    }
+}
+
+// Ancestor word of one node: bit j set when the node may attend to tree node j (itself or an
+// ancestor).  Follows src/llm/transformer.mm:829-839; the walk is cut after n hops, which changes
+// nothing for an acyclic parent array.  Parents outside [-1, n) end the walk (and are reported).
+__device__ __forceinline__ unsigned long long ancestor_word(const int* parents, int node, int n) {
+    unsigned long long w = 1ull << node;
+    int cur = parents[node];
+    for (int hops = 0; cur >= 0 && cur < n && hops < n; hops++) {
+        w |= 1ull << cur;
+        cur = parents[cur];
+    }
+    return w;
+}
+
+// masks[b * n + i] = ancestor word of node i of sequence b.
+__global__ void tree_mask_kernel(const int32_t* parents, unsigned long long* masks, int batch, int n, int* status) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= batch * n) return;
+    const int b = idx / n, i = idx % n;
+    const int32_t* p = parents + (size_t)b * n;
+    if (p[i] < -1 || p[i] >= n) atomicOr(status, kStatusBadParent);
+    masks[idx] = ancestor_word(p, i, n);
+}
+
+__device__ __forceinline__ void softmax_group_sync() {
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the two softmax warpgroups only
+}
+
+// kTree:   tree verification (else causal prefill).   kPaged: tree prefix in the paged pool.
+// kSplitQ: queries given as fp16 hi + lo arrays (fp32 queries): S = Q_hi K^T + Q_lo K^T; one tile only.
+// kTiles:  query tiles per item (1 or 2).
+template <bool kTree, bool kPaged, bool kSplitQ, int kTiles>
+__global__ void __launch_bounds__(kTcThreads, 1)
+fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap qlomap,
+             const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+             const __grid_constant__ CUtensorMap ktmap, const __grid_constant__ CUtensorMap vtmap, TcParams p) {
+    static_assert(!(kSplitQ && kTiles == 2), "split queries take both query slots");
+    constexpr int kQSlots = kSplitQ ? 2 : kTiles;
+    constexpr int kStages = kQSlots == 1 ? 3 : 2;
+    // barriers and exchange slots first, then the 1024-byte aligned tiles (128-byte swizzle atoms)
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    TcSmem* sh = reinterpret_cast<TcSmem*>(smem_raw);
+    uint8_t* q_smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + sizeof(TcSmem) + 1023) & ~uintptr_t(1023));
+    uint8_t* k_smem = q_smem + kQSlots * kTileBytes;
+    uint8_t* v_smem = k_smem + kStages * kTileBytes;
+    volatile int* abort_flag = &sh->abort_flag;
+    {
+        uint32_t dyn_size;
+        asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+        if (v_smem + kStages * kTileBytes > smem_raw + dyn_size) {  // cannot happen with a 1 KB aligned window
+            if (threadIdx.x == 0) atomicOr(p.status, kStatusLayout);
+            return;
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int N = p.num_nodes;
+#ifdef GB_FA_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        p.trace[3 * 256 + 0] = gt;
+        p.trace[3 * 256 + 1] = clock64();
+    }
+#endif
+
+    // ---- work items.  Prefill: ordered heaviest query block first and dealt to the CTAs in a snake
+    // (round r left to right when even, right to left when odd), which keeps the summed causal work
+    // per CTA within about one K/V step of the mean.  Tree: equal items, same dealing.
+    const int n_items = kTree ? p.batch * p.num_kv_heads * p.units_per_kvh
+                              : p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
+    const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto item_of = [&](int r) {
+        TcItem it;
+        const int pos = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        it.valid = pos < n_items;
+        int pp = it.valid ? pos : 0;
+        const int unit = pp % p.units_per_kvh;
+        pp /= p.units_per_kvh;
+        it.kvh = pp % p.num_kv_heads;
+        pp /= p.num_kv_heads;
+        if (kTree) {
+            it.b = pp;
+            it.head0 = it.kvh * p.group + unit * 2 * kTiles;  // two heads per tile
+            int len = p.cache_lens ? p.cache_lens[it.b] : p.cache_len;
+            const int cap = kPaged ? p.max_blocks * kPageRows : p.cache_stride;
+            if (len < 0 || len > cap) {
+                if (threadIdx.x == 0) atomicOr(p.status, kStatusBadSeqLen);
+                len = 0;
+            }
+            it.cache_len = len;
+            it.n_prefix = (len + kT - 1) / kT;
+            it.n_steps = it.n_prefix + 1;  // the last step is the tree tile
+            it.q0 = 0;
+            it.rows_here = kT;
+        } else {
+            it.b = 0;
+            it.head0 = it.kvh * p.group + unit * kTiles;  // one head per tile
+            it.q0 = (p.n_qblocks - 1 - pp) * kT;
+            it.rows_here = min(kT, p.seq_q - it.q0);
+            const int k_end = min(p.seq_kv, p.start_pos + it.q0 + it.rows_here);  // exclusive: last visible key + 1
+            it.n_steps = (k_end + kT - 1) / kT;
+            it.n_prefix = it.n_steps;
+            it.cache_len = 0;
+        }
+        return it;
+    };
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sh->q_full, 1);
+        mbar_init(&sh->q_empty, 1);
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(&sh->k_full[i], 1);
+            mbar_init(&sh->k_empty[i], 1);
+            mbar_init(&sh->v_full[i], 1);
+            mbar_init(&sh->v_empty[i], 2);  // both output-MMA issuers commit
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&sh->s_full[i], 1);
+            mbar_init(&sh->s_free[i], 2);
+            mbar_init(&sh->p_ready[i], 256);
+        }
+        mbar_init(&sh->o_final, 2);
+        sh->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&sh->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp < 4) {
+        setmaxnreg_dec<56>();  // producer / MMA warpgroup gives registers up
+        if (warp == 0) {
+            // -------------------------------------------------------------- TMA producer (whole warp)
+            if (lane == 0) {
+                tma_prefetch_desc(&qmap);
+                tma_prefetch_desc(&kmap);
+                tma_prefetch_desc(&vmap);
+                if (kTree) {
+                    tma_prefetch_desc(&ktmap);
+                    tma_prefetch_desc(&vtmap);
+                }
+            }
+            int st = 0, items_done = 0;
+            uint32_t ph = 1;  // a fresh barrier passes a wait on parity 1
+            int alive = 1;
+            for (int r = 0; r < n_rounds && alive; r++) {
+                const TcItem it = item_of(r);
+                if (!it.valid) continue;
+                if (lane == 0) {
+                    // the query tiles are replaced once the last score MMA of the previous item is done
+                    alive = mbar_wait(&sh->q_empty, (items_done & 1) ^ 1, abort_flag);
+                    if (alive) {
+                        mbar_arrive_expect_tx(&sh->q_full, kQSlots * kTileBytes);
+                        for (int c = 0; c < 2; c++) {
+                            if (kTree) {
+                                // Q [batch*Hq, N, 128]: a box is 64 halfs x 64 nodes x 2 heads (16 KB)
+                                const int z0 = it.b * p.num_heads + it.head0;
+                                for (int t = 0; t < kTiles; t++)
+                                    tma_load_3d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full, c * 64, 0, z0 + 2 * t);
+                                if (kSplitQ)
+                                    tma_load_3d(q_smem + kTileBytes + c * kChunkBytes, &qlomap, &sh->q_full, c * 64, 0, z0);
+                            } else {
+                                for (int t = 0; t < kTiles; t++)
+                                    tma_load_2d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full,
+                                                (it.head0 + t) * kT + c * 64, it.q0);
+                                if (kSplitQ)
+                                    tma_load_2d(q_smem + kTileBytes + c * kChunkBytes, &qlomap, &sh->q_full,
+                                                it.head0 * kT + c * 64, it.q0);
+                            }
+                        }
+                    }
+                }
+                alive = __shfl_sync(0xffffffffu, alive, 0);
+                if (!alive) break;
+                items_done++;
+                // page entries of the next prefix tile are fetched one tile ahead (lanes 0-7, one page each)
+                auto load_entry = [&](int j) {
+                    int e = 0;
+                    if (kTree && kPaged && j < it.n_prefix && lane < 8) {
+                        const int logical = j * 8 + lane;
+                        if (logical * kPageRows < it.cache_len) {
+                            e = p.tables[(size_t)it.b * p.max_blocks + logical];
+                            if (e < 0 || e >= p.num_blocks) {
+                                atomicOr(p.status, kStatusBadTable);
+                                e = 0;
+                            }
+                        }
+                    }
+                    return e;
+                };
+                int entry_next = load_entry(0);
+                for (int j = 0; j < it.n_steps; j++) {
+                    const bool tree_step = kTree && j == it.n_prefix;
+                    const int entry = entry_next;
+                    entry_next = load_entry(j + 1);
+                    const uint32_t bytes = tree_step ? kTileBytes / 2 : kTileBytes;
+                    uint8_t* kd = k_smem + st * kTileBytes;
+                    uint8_t* vd = v_smem + st * kTileBytes;
+                    const int c = lane & 1;
+                    // K first: its slot is released as soon as the score MMAs that read it are done,
+                    // a whole softmax earlier than the V slot, so K runs further ahead
+#pragma unroll
+                    for (int is_v = 0; is_v < 2; is_v++) {
+                        uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
+                        if (lane == 0) {
+                            alive = mbar_wait(is_v ? &sh->v_empty[st] : &sh->k_empty[st], ph, abort_flag);
+                            if (alive) mbar_arrive_expect_tx(full, bytes);
+                        }
+                        alive = __shfl_sync(0xffffffffu, alive, 0);
+                        if (!alive) break;
+                        uint8_t* dst = is_v ? vd : kd;
+                        if (tree_step) {
+                            // tree K/V [batch*Hkv, N, 128]: 64-row boxes; rows >= N are zero-filled by TMA
+                            if (lane < 2)
+                                tma_load_3d(dst + c * kChunkBytes, is_v ? &vtmap : &ktmap, full, c * 64, 0,
+                                            it.b * p.num_kv_heads + it.kvh);
+                        } else if (kTree && kPaged) {
+                            // lane = (page, chunk): 8 pages x 2 chunks
+                            const int pg = (lane >> 1) & 7;
+                            const int e = __shfl_sync(0xffffffffu, entry, pg);
+                            if (lane < 16)
+                                tma_load_2d(dst + c * kChunkBytes + pg * 2048, is_v ? &vmap : &kmap, full,
+                                            it.kvh * kT + c * 64, e * kPageRows);
+                        } else if (lane < 2) {
+                            // contiguous cache [.., max rows, 128]: one 128-row box per chunk
+                            const int y = kTree ? (it.b * p.num_kv_heads + it.kvh) * p.cache_stride + j * kT
+                                                : it.kvh * p.max_seq + j * kT;
+                            tma_load_2d(dst + c * kChunkBytes, is_v ? &vmap : &kmap, full, c * 64, y);
+                        }
+                    }
+                    if (!alive) break;
+                    if (++st == kStages) {
+                        st = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!alive && lane == 0) atomicOr(p.status, kStatusTimeout);
+        } else if (warp == 1) {
+            // -------------------------------------------------------------- score MMAs: S_b = Q_t K_j^T
+            if (lane == 0) {
+                constexpr uint32_t idesc_qk = umma_idesc_f16(kT, kT, false, false);
+                constexpr uint32_t idesc_qk_tree = umma_idesc_f16(kT, kNodeSlots, false, false);
+                const uint32_t q_lo0 = desc_lo(smem_u32(q_smem), 16);
+                const uint32_t k_lo0 = desc_lo(smem_u32(k_smem), 16);
+                bool ok = true;
+                int st = 0, items_done = 0;
+                int vs = 0;  // virtual steps issued so far across items: S buffer = vs & 1
+                uint32_t ph = 0;
+                for (int r = 0; r < n_rounds && ok; r++) {
+                    const TcItem it = item_of(r);
+                    if (!it.valid) continue;
+                    ok = mbar_wait(&sh->q_full, items_done & 1, abort_flag);
+                    items_done++;
+                    for (int j = 0; j < it.n_steps && ok; j++) {
+                        FA_TRACE(0, vs, 3);
+                        ok = mbar_wait(&sh->k_full[st], ph, abort_flag);
+                        const uint32_t idesc = (kTree && j == it.n_prefix) ? idesc_qk_tree : idesc_qk;  // 64 keys in the tree tile
+                        const uint32_t k_lo = k_lo0 + st * (kTileBytes >> 4);
+#pragma unroll
+                        for (int t = 0; t < kTiles; t++, vs++) {
+                            const int b = vs & 1;
+                            FA_TRACE(0, vs, 0);
+                            // S_b still holds P of virtual step vs-2 until both output-MMA halves of it are done
+                            if (ok && vs >= 2) ok = mbar_wait(&sh->s_free[b], ((vs >> 1) - 1) & 1, abort_flag);
+                            if (!ok) break;
+                            FA_TRACE(0, vs, 1);
+                            tc_fence_after_sync();
+                            const uint32_t d = tmem + b * kT;
+                            const uint32_t q_lo = q_lo0 + t * (kTileBytes >> 4);
+                            // K-major operands: 8 steps of 16 along head_dim (32 bytes inside the swizzled
+                            // row, the second 64-wide block 16 KB further)
+#pragma unroll
+                            for (int ks = 0; ks < 8; ks++) {
+                                const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                                umma_ss_words(d, q_lo + off, k_lo + off, kDescHiSw128, idesc, ks > 0 ? 1u : 0u);
+                            }
+                            if (kSplitQ) {
+#pragma unroll
+                                for (int ks = 0; ks < 8; ks++) {
+                                    const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                                    umma_ss_words(d, q_lo0 + (kTileBytes >> 4) + off, k_lo + off, kDescHiSw128, idesc, 1u);
+                                }
+                            }
+                            tc_commit(&sh->s_full[b]);
+                            FA_TRACE(0, vs, 2);
+                        }
+                        if (!ok) break;
+                        tc_commit(&sh->k_empty[st]);
+                        if (j + 1 == it.n_steps) tc_commit(&sh->q_empty);  // the query tiles may be replaced
+                        if (++st == kStages) {
+                            st = 0;
+                            ph ^= 1;
+                        }
+                    }
+                }
+                if (!ok) atomicOr(p.status, kStatusTimeout);
+            }
+        } else {
+            // -------------------------------------------------------------- output MMAs: O_t += P_b V_j
+            // warp 2 multiplies the hi half of P, warp 3 the lo half; O was zeroed by the softmax
+            // warps, so every MMA accumulates and the two issuers need no order between them
+            if (lane == 0) {
+                constexpr uint32_t idesc_pv = umma_idesc_f16(kT, kT, false, true);
+                const uint32_t part = warp - 2;  // 0: hi, 1: lo
+                const uint32_t v_lo0 = desc_lo(smem_u32(v_smem), kChunkBytes);
+                bool ok = true;
+                int st = 0, vs = 0;
+                uint32_t ph = 0;
+                for (int r = 0; r < n_rounds && ok; r++) {
+                    const TcItem it = item_of(r);
+                    if (!it.valid) continue;
+                    for (int j = 0; j < it.n_steps && ok; j++) {
+                        if (part == 0) FA_TRACE(1, vs, 3);
+                        ok = mbar_wait(&sh->v_full[st], ph, abort_flag);
+                        const uint32_t v_lo = v_lo0 + st * (kTileBytes >> 4);
+                        const int nks = (kTree && j == it.n_prefix) ? 4 : 8;  // 16 keys per step; the tree tile has 64
+#pragma unroll
+                        for (int t = 0; t < kTiles; t++, vs++) {
+                            const int b = vs & 1;
+                            if (part == 0) FA_TRACE(1, vs, 0);
+                            if (ok) ok = mbar_wait(&sh->p_ready[b], (vs >> 1) & 1, abort_flag);
+                            if (!ok) break;
+                            if (part == 0) FA_TRACE(1, vs, 1);
+                            tc_fence_after_sync();
+                            const uint32_t d = tmem + 2 * kT + t * kT;
+                            // P: each 64-column half of S_b became 32 columns of hi + 32 of lo (8 columns per
+                            // 16 keys); V MN-major: 16 keys = 2 KB further per step, second 64 dims via LBO
+#pragma unroll
+                            for (int ks = 0; ks < 8; ks++) {
+                                if (ks < nks) {
+                                    const uint32_t a = tmem + b * kT + (ks >> 2) * 64 + (ks & 3) * 8 + part * 32;
+                                    umma_ts_words(d, a, v_lo + ks * (2048 >> 4), kDescHiSw128, idesc_pv, 1u);
+                                }
+                            }
+                            tc_commit(&sh->s_free[b]);
+                            if (part == 0) FA_TRACE(1, vs, 2);
+                        }
+                        if (!ok) break;
+                        tc_commit(&sh->v_empty[st]);
+                        if (j + 1 == it.n_steps) tc_commit(&sh->o_final);
+                        if (++st == kStages) {
+                            st = 0;
+                            ph ^= 1;
+                        }
+                    }
+                }
+                if (!ok) atomicOr(p.status, kStatusTimeout);
+            }
+        }
+    } else {
+        setmaxnreg_inc<224>();
+        // ------------------------------------------------------------------ softmax + epilogue
+        // Both warpgroups work on every virtual step, the first on key columns 0-63, the second on
+        // 64-127; row maxima and sums go through shared memory.  (Giving each warpgroup a whole tile
+        // of its own - 128 columns per thread, no exchange - measured 35 % slower.)
+        constexpr bool kColSplit = true;
+        constexpr int kChunks = 2;   // 32-column chunks of S per thread
+        const int wg = (warp - 4) >> 2;
+        const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+        const int row = quarter * 32 + lane;     // query row inside the tile
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int col0 = kColSplit ? wg * 64 : 0;  // first S / O column of this thread
+        const int node = row & (kNodeSlots - 1); // tree: node slot of this row
+        bool ok = true;
+        int vs = 0, kvs = 0, items_done = 0;     // virtual steps, K/V steps, items handled so far
+        for (int r = 0; r < n_rounds; r++) {
+            const TcItem it = item_of(r);
+            if (!it.valid) continue;
+            // prefill: the last key this row may see; tree: the row's ancestor word
+            const int q_pos = it.q0 + row;
+            const int last_visible = kTree ? it.cache_len - 1 : min(p.start_pos + q_pos, p.seq_kv - 1);
+            unsigned long long anc = 1ull;
+            if (kTree && node < N) {
+                const int32_t* par = p.parents + (size_t)it.b * N;
+                if (par[node] < -1 || par[node] >= N) atomicOr(p.status, kStatusBadParent);
+                anc = ancestor_word(par, node, N);
+            }
+            float m_used_t[kTiles], l_run_t[kTiles];  // running maximum and sum of this row, per query tile
+            {
+                // O starts at zero so that every output MMA can accumulate
+                uint32_t z[32];
+#pragma unroll
+                for (int c = 0; c < 32; c++) z[c] = 0u;
+#pragma unroll
+                for (int t = 0; t < kTiles; t++) {
+                    m_used_t[t] = -INFINITY;
+                    l_run_t[t] = 0.f;
+#pragma unroll
+                    for (int ch = 0; ch < kChunks; ch++) tmem_st32(lane_base + 2 * kT + t * kT + col0 + ch * 32, z);
+                }
+                tmem_wait_st();
+            }
+            for (int j = 0; j < it.n_steps; j++, kvs++) {
+                const bool tree_step = kTree && j == it.n_prefix;
+                const int k0 = j * kT;
+                // prefill: the diagonal tile and a ragged last tile; tree prefix: a ragged last tile
+                const bool need_mask = kTree ? (!tree_step && k0 + kT > it.cache_len)
+                                             : ((k0 + kT - 1 > p.start_pos + it.q0) || (k0 + kT > p.seq_kv));
+                const int limit = last_visible - k0 - col0;                    // own column c is visible iff c <= limit
+                const bool has_cols = !(tree_step && kColSplit && wg == 1);   // the tree tile has 64 key columns only
+#pragma unroll
+                for (int t = 0; t < kTiles; t++, vs++) {
+                    float& m_used = m_used_t[t];
+                    float& l_run = l_run_t[t];
+                    const int b = vs & 1;
+                    const uint32_t s_addr = lane_base + b * kT + col0;
+                    const uint32_t o_addr = lane_base + 2 * kT + t * kT + col0;
+                    if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
+                    if (!ok) {  // keep the barrier count intact so nobody is left waiting
+                        if (kColSplit) softmax_group_sync();
+                        continue;
+                    }
+                    tc_fence_after_sync();
+                    // this thread's scores into registers: all loads in flight, one wait
+                    uint32_t x[kChunks][32];
+                    if (has_cols) {
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ch++)
+                            if (!(tree_step && ch >= 2)) tmem_ld32(s_addr + ch * 32, x[ch]);
+                        tmem_wait_ld();
+                    }
+                    if (tree_step) {
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ch++)
+#pragma unroll
+                            for (int c = 0; c < 32; c++)
+                                if (!has_cols || ch >= 2 || !((anc >> (ch * 32 + c)) & 1ull)) x[ch][c] = kNegInf;
+                    } else if (need_mask) {
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ch++)
+#pragma unroll
+                            for (int c = 0; c < 32; c++)
+                                if (ch * 32 + c > limit) x[ch][c] = kNegInf;
+                    }
+                    float mx;
+                    {
+                        float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ch++)
+#pragma unroll
+                            for (int c = 0; c < 32; c += 2) {
+                                const int k = (kChunks == 4) ? ch : ch * 2 + ((c >> 1) & 1);
+                                mm[k] = fmaxf(mm[k], fmaxf(__uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1])));
+                            }
+                        mx = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+                    }
+                    if (kColSplit) {
+                        // the other warpgroup holds the other 64 columns of the same row
+                        sh->xchg[b][wg][row] = mx;
+                        softmax_group_sync();
+                        mx = fmaxf(mx, sh->xchg[b][wg ^ 1][row]);
+                    }
+                    mx *= p.scale_log2;
+                    if (j == 0) {
+                        m_used = mx;
+                    } else {
+                        const bool grow = mx > m_used + kLazyLog2;
+                        if (__any_sync(0xffffffffu, grow)) {
+                            // O_t must be quiescent: wait until both halves of its previous output MMA are done
+                            ok = mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag);
+                            tc_fence_after_sync();
+                            const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
+                            if (grow) m_used = mx;
+                            l_run *= alpha;
+                            uint32_t rr[32];
+#pragma unroll 1
+                            for (int ch = 0; ch < kChunks; ch++) {
+                                tmem_ld32(o_addr + ch * 32, rr);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 32; c++) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * alpha);
+                                tmem_st32(o_addr + ch * 32, rr);
+                            }
+                        }
+                    }
+                    if (has_cols) {
+                        // P = 2^(s*scale - m): each 64-column half of S becomes 32 columns of fp16 hi
+                        // followed by 32 columns of lo
+                        float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial sums
+                        const float neg_m = -m_used;
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ch++) {
+                            if (tree_step && ch >= 2) continue;
+                            uint32_t hi[16], lo[16];
+#pragma unroll
+                            for (int c = 0; c < 32; c += 2) {
+                                // masked scores are -inf: exp2 gives exactly 0
+                                const float p0 = fast_exp2(fmaf(__uint_as_float(x[ch][c]), p.scale_log2, neg_m));
+                                const float p1 = fast_exp2(fmaf(__uint_as_float(x[ch][c + 1]), p.scale_log2, neg_m));
+                                ls[c & 6] += p0;
+                                ls[(c & 6) + 1] += p1;
+                                split_hi_lo(p0, p1, hi[c >> 1], lo[c >> 1]);
+                            }
+                            tmem_st16(s_addr + (ch >> 1) * 64 + (ch & 1) * 16, hi);
+                            tmem_st16(s_addr + (ch >> 1) * 64 + 32 + (ch & 1) * 16, lo);
+                        }
+                        l_run += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
+                    }
+                    if (t == 0 && wg == 0 && need_mask && k0 + kT > (kTree ? it.cache_len : p.seq_kv)) {
+                        // keys past the live length carry P = 0, but their V rows may hold anything (even
+                        // NaN): zero them in shared memory before the MMAs read the tile
+                        const int st = kvs % kStages;
+                        ok = mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag);
+                        const int first_bad = (kTree ? it.cache_len : p.seq_kv) - k0;
+                        uint8_t* vt = v_smem + st * kTileBytes;
+                        for (int i = row; i < (kT - first_bad) * 16; i += 128) {
+                            const int vr = first_bad + (i >> 4), u = i & 15;
+                            *reinterpret_cast<uint4*>(vt + (u >> 3) * kChunkBytes + vr * 128 + (((u & 7) ^ (vr & 7)) << 4)) =
+                                make_uint4(0, 0, 0, 0);
+                        }
+                        fence_proxy_async_smem();
+                    }
+                    __syncwarp();
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&sh->p_ready[b]);
+                }
+            }
+            // row sums of the two column halves
+            float l_total_t[kTiles];
+            softmax_group_sync();  // every thread is done with the exchange slots of the last steps
+#pragma unroll
+            for (int t = 0; t < kTiles; t++) sh->xchg[t][wg][row] = l_run_t[t];
+            softmax_group_sync();
+#pragma unroll
+            for (int t = 0; t < kTiles; t++) l_total_t[t] = l_run_t[t] + sh->xchg[t][wg ^ 1][row];
+            softmax_group_sync();  // the slots are reused by the next item's first steps
+            if (ok) ok = mbar_wait(&sh->o_final, items_done & 1, abort_flag);
+            items_done++;
+            if (ok) {
+                tc_fence_after_sync();
+#pragma unroll
+                for (int t = 0; t < kTiles; t++) {
+                const float inv = 1.0f / l_total_t[t];
+                const uint32_t o_addr = lane_base + 2 * kT + t * kT + col0;
+                bool store;
+                size_t base;  // element offset of this thread's first output value
+                if (kTree) {
+                    const int head = it.head0 + 2 * t + (row >> 6);
+                    store = node < N && head < (it.kvh + 1) * p.group;
+                    base = (((size_t)it.b * p.num_heads + head) * N + node) * kT + col0;
+                } else {
+                    store = row < it.rows_here;
+                    base = ((size_t)q_pos * p.num_heads + it.head0 + t) * kT + col0;
+                }
+                uint32_t rr[32];
+#pragma unroll 1
+                for (int ch = 0; ch < kChunks; ch++) {
+                    __syncwarp();
+                    tmem_ld32(o_addr + ch * 32, rr);
+                    tmem_wait_ld();
+                    if (store) {
+                        if (!kTree && p.out_fp16) {
+                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + base + ch * 32);
+#pragma unroll
+                            for (int v = 0; v < 4; v++) {
+                                uint4 o;
+                                o.x = pack_half2(__uint_as_float(rr[v * 8 + 0]) * inv, __uint_as_float(rr[v * 8 + 1]) * inv);
+                                o.y = pack_half2(__uint_as_float(rr[v * 8 + 2]) * inv, __uint_as_float(rr[v * 8 + 3]) * inv);
+                                o.z = pack_half2(__uint_as_float(rr[v * 8 + 4]) * inv, __uint_as_float(rr[v * 8 + 5]) * inv);
+                                o.w = pack_half2(__uint_as_float(rr[v * 8 + 6]) * inv, __uint_as_float(rr[v * 8 + 7]) * inv);
+                                dst[v] = o;
+                            }
+                        } else {
+                            float* outp = kTree ? p.tree_out : static_cast<float*>(p.out);
+                            float4* dst = reinterpret_cast<float4*>(outp + base + ch * 32);
+#pragma unroll
+                            for (int v = 0; v < 8; v++)
+                                dst[v] = make_float4(__uint_as_float(rr[v * 4 + 0]) * inv, __uint_as_float(rr[v * 4 + 1]) * inv,
+                                                     __uint_as_float(rr[v * 4 + 2]) * inv, __uint_as_float(rr[v * 4 + 3]) * inv);
+                        }
+                    }
+                }
+                }  // tiles
+            } else if (lane == 0) {
+                atomicOr(p.status, kStatusTimeout);
+            }
+        }  // items
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+#ifdef GB_FA_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        p.trace[3 * 256 + 2] = gt;
+        p.trace[3 * 256 + 3] = clock64();
+    }
+#endif
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------ host
+typedef void (*TcKernel)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, TcParams);
+
+static int launch_tc(granite_cuda_compute* c, TcKernel kern, const char* name, int n_items, int q_slots,
+                     const CUtensorMap* qmap, const CUtensorMap* qlomap, const CUtensorMap* kmap,
+                     const CUtensorMap* vmap, const CUtensorMap* ktmap, const CUtensorMap* vtmap, const TcParams& p) {
+    // Q slots + K and V rings: 3 stages fit beside one query slot, 2 beside two
+    const int stages = q_slots == 1 ? 3 : 2;
+    size_t smem_bytes = (sizeof(TcSmem) + 1023) / 1024 * 1024 + 1024 + (size_t)(q_slots + 2 * stages) * kTileBytes;
+    if (smem_bytes > (size_t)c->smem_optin) smem_bytes = (size_t)c->smem_optin;  // the window is 1 KB aligned in practice
+    GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    const int grid = n_items < c->sm_count ? n_items : c->sm_count;  // persistent CTAs, one per SM
+#ifdef GB_FA_TRACE
+    static unsigned long long* trace_buf = nullptr;
+    if (!trace_buf) cudaMalloc(&trace_buf, 4 * 256 * sizeof(unsigned long long));
+    cudaMemsetAsync(trace_buf, 0, 4 * 256 * sizeof(unsigned long long), c->stream);
+    TcParams pt = p;
+    pt.trace = trace_buf;
+    {
+        LaunchScope t(c, name);
+        kern<<<grid, kTcThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, *ktmap, *vtmap, pt);
+    }
+    static unsigned long long host_trace[4 * 256];
+    cudaMemcpyAsync(host_trace, trace_buf, sizeof(host_trace), cudaMemcpyDeviceToHost, c->stream);
+    cudaStreamSynchronize(c->stream);
+    {
+        fprintf(stderr, "trace cta0: %lld ns, %lld cycles -> %.3f GHz\n", (long long)(host_trace[768 + 2] - host_trace[768 + 0]),
+                (long long)(host_trace[768 + 3] - host_trace[768 + 1]),
+                (double)(host_trace[768 + 3] - host_trace[768 + 1]) / (double)(host_trace[768 + 2] - host_trace[768 + 0]));
+        const unsigned long long t0 = host_trace[2 * 256 + 1];
+        const char* roles[3] = {"qk ", "pvh", "smx"};
+        for (int step = 0; step < 64; step++)
+            for (int r = 0; r < 3; r++)
+                fprintf(stderr, "trace %s vstep %2d: %8lld %8lld %8lld %8lld\n", roles[r], step,
+                        (long long)(host_trace[r * 256 + step * 4 + 0] - t0), (long long)(host_trace[r * 256 + step * 4 + 1] - t0),
+                        (long long)(host_trace[r * 256 + step * 4 + 2] - t0), (long long)(host_trace[r * 256 + step * 4 + 3] - t0));
+    }
+#else
+    {
+        LaunchScope t(c, name);
+        kern<<<grid, kTcThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, *ktmap, *vtmap, p);
+    }
+#endif
+    GB_CUDA_TRY(cudaGetLastError());
+    return GRANITE_CUDA_SUCCESS;
+}
+
+// fp32 queries -> hi / lo fp16 arrays in the scratch arena
+static int split_queries(granite_cuda_compute* c, const void* q, size_t n, const void** hi_out, const void** lo_out) {
+    const size_t half_bytes = (n * 2 + 255) / 256 * 256;
+    int rc = c->ensure_scratch(2 * half_bytes);
+    if (rc) return rc;
+    LaunchScope t(c, "split_q_f16");
+    __half* hi = static_cast<__half*>(c->scratch);
+    __half* lo = reinterpret_cast<__half*>(static_cast<uint8_t*>(c->scratch) + half_bytes);
+    split_f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(static_cast<const float*>(q), hi, lo, n);
+    *hi_out = hi;
+    *lo_out = lo;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
+    if (!a.q || !a.k || !a.v || !a.output) return fail(GRANITE_CUDA_NULL_POINTER, "prefill: null buffer");
+    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: head_dim must be 128");
+    if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: num_heads must be a multiple of num_kv_heads");
+    if (a.q_dtype > 1 || a.out_dtype > 1) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: dtype must be 0 (fp32) or 1 (fp16)");
+    const uint32_t max_seq = a.max_seq ? a.max_seq : a.seq_kv;
+    if (a.seq_kv == 0 || a.seq_kv > max_seq) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: seq_kv must be in [1, max_seq]");
+
+    const bool split_q = a.q_dtype == 0;
+    const void *q16 = a.q, *q16_lo = a.q;
+    if (split_q) {
+        int rc = split_queries(c, a.q, (size_t)a.seq_q * a.num_heads * kT, &q16, &q16_lo);
+        if (rc) return rc;
+    }
+    TcParams p{};
+    p.num_heads = (int)a.num_heads;
+    p.num_kv_heads = (int)a.num_kv_heads;
+    p.group = (int)(a.num_heads / a.num_kv_heads);
+    const int tiles = 1;  // one query head per item: measured faster than a GQA pair sharing K/V tiles
+    p.units_per_kvh = p.group / tiles;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = c->d_status;
+    p.out = a.output;
+    p.out_fp16 = a.out_dtype == 1;
+    p.seq_q = (int)a.seq_q;
+    p.seq_kv = (int)a.seq_kv;
+    p.max_seq = (int)max_seq;
+    p.n_qblocks = (p.seq_q + kT - 1) / kT;
+    p.start_pos = (int)a.start_pos;
+
+    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const uint64_t kv_rows = (uint64_t)a.num_kv_heads * max_seq;
+    const CUtensorMap* kmap = c->tensor_map_2d(a.k, kT, kv_rows, kT * 2, 64, kT, 128);
+    const CUtensorMap* vmap = c->tensor_map_2d(a.v, kT, kv_rows, kT * 2, 64, kT, 128);
+    if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
+
+    TcKernel kern = split_q ? fa_tc_kernel<false, false, true, 1> : fa_tc_kernel<false, false, false, 1>;
+    const int n_items = p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
+    return launch_tc(c, kern, "prefill_causal_fa", n_items, split_q ? 2 : tiles, qmap, qlomap, kmap, vmap, kmap, vmap, p);
+}
+
+int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* masks, uint32_t batch, uint32_t n) {
+    if (!parents || !masks) return fail(GRANITE_CUDA_NULL_POINTER, "tree mask: null buffer");
+    if (n == 0 || n > (uint32_t)kNodeSlots)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "tree mask: num_nodes must be in [1, 64]");
+    if (batch == 0) return GRANITE_CUDA_SUCCESS;
+    LaunchScope t(c, "tree_mask");
+    const uint32_t total = batch * n;
+    tree_mask_kernel<<<(total + 127) / 128, 128, 0, c->stream>>>(parents, reinterpret_cast<unsigned long long*>(masks),
+                                                                 (int)batch, (int)n, c->d_status);
+    GB_CUDA_TRY(cudaGetLastError());
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a) {
+    if (!a.q || !a.k_tree || !a.v_tree || !a.parent_indices || !a.output)
+        return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null buffer");
+    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: head_dim must be 128");
+    if (a.num_nodes == 0 || a.num_nodes > (uint32_t)kNodeSlots)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: num_nodes must be in [1, 64]");
+    if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: num_heads must be a multiple of num_kv_heads");
+    if (a.q_dtype > 1) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: q_dtype must be 0 (fp32) or 1 (fp16)");
+    if (a.batch_size == 0) return GRANITE_CUDA_SUCCESS;
+    const bool paged = a.block_tables != nullptr;
+    const bool has_cache = a.cache_lens != nullptr || a.cache_len > 0;
+    if (has_cache && (!a.k_cache || !a.v_cache)) return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null cache");
+    if (paged && (a.block_size != (uint32_t)kPageRows || a.num_blocks == 0 || a.max_blocks_per_seq == 0))
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: paged prefix needs block_size 16 and a non-empty pool");
+    const uint32_t cache_stride = a.cache_stride ? a.cache_stride : a.cache_len;
+    if (!paged && has_cache && a.cache_len > cache_stride)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: cache_len exceeds cache_stride");
+
+    const bool split_q = a.q_dtype == 0;
+    const void *q16 = a.q, *q16_lo = a.q;
+    if (split_q) {
+        int rc = split_queries(c, a.q, (size_t)a.batch_size * a.num_heads * a.num_nodes * kT, &q16, &q16_lo);
+        if (rc) return rc;
+    }
+    TcParams p{};
+    p.num_heads = (int)a.num_heads;
+    p.num_kv_heads = (int)a.num_kv_heads;
+    p.group = (int)(a.num_heads / a.num_kv_heads);
+    const int tiles = (!split_q && p.group % 4 == 0) ? 2 : 1;  // two heads per tile; two tiles share the K/V tiles
+    p.units_per_kvh = (p.group + 2 * tiles - 1) / (2 * tiles);
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = c->d_status;
+    p.tree_out = a.output;
+    p.parents = a.parent_indices;
+    p.tables = a.block_tables;
+    p.cache_lens = a.cache_lens;
+    p.batch = (int)a.batch_size;
+    p.num_nodes = (int)a.num_nodes;
+    p.cache_len = (int)a.cache_len;
+    p.cache_stride = (int)cache_stride;
+    p.max_blocks = (int)a.max_blocks_per_seq;
+    p.num_blocks = (int)a.num_blocks;
+
+    // Q / tree K / tree V as [heads, nodes, 128]: box = 64 halfs x 64 nodes x 2 heads (Q) or 1 head (K/V)
+    const uint64_t qz = (uint64_t)a.batch_size * a.num_heads;
+    const uint64_t node_pitch = (uint64_t)a.num_nodes * kT * 2;
+    const CUtensorMap* qmap = c->tensor_map_3d(q16, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, kNodeSlots, 2, 128);
+    const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, kNodeSlots, 2, 128);
+    const uint64_t tz = (uint64_t)a.batch_size * a.num_kv_heads;
+    const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);
+    const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);
+    const CUtensorMap *kmap = ktmap, *vmap = vtmap;  // placeholders when there is no prefix
+    if (has_cache) {
+        if (paged) {
+            const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * kT;
+            kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
+            vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
+        } else {
+            const uint64_t rows = (uint64_t)a.batch_size * a.num_kv_heads * cache_stride;
+            kmap = c->tensor_map_2d(a.k_cache, kT, rows, kT * 2, 64, kT, 128);
+            vmap = c->tensor_map_2d(a.v_cache, kT, rows, kT * 2, 64, kT, 128);
+        }
+    }
+    if (!qmap || !qlomap || !ktmap || !vtmap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
+
+    TcKernel kern;
+    if (split_q) kern = paged ? fa_tc_kernel<true, true, true, 1> : fa_tc_kernel<true, false, true, 1>;
+    else if (tiles == 2) kern = paged ? fa_tc_kernel<true, true, false, 2> : fa_tc_kernel<true, false, false, 2>;
+    else kern = paged ? fa_tc_kernel<true, true, false, 1> : fa_tc_kernel<true, false, false, 1>;
+    const int n_items = p.batch * p.num_kv_heads * p.units_per_kvh;
+    return launch_tc(c, kern, "tree_verify", n_items, split_q ? 2 : tiles, qmap, qlomap, kmap, vmap, ktmap, vtmap, p);
+}
+
+}  // namespace gb200
