@@ -200,7 +200,23 @@ def hold_queue(dev, ms: float = 8.0):
     torch.cuda._sleep(int(ms * 1.9e6))
 
 
-def measure_prefill(compute, dev, reps: int = 40):
+def region_ms_per_launch(dev, step, reps: int) -> float:
+    """Average duration of `reps` launches issued back to back behind a queue-holding kernel, one
+    CUDA event pair around the whole region on the launching stream (an event pair around every
+    single launch adds the front-end's gap between dependent operations to each of them)."""
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    hold_queue(dev)
+    e0.record()
+    for i in range(reps):
+        step(i)
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def measure_prefill(compute, dev, reps: int = 200):
     """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (BASELINE.json configs[1]); the
     kernel's own event-timed duration, rotating over 4 input sets."""
     import torch
@@ -229,18 +245,20 @@ def measure_prefill(compute, dev, reps: int = 40):
         step(i)
     st = compute.get_kernel_timing_stats()
     compute.enable_kernel_timing(False)
-    ms = st["prefill_causal_fa"][0] / st["prefill_causal_fa"][1]
+    ms_each = st["prefill_causal_fa"][0] / st["prefill_causal_fa"][1]
+    ms = region_ms_per_launch(dev, step, reps)
     flops = 4 * d * hq * seq * (seq + 1) // 2
     burst, sustained, kind = tensor_peak()
     tf = flops / ms / 1e9
-    return {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms, "launches": reps,
+    return {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms,
+            "kernel_ms_timed_singly": ms_each, "launches": reps,
             "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst,
             "frac": tf / burst, "frac_of_sustained": tf / sustained, "peak_kind": kind,
             "note": "unmasked half of the causal square counted only; P enters the PV product as fp16 hi+lo "
                     "(two MMAs) to keep the CPU path's precision, which the flop count does not credit"}
 
 
-def measure_tree(compute, dev, reps: int = 30):
+def measure_tree(compute, dev, reps: int = 200):
     """Tree verification: 16 sequences x (4096-token paged prefix + 64-node tree), Hq 32, Hkv 8
     (BASELINE.json configs[3]); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
     import torch
@@ -276,7 +294,8 @@ def measure_tree(compute, dev, reps: int = 30):
         step(i)
     st = compute.get_kernel_timing_stats()
     compute.enable_kernel_timing(False)
-    ms = st["tree_verify"][0] / st["tree_verify"][1]
+    ms_each = st["tree_verify"][0] / st["tree_verify"][1]
+    ms = region_ms_per_launch(dev, step, reps)
     visible = 0
     for b in range(batch):  # self + ancestors of every node
         for i in range(n):
@@ -291,7 +310,8 @@ def measure_tree(compute, dev, reps: int = 30):
     hbm, hkind = measured_peaks()
     tf = flops / ms / 1e9
     gbs = nbytes / ms / 1e6
-    return {"workload": "tree_verify_b16", "kernel": "tree_verify", "kernel_ms": ms, "launches": reps,
+    return {"workload": "tree_verify_b16", "kernel": "tree_verify", "kernel_ms": ms,
+            "kernel_ms_timed_singly": ms_each, "launches": reps,
             "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
             "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
             "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind}

@@ -166,11 +166,18 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.num_nodes;
 #ifdef GB_FA_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
         unsigned long long gt;
+        unsigned smid;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        p.trace[3 * 256 + 0] = gt;
-        p.trace[3 * 256 + 1] = clock64();
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        if (blockIdx.x == 0) {
+            p.trace[3 * 256 + 0] = gt;
+            p.trace[3 * 256 + 1] = clock64();
+        }
+        p.trace[1024 + blockIdx.x * 4 + 0] = gt;
+        p.trace[1024 + blockIdx.x * 4 + 2] = smid;
+        p.trace[1024 + blockIdx.x * 4 + 3] = clock64();
     }
 #endif
 
@@ -421,11 +428,15 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 const uint32_t part = warp - 2;  // 0: hi, 1: lo
                 const uint32_t v_lo0 = desc_lo(smem_u32(v_smem), kChunkBytes);
                 bool ok = true;
-                int st = 0, vs = 0;
+                int st = 0, vs = 0, items_done = 0;
                 uint32_t ph = 0;
                 for (int r = 0; r < n_rounds && ok; r++) {
                     const TcItem it = item_of(r);
                     if (!it.valid) continue;
+                    // one tile per item: O alternates between the two accumulators from item to item,
+                    // so the previous item's result can be read out while this one accumulates
+                    const uint32_t o_sel = kTiles == 1 ? (items_done & 1) : 0;
+                    items_done++;
                     for (int j = 0; j < it.n_steps && ok; j++) {
                         if (part == 0) FA_TRACE(1, vs, 3);
                         ok = mbar_wait(&sh->v_full[st], ph, abort_flag);
@@ -439,7 +450,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             if (!ok) break;
                             if (part == 0) FA_TRACE(1, vs, 1);
                             tc_fence_after_sync();
-                            const uint32_t d = tmem + 2 * kT + t * kT;
+                            const uint32_t d = tmem + 2 * kT + (t + o_sel) * kT;
                             // P: each 64-column half of S_b became 32 columns of hi + 32 of lo (8 columns per
                             // 16 keys); V MN-major: 16 keys = 2 KB further per step, second 64 dims via LBO
 #pragma unroll
@@ -480,6 +491,83 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         const int node = row & (kNodeSlots - 1); // tree: node slot of this row
         bool ok = true;
         int vs = 0, kvs = 0, items_done = 0;     // virtual steps, K/V steps, items handled so far
+
+        // Read-out of a finished item.  With one tile per item it is deferred: the item's O stays in
+        // its accumulator while the next item starts in the other one, and one 32-column chunk is
+        // written after each of the next item's first softmax steps, behind the MMAs of those steps.
+        constexpr bool kDefer = kTiles == 1;
+        struct Readout {
+            int chunks_left;     // 0: nothing pending
+            uint32_t phase;      // o_final parity of the item
+            uint32_t o_addr;     // this thread's first O column in TMEM
+            float inv;           // 1 / row sum
+            bool store;          // this row is a live output row
+            size_t base;         // element offset of this thread's first output value
+            int rows_in_quad;    // prefill, fp16 output: live rows among the four of this lane's quad
+            size_t quad_base;    // same path: element offset of the quad's first row, at this lane's 8 columns
+        } pend;
+        pend.chunks_left = 0;
+        auto readout_chunk = [&](Readout& e) {
+            const int ch = kChunks - e.chunks_left;
+            if (ch == 0) {
+                if (ok) ok = mbar_wait(&sh->o_final, e.phase, abort_flag);
+                tc_fence_after_sync();
+            }
+            e.chunks_left--;
+            if (!ok) return;
+            uint32_t rr[32];
+            __syncwarp();
+            tmem_ld32(e.o_addr + ch * 32, rr);
+            tmem_wait_ld();
+            if (!kTree && p.out_fp16) {
+                // four 16-byte pieces per row; a 4 x 4 exchange inside each quad of lanes makes every
+                // store instruction write 64 contiguous bytes per row instead of 16
+                uint4 x[4];
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    x[v].x = pack_half2(__uint_as_float(rr[v * 8 + 0]) * e.inv, __uint_as_float(rr[v * 8 + 1]) * e.inv);
+                    x[v].y = pack_half2(__uint_as_float(rr[v * 8 + 2]) * e.inv, __uint_as_float(rr[v * 8 + 3]) * e.inv);
+                    x[v].z = pack_half2(__uint_as_float(rr[v * 8 + 4]) * e.inv, __uint_as_float(rr[v * 8 + 5]) * e.inv);
+                    x[v].w = pack_half2(__uint_as_float(rr[v * 8 + 6]) * e.inv, __uint_as_float(rr[v * 8 + 7]) * e.inv);
+                }
+                auto swap4 = [&](uint4 give, int mask) {
+                    uint4 got;
+                    got.x = __shfl_xor_sync(0xffffffffu, give.x, mask);
+                    got.y = __shfl_xor_sync(0xffffffffu, give.y, mask);
+                    got.z = __shfl_xor_sync(0xffffffffu, give.z, mask);
+                    got.w = __shfl_xor_sync(0xffffffffu, give.w, mask);
+                    return got;
+                };
+                const bool i0 = lane & 1, i1 = lane & 2;
+                uint4 z[4], y[4];
+                // stage 1 (lane ^ 1): z[u + w] = piece u + i0 of the row with low bit w
+#pragma unroll
+                for (int u = 0; u < 4; u += 2) {
+                    const uint4 got = swap4(i0 ? x[u] : x[u + 1], 1);
+                    z[u] = i0 ? got : x[u];
+                    z[u + 1] = i0 ? x[u + 1] : got;
+                }
+                // stage 2 (lane ^ 2): y[s] = piece (lane & 3) of row s of the quad
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    const uint4 got = swap4(i1 ? z[w] : z[2 + w], 2);
+                    y[w] = i1 ? got : z[w];
+                    y[2 + w] = i1 ? z[2 + w] : got;
+                }
+                __half* outp = static_cast<__half*>(p.out) + e.quad_base + ch * 32;
+#pragma unroll
+                for (int sr = 0; sr < 4; sr++)
+                    if (sr < e.rows_in_quad) *reinterpret_cast<uint4*>(outp + (size_t)sr * p.num_heads * kT) = y[sr];
+            } else if (e.store) {
+                float* outp = kTree ? p.tree_out : static_cast<float*>(p.out);
+                float4* dst = reinterpret_cast<float4*>(outp + e.base + ch * 32);
+#pragma unroll
+                for (int v = 0; v < 8; v++)
+                    dst[v] = make_float4(__uint_as_float(rr[v * 4 + 0]) * e.inv, __uint_as_float(rr[v * 4 + 1]) * e.inv,
+                                         __uint_as_float(rr[v * 4 + 2]) * e.inv, __uint_as_float(rr[v * 4 + 3]) * e.inv);
+            }
+        };
+
         for (int r = 0; r < n_rounds; r++) {
             const TcItem it = item_of(r);
             if (!it.valid) continue;
@@ -493,6 +581,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 anc = ancestor_word(par, node, N);
             }
             float m_used_t[kTiles], l_run_t[kTiles];  // running maximum and sum of this row, per query tile
+            const int o_sel = kDefer ? (items_done & 1) : 0;  // accumulator of this item (see the output MMAs)
             {
                 // O starts at zero so that every output MMA can accumulate
                 uint32_t z[32];
@@ -503,7 +592,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     m_used_t[t] = -INFINITY;
                     l_run_t[t] = 0.f;
 #pragma unroll
-                    for (int ch = 0; ch < kChunks; ch++) tmem_st32(lane_base + 2 * kT + t * kT + col0 + ch * 32, z);
+                    for (int ch = 0; ch < kChunks; ch++) tmem_st32(lane_base + 2 * kT + (t + o_sel) * kT + col0 + ch * 32, z);
                 }
                 tmem_wait_st();
             }
@@ -521,8 +610,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     float& l_run = l_run_t[t];
                     const int b = vs & 1;
                     const uint32_t s_addr = lane_base + b * kT + col0;
-                    const uint32_t o_addr = lane_base + 2 * kT + t * kT + col0;
+                    const uint32_t o_addr = lane_base + 2 * kT + (t + o_sel) * kT + col0;
+                    if (warp == 4) FA_TRACE(2, vs, 0);
                     if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
+                    if (warp == 4) FA_TRACE(2, vs, 1);
                     if (!ok) {  // keep the barrier count intact so nobody is left waiting
                         if (kColSplit) softmax_group_sync();
                         continue;
@@ -631,79 +722,68 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(&sh->p_ready[b]);
+                    if (warp == 4) FA_TRACE(2, vs, 2);
+                    if (kDefer && pend.chunks_left > 0) readout_chunk(pend);  // behind the MMAs of this step
+                    if (warp == 4) FA_TRACE(2, vs, 3);
                 }
             }
-            // row sums of the two column halves
+            while (kDefer && pend.chunks_left > 0) readout_chunk(pend);  // an item shorter than the read-out
+            // row sums of the two column halves, through the exchange slot the last step did not use
+            // (its readers all passed that step's barrier)
             float l_total_t[kTiles];
-            softmax_group_sync();  // every thread is done with the exchange slots of the last steps
+            if (kTiles == 2) softmax_group_sync();  // both slots were in use by the last two virtual steps
+            const int xs = kTiles == 2 ? 0 : (vs & 1);
 #pragma unroll
-            for (int t = 0; t < kTiles; t++) sh->xchg[t][wg][row] = l_run_t[t];
+            for (int t = 0; t < kTiles; t++) sh->xchg[xs ^ t][wg][row] = l_run_t[t];
             softmax_group_sync();
 #pragma unroll
-            for (int t = 0; t < kTiles; t++) l_total_t[t] = l_run_t[t] + sh->xchg[t][wg ^ 1][row];
+            for (int t = 0; t < kTiles; t++) l_total_t[t] = l_run_t[t] + sh->xchg[xs ^ t][wg ^ 1][row];
             softmax_group_sync();  // the slots are reused by the next item's first steps
-            if (ok) ok = mbar_wait(&sh->o_final, items_done & 1, abort_flag);
-            items_done++;
-            if (ok) {
-                tc_fence_after_sync();
 #pragma unroll
-                for (int t = 0; t < kTiles; t++) {
-                const float inv = 1.0f / l_total_t[t];
-                const uint32_t o_addr = lane_base + 2 * kT + t * kT + col0;
-                bool store;
-                size_t base;  // element offset of this thread's first output value
+            for (int t = 0; t < kTiles; t++) {
+                Readout e;
+                e.chunks_left = kChunks;
+                e.phase = items_done & 1;
+                e.o_addr = lane_base + 2 * kT + (t + o_sel) * kT + col0;
+                e.inv = 1.0f / l_total_t[t];
+                e.rows_in_quad = 0;
+                e.quad_base = 0;
                 if (kTree) {
                     const int head = it.head0 + 2 * t + (row >> 6);
-                    store = node < N && head < (it.kvh + 1) * p.group;
-                    base = (((size_t)it.b * p.num_heads + head) * N + node) * kT + col0;
+                    e.store = node < N && head < (it.kvh + 1) * p.group;
+                    e.base = (((size_t)it.b * p.num_heads + head) * N + node) * kT + col0;
                 } else {
-                    store = row < it.rows_here;
-                    base = ((size_t)q_pos * p.num_heads + it.head0 + t) * kT + col0;
+                    e.store = row < it.rows_here;
+                    e.base = ((size_t)q_pos * p.num_heads + it.head0 + t) * kT + col0;
+                    const int quad_row = row & ~3;
+                    e.rows_in_quad = it.rows_here - quad_row;  // may be <= 0 or > 4
+                    e.quad_base = ((size_t)(it.q0 + quad_row) * p.num_heads + it.head0 + t) * kT + col0 + (lane & 3) * 8;
                 }
-                uint32_t rr[32];
-#pragma unroll 1
-                for (int ch = 0; ch < kChunks; ch++) {
-                    __syncwarp();
-                    tmem_ld32(o_addr + ch * 32, rr);
-                    tmem_wait_ld();
-                    if (store) {
-                        if (!kTree && p.out_fp16) {
-                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + base + ch * 32);
-#pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                uint4 o;
-                                o.x = pack_half2(__uint_as_float(rr[v * 8 + 0]) * inv, __uint_as_float(rr[v * 8 + 1]) * inv);
-                                o.y = pack_half2(__uint_as_float(rr[v * 8 + 2]) * inv, __uint_as_float(rr[v * 8 + 3]) * inv);
-                                o.z = pack_half2(__uint_as_float(rr[v * 8 + 4]) * inv, __uint_as_float(rr[v * 8 + 5]) * inv);
-                                o.w = pack_half2(__uint_as_float(rr[v * 8 + 6]) * inv, __uint_as_float(rr[v * 8 + 7]) * inv);
-                                dst[v] = o;
-                            }
-                        } else {
-                            float* outp = kTree ? p.tree_out : static_cast<float*>(p.out);
-                            float4* dst = reinterpret_cast<float4*>(outp + base + ch * 32);
-#pragma unroll
-                            for (int v = 0; v < 8; v++)
-                                dst[v] = make_float4(__uint_as_float(rr[v * 4 + 0]) * inv, __uint_as_float(rr[v * 4 + 1]) * inv,
-                                                     __uint_as_float(rr[v * 4 + 2]) * inv, __uint_as_float(rr[v * 4 + 3]) * inv);
-                        }
-                    }
+                if (kDefer) {
+                    pend = e;
+                } else {
+                    while (e.chunks_left > 0) readout_chunk(e);
                 }
-                }  // tiles
-            } else if (lane == 0) {
-                atomicOr(p.status, kStatusTimeout);
             }
+            items_done++;
         }  // items
+        while (kDefer && pend.chunks_left > 0) readout_chunk(pend);
+        if (!ok && lane == 0) atomicOr(p.status, kStatusTimeout);
     }
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
 #ifdef GB_FA_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        p.trace[3 * 256 + 2] = gt;
-        p.trace[3 * 256 + 3] = clock64();
+        if (blockIdx.x == 0) {
+            p.trace[3 * 256 + 2] = gt;
+            p.trace[3 * 256 + 3] = clock64();
+        }
+        p.trace[1024 + blockIdx.x * 4 + 1] = gt;
+        p.trace[1024 + blockIdx.x * 4 + 3] = clock64() - p.trace[1024 + blockIdx.x * 4 + 3];
     }
 #endif
     if (warp == 1) {
@@ -726,22 +806,33 @@ static int launch_tc(granite_cuda_compute* c, TcKernel kern, const char* name, i
     const int grid = n_items < c->sm_count ? n_items : c->sm_count;  // persistent CTAs, one per SM
 #ifdef GB_FA_TRACE
     static unsigned long long* trace_buf = nullptr;
-    if (!trace_buf) cudaMalloc(&trace_buf, 4 * 256 * sizeof(unsigned long long));
-    cudaMemsetAsync(trace_buf, 0, 4 * 256 * sizeof(unsigned long long), c->stream);
+    if (!trace_buf) cudaMalloc(&trace_buf, 8 * 256 * sizeof(unsigned long long));
+    cudaMemsetAsync(trace_buf, 0, 8 * 256 * sizeof(unsigned long long), c->stream);
     TcParams pt = p;
     pt.trace = trace_buf;
     {
         LaunchScope t(c, name);
         kern<<<grid, kTcThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, *ktmap, *vtmap, pt);
     }
-    static unsigned long long host_trace[4 * 256];
+    static unsigned long long host_trace[8 * 256];
     cudaMemcpyAsync(host_trace, trace_buf, sizeof(host_trace), cudaMemcpyDeviceToHost, c->stream);
     cudaStreamSynchronize(c->stream);
     {
         fprintf(stderr, "trace cta0: %lld ns, %lld cycles -> %.3f GHz\n", (long long)(host_trace[768 + 2] - host_trace[768 + 0]),
                 (long long)(host_trace[768 + 3] - host_trace[768 + 1]),
                 (double)(host_trace[768 + 3] - host_trace[768 + 1]) / (double)(host_trace[768 + 2] - host_trace[768 + 0]));
-        const unsigned long long t0 = host_trace[2 * 256 + 1];
+        unsigned long long first = ~0ull, last = 0;
+        for (int b = 0; b < grid; b++) {
+            first = host_trace[1024 + b * 4] < first ? host_trace[1024 + b * 4] : first;
+            last = host_trace[1024 + b * 4 + 1] > last ? host_trace[1024 + b * 4 + 1] : last;
+        }
+        fprintf(stderr, "trace grid: first start -> last end %lld ns\n", (long long)(last - first));
+        for (int b = 0; b < grid; b++)
+            fprintf(stderr, "trace cta %3d sm %3d: start +%6lld ns, end +%6lld ns, life %6lld ns, %7lld clk\n", b,
+                    (int)host_trace[1024 + b * 4 + 2], (long long)(host_trace[1024 + b * 4] - first),
+                    (long long)(host_trace[1024 + b * 4 + 1] - first),
+                    (long long)(host_trace[1024 + b * 4 + 1] - host_trace[1024 + b * 4]), (long long)host_trace[1024 + b * 4 + 3]);
+        const unsigned long long t0 = host_trace[768 + 1];
         const char* roles[3] = {"qk ", "pvh", "smx"};
         for (int step = 0; step < 64; step++)
             for (int r = 0; r < 3; r++)
