@@ -648,7 +648,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
 #pragma unroll
                             for (int c = 0; c < 32; c += 2) {
                                 const int k = (kChunks == 4) ? ch : ch * 2 + ((c >> 1) & 1);
-                                mm[k] = fmaxf(mm[k], fmaxf(__uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1])));
+                                mm[k] = max3(mm[k], __uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1]));
                             }
                         mx = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
                     }
@@ -684,8 +684,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     if (has_cols) {
                         // P = 2^(s*scale - m): each 64-column half of S becomes 32 columns of fp16 hi
                         // followed by 32 columns of lo
-                        float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial sums
-                        const float neg_m = -m_used;
+                        uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};  // independent partial sums, packed pairs of fp32
+                        const uint64_t scale2 = f32x2(p.scale_log2, p.scale_log2);
+                        const uint64_t neg_m2 = f32x2(-m_used, -m_used);
 #pragma unroll
                         for (int ch = 0; ch < kChunks; ch++) {
                             if (tree_step && ch >= 2) continue;
@@ -693,16 +694,18 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
 #pragma unroll
                             for (int c = 0; c < 32; c += 2) {
                                 // masked scores are -inf: exp2 gives exactly 0
-                                const float p0 = fast_exp2(fmaf(__uint_as_float(x[ch][c]), p.scale_log2, neg_m));
-                                const float p1 = fast_exp2(fmaf(__uint_as_float(x[ch][c + 1]), p.scale_log2, neg_m));
-                                ls[c & 6] += p0;
-                                ls[(c & 6) + 1] += p1;
-                                split_hi_lo(p0, p1, hi[c >> 1], lo[c >> 1]);
+                                float t0, t1;
+                                f32x2_get(fma_f32x2(f32x2(__uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1])), scale2, neg_m2), t0, t1);
+                                const uint64_t pp = f32x2(fast_exp2(t0), fast_exp2(t1));
+                                ls[(c >> 1) & 3] = add_f32x2(ls[(c >> 1) & 3], pp);
+                                split_hi_lo_x2(pp, hi[c >> 1], lo[c >> 1]);
                             }
                             tmem_st16(s_addr + (ch >> 1) * 64 + (ch & 1) * 16, hi);
                             tmem_st16(s_addr + (ch >> 1) * 64 + 32 + (ch & 1) * 16, lo);
                         }
-                        l_run += ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
+                        float la, lb;
+                        f32x2_get(add_f32x2(add_f32x2(ls[0], ls[1]), add_f32x2(ls[2], ls[3])), la, lb);
+                        l_run += la + lb;
                     }
                     if (t == 0 && wg == 0 && need_mask && k0 + kT > (kTree ? it.cache_len : p.seq_kv)) {
                         // keys past the live length carry P = 0, but their V rows may hold anything (even

@@ -261,6 +261,45 @@ __device__ __forceinline__ void split_hi_lo(float x0, float x1, uint32_t& hi, ui
     hi = pack_half2(h0, h1);
     lo = pack_half2(x0 - h0, x1 - h1);
 }
+// Packed pairs of fp32 in one 64-bit register: one issue slot for two lanes of arithmetic.
+__device__ __forceinline__ uint64_t f32x2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f32x2_get(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// split_hi_lo on a packed pair
+__device__ __forceinline__ void split_hi_lo_x2(uint64_t p, uint32_t& hi, uint32_t& lo) {
+    const uint64_t h = p & 0xFFFFE000FFFFE000ull;
+    const uint64_t l = sub_f32x2(p, h);
+    float h0, h1, l0, l1;
+    f32x2_get(h, h0, h1);
+    f32x2_get(l, l0, l1);
+    hi = pack_half2(h0, h1);
+    lo = pack_half2(l0, l1);
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
