@@ -112,6 +112,34 @@ class PagedKvAppendArgs(C.Structure):
                 ("table_len", C.c_uint32), ("batch_size", C.c_uint32)]
 
 
+class RopeAppendArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("cos_table", C.c_void_p),
+                ("sin_table", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("block_tables", C.c_void_p), ("positions", C.c_void_p),
+                ("batch_size", C.c_uint32), ("new_len", C.c_uint32), ("num_heads", C.c_uint32),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("block_size", C.c_uint32),
+                ("max_blocks_per_seq", C.c_uint32), ("num_blocks", C.c_uint32), ("table_len", C.c_uint32),
+                ("start_pos", C.c_uint32)]
+
+
+class TreeCommitArgs(C.Structure):
+    _fields_ = [("k_tree", C.c_void_p), ("v_tree", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("block_tables", C.c_void_p), ("cache_lens", C.c_void_p), ("accepted", C.c_void_p),
+                ("num_accepted", C.c_void_p),
+                ("batch_size", C.c_uint32), ("num_nodes", C.c_uint32), ("max_accepted", C.c_uint32),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("block_size", C.c_uint32),
+                ("max_blocks_per_seq", C.c_uint32), ("num_blocks", C.c_uint32)]
+
+
+class PagedPrefillArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("block_table", C.c_void_p),
+                ("output", C.c_void_p),
+                ("num_heads", C.c_uint32), ("num_kv_heads", C.c_uint32), ("seq_q", C.c_uint32),
+                ("start_pos", C.c_uint32), ("head_dim", C.c_uint32), ("block_size", C.c_uint32),
+                ("max_blocks_per_seq", C.c_uint32), ("num_blocks", C.c_uint32), ("q_dtype", C.c_uint32),
+                ("out_dtype", C.c_uint32), ("scale", C.c_float)]
+
+
 class KernelTiming(C.Structure):
     _fields_ = [("name", C.c_char * 64), ("gpu_time_ms", C.c_double), ("dispatches", C.c_uint64)]
 
@@ -148,6 +176,13 @@ _sig("granite_cuda_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(KvAppendArgs
 _sig("granite_cuda_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(PagedKvAppendArgs))
 _sig("granite_cuda_attention_tree", C.c_int, C.c_void_p, C.POINTER(TreeAttentionArgs))
 _sig("granite_cuda_build_tree_mask", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32)
+_sig("granite_cuda_rope_table_create", C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float,
+     C.POINTER(C.c_void_p), C.POINTER(C.c_void_p))
+_sig("granite_cuda_rope_multihead", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+     C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32)
+_sig("granite_cuda_rope_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(RopeAppendArgs))
+_sig("granite_cuda_tree_commit", C.c_int, C.c_void_p, C.POINTER(TreeCommitArgs))
+_sig("granite_cuda_paged_prefill_attention", C.c_int, C.c_void_p, C.POINTER(PagedPrefillArgs))
 _sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
      C.c_void_p)
 
@@ -296,6 +331,42 @@ class CudaCompute:
                               _ptr(positions), num_kv_heads, head_dim, start_pos, new_len, block_size,
                               num_blocks, table_len, batch_size)
         check(lib.granite_cuda_paged_kv_cache_append(self._h, C.byref(a)))
+
+    def rope_table_create(self, max_seq_len: int, head_dim: int, theta: float = 10000.0) -> tuple[int, int]:
+        """Device addresses of the cos and sin tables [max_seq_len, head_dim/2] (free with destroy_buffer)."""
+        cos, sin = C.c_void_p(), C.c_void_p()
+        check(lib.granite_cuda_rope_table_create(self._h, max_seq_len, head_dim, theta, C.byref(cos), C.byref(sin)))
+        return cos.value, sin.value
+
+    def rope_multihead(self, q, k, num_heads_q, num_heads_k, seq_len, head_dim, start_pos, cos_table, sin_table,
+                       table_len) -> None:
+        check(lib.granite_cuda_rope_multihead(self._h, C.c_void_p(_ptr(q)), C.c_void_p(_ptr(k)), num_heads_q,
+                                              num_heads_k, seq_len, head_dim, start_pos,
+                                              C.c_void_p(_ptr(cos_table)), C.c_void_p(_ptr(sin_table)), table_len))
+
+    def rope_paged_kv_cache_append(self, q, k, v, cos_table, sin_table, K_cache, V_cache, block_tables, positions,
+                                   batch_size, new_len, num_heads, num_kv_heads, head_dim, block_size,
+                                   max_blocks_per_seq, num_blocks, table_len, start_pos=0) -> None:
+        a = RopeAppendArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(cos_table), _ptr(sin_table), _ptr(K_cache),
+                           _ptr(V_cache), _ptr(block_tables), _ptr(positions), batch_size, new_len, num_heads,
+                           num_kv_heads, head_dim, block_size, max_blocks_per_seq, num_blocks, table_len, start_pos)
+        check(lib.granite_cuda_rope_paged_kv_cache_append(self._h, C.byref(a)))
+
+    def tree_commit(self, K_tree, V_tree, K_cache, V_cache, block_tables, cache_lens, accepted, num_accepted,
+                    batch_size, num_nodes, max_accepted, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                    num_blocks) -> None:
+        a = TreeCommitArgs(_ptr(K_tree), _ptr(V_tree), _ptr(K_cache), _ptr(V_cache), _ptr(block_tables),
+                           _ptr(cache_lens), _ptr(accepted), _ptr(num_accepted), batch_size, num_nodes,
+                           max_accepted, num_kv_heads, head_dim, block_size, max_blocks_per_seq, num_blocks)
+        check(lib.granite_cuda_tree_commit(self._h, C.byref(a)))
+
+    def paged_prefill_attention(self, Q, K_cache, V_cache, block_table, output, num_heads, num_kv_heads, seq_q,
+                                start_pos, head_dim, block_size, max_blocks_per_seq, num_blocks, scale,
+                                q_dtype=0, out_dtype=0) -> None:
+        a = PagedPrefillArgs(_ptr(Q), _ptr(K_cache), _ptr(V_cache), _ptr(block_table), _ptr(output), num_heads,
+                             num_kv_heads, seq_q, start_pos, head_dim, block_size, max_blocks_per_seq, num_blocks,
+                             q_dtype, out_dtype, scale)
+        check(lib.granite_cuda_paged_prefill_attention(self._h, C.byref(a)))
 
     def build_tree_mask(self, parent_indices, masks, batch_size, num_nodes) -> None:
         check(lib.granite_cuda_build_tree_mask(self._h, C.c_void_p(_ptr(parent_indices)),

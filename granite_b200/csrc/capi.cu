@@ -1,9 +1,11 @@
 // extern "C" entry points declared in include/granite_cuda.h: compute-object lifecycle, raw
 // buffers, and the attention calls.  Errors are values (granite::ErrorCode numbers), never
 // exceptions; there is no CPU fallback anywhere below this boundary.
+#include <cmath>
 #include <cstring>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "compute_internal.h"
 
@@ -353,6 +355,68 @@ int granite_cuda_paged_kv_cache_append(granite_cuda_compute_t* c, const GraniteC
     if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "paged_kv_cache_append: null argument");
     GB_CUDA_TRY(cudaSetDevice(c->device));
     return launch_paged_kv_cache_append(c, *args);
+}
+
+int granite_cuda_rope_table_create(granite_cuda_compute_t* c, uint32_t max_seq_len, uint32_t head_dim, float theta,
+                                   float** cos_table, float** sin_table) {
+    if (!c || !cos_table || !sin_table) return fail(GRANITE_CUDA_NULL_POINTER, "rope_table_create: null argument");
+    if (max_seq_len == 0 || head_dim < 2 || head_dim % 2 != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "rope_table_create: head_dim must be even and max_seq_len positive");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    // Host arithmetic on purpose: the tables must carry the bits of the CPU path's own
+    // float pow / cos / sin (src/llm/rope.cpp:13-20), which device intrinsics do not promise.
+    const size_t half_dim = head_dim / 2, n = (size_t)max_seq_len * half_dim;
+    std::vector<float> inv_freq(half_dim), cos_h(n), sin_h(n);
+    for (size_t i = 0; i < half_dim; i++)
+        inv_freq[i] = 1.0f / std::pow(theta, static_cast<float>(2 * i) / static_cast<int>(head_dim));
+    for (size_t pos = 0; pos < max_seq_len; pos++)
+        for (size_t i = 0; i < half_dim; i++) {
+            const float angle = static_cast<float>(pos) * inv_freq[i];
+            cos_h[pos * half_dim + i] = std::cos(angle);
+            sin_h[pos * half_dim + i] = std::sin(angle);
+        }
+    float *cos_d = nullptr, *sin_d = nullptr;
+    cudaError_t e = cudaMalloc(&cos_d, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&sin_d, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(cos_d, cos_h.data(), n * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(sin_d, sin_h.data(), n * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);  // the host vectors go away on return
+    if (e != cudaSuccess) {
+        cudaFree(cos_d);
+        cudaFree(sin_d);
+        cudaGetLastError();
+        return fail(e == cudaErrorMemoryAllocation ? GRANITE_CUDA_OUT_OF_MEMORY : GRANITE_CUDA_INTERNAL_ERROR,
+                    std::string("rope_table_create: ") + cudaGetErrorString(e));
+    }
+    *cos_table = cos_d;
+    *sin_table = sin_d;
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int granite_cuda_rope_multihead(granite_cuda_compute_t* c, float* q, float* k, uint32_t num_heads_q, uint32_t num_heads_k,
+                                uint32_t seq_len, uint32_t head_dim, uint32_t start_pos, const float* cos_table,
+                                const float* sin_table, uint32_t table_len) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "rope_multihead: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_rope_multihead(c, q, k, num_heads_q, num_heads_k, seq_len, head_dim, start_pos, cos_table, sin_table, table_len);
+}
+
+int granite_cuda_rope_paged_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaRopeAppendArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "rope_paged_kv_cache_append: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_rope_paged_append(c, *args);
+}
+
+int granite_cuda_tree_commit(granite_cuda_compute_t* c, const GraniteCudaTreeCommitArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "tree_commit: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_tree_commit(c, *args);
+}
+
+int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const GraniteCudaPagedPrefillArgs* args) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "paged_prefill_attention: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_paged_prefill(c, *args);
 }
 
 int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTreeAttentionArgs* args) {

@@ -114,4 +114,9 @@ int launch_kv_cache_append(granite_cuda_compute* c, const GraniteCudaKvAppendArg
 int launch_paged_kv_cache_append(granite_cuda_compute* c, const GraniteCudaPagedKvAppendArgs& a);
 int launch_sdpa_operator(granite_cuda_compute* c, const GraniteCudaSdpaArgs& a);
 int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* masks, uint32_t batch, uint32_t n);
+int launch_rope_multihead(granite_cuda_compute* c, float* q, float* k, uint32_t hq, uint32_t hk, uint32_t seq_len,
+                          uint32_t head_dim, uint32_t start_pos, const float* cos_t, const float* sin_t, uint32_t table_len);
+int launch_rope_paged_append(granite_cuda_compute* c, const GraniteCudaRopeAppendArgs& a);
+int launch_tree_commit(granite_cuda_compute* c, const GraniteCudaTreeCommitArgs& a);
+int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a);
 }  // namespace gb200

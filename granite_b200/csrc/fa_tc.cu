@@ -218,7 +218,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             const int k_end = min(p.seq_kv, p.start_pos + it.q0 + it.rows_here);  // exclusive: last visible key + 1
             it.n_steps = (k_end + kT - 1) / kT;
             it.n_prefix = it.n_steps;
-            it.cache_len = 0;
+            it.cache_len = p.seq_kv;  // paged K/V: pages past the live length are not looked up
         }
         return it;
     };
@@ -299,7 +299,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 // page entries of the next prefix tile are fetched one tile ahead (lanes 0-7, one page each)
                 auto load_entry = [&](int j) {
                     int e = 0;
-                    if (kTree && kPaged && j < it.n_prefix && lane < 8) {
+                    if (kPaged && j < it.n_prefix && lane < 8) {
                         const int logical = j * 8 + lane;
                         if (logical * kPageRows < it.cache_len) {
                             e = p.tables[(size_t)it.b * p.max_blocks + logical];
@@ -337,7 +337,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             if (lane < 2)
                                 tma_load_3d(dst + c * kChunkBytes, is_v ? &vtmap : &ktmap, full, c * 64, 0,
                                             it.b * p.num_kv_heads + it.kvh);
-                        } else if (kTree && kPaged) {
+                        } else if (kPaged) {
                             // lane = (page, chunk): 8 pages x 2 chunks
                             const int pg = (lane >> 1) & 7;
                             const int e = __shfl_sync(0xffffffffu, entry, pg);
@@ -908,6 +908,60 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     TcKernel kern = split_q ? fa_tc_kernel<false, false, true, 1> : fa_tc_kernel<false, false, false, 1>;
     const int n_items = p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
     return launch_tc(c, kern, "prefill_causal_fa", n_items, split_q ? 2 : tiles, qmap, qlomap, kmap, vmap, kmap, vmap, p);
+}
+
+// Causal attention of a chunk of new tokens against the sequence's paged cache: the prefill
+// kernel with its K/V tiles gathered page by page through the block table.
+int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a) {
+    if (!a.q || !a.k_cache || !a.v_cache || !a.block_table || !a.output)
+        return fail(GRANITE_CUDA_NULL_POINTER, "paged_prefill_attention: null buffer");
+    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: head_dim must be 128");
+    if (a.block_size != (uint32_t)kPageRows || a.num_blocks == 0 || a.max_blocks_per_seq == 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: block_size must be 16 and the pool non-empty");
+    if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: num_heads must be a multiple of num_kv_heads");
+    if (a.q_dtype > 1 || a.out_dtype > 1)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: dtype must be 0 (fp32) or 1 (fp16)");
+    if (a.seq_q == 0) return GRANITE_CUDA_SUCCESS;
+    const uint64_t seq_kv = (uint64_t)a.start_pos + a.seq_q;
+    if (seq_kv > (uint64_t)a.max_blocks_per_seq * kPageRows)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: the chunk ends beyond the block table");
+
+    const bool split_q = a.q_dtype == 0;
+    const void *q16 = a.q, *q16_lo = a.q;
+    if (split_q) {
+        int rc = split_queries(c, a.q, (size_t)a.seq_q * a.num_heads * kT, &q16, &q16_lo);
+        if (rc) return rc;
+    }
+    TcParams p{};
+    p.num_heads = (int)a.num_heads;
+    p.num_kv_heads = (int)a.num_kv_heads;
+    p.group = (int)(a.num_heads / a.num_kv_heads);
+    p.units_per_kvh = p.group;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = c->d_status;
+    p.out = a.output;
+    p.out_fp16 = a.out_dtype == 1;
+    p.seq_q = (int)a.seq_q;
+    p.seq_kv = (int)seq_kv;
+    p.max_seq = (int)seq_kv;
+    p.n_qblocks = (p.seq_q + kT - 1) / kT;
+    p.start_pos = (int)a.start_pos;
+    p.tables = a.block_table;
+    p.batch = 1;
+    p.max_blocks = (int)a.max_blocks_per_seq;
+    p.num_blocks = (int)a.num_blocks;
+
+    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * kT;
+    const CUtensorMap* kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
+    const CUtensorMap* vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
+    if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
+
+    TcKernel kern = split_q ? fa_tc_kernel<false, true, true, 1> : fa_tc_kernel<false, true, false, 1>;
+    const int n_items = p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
+    return launch_tc(c, kern, "paged_prefill_fa", n_items, split_q ? 2 : 1, qmap, qlomap, kmap, vmap, kmap, vmap, p);
 }
 
 int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* masks, uint32_t batch, uint32_t n) {

@@ -120,6 +120,96 @@ Result<void> CudaCompute::batched_paged_attention_decode(const float* Q, const v
     return cuda_result(granite_cuda_batched_paged_attention_decode(h_, &a));
 }
 
+Result<void> CudaCompute::rope_multihead(float* q, float* k, uint32_t num_heads_q, uint32_t num_heads_k,
+                                         uint32_t seq_len, uint32_t head_dim, uint32_t start_pos,
+                                         const float* cos_table, const float* sin_table, uint32_t table_len) {
+    return cuda_result(granite_cuda_rope_multihead(h_, q, k, num_heads_q, num_heads_k, seq_len, head_dim, start_pos,
+                                                   cos_table, sin_table, table_len));
+}
+
+Result<void> CudaCompute::rope_paged_kv_cache_append(const GraniteCudaRopeAppendArgs& args) {
+    return cuda_result(granite_cuda_rope_paged_kv_cache_append(h_, &args));
+}
+
+Result<void> CudaCompute::tree_commit(const GraniteCudaTreeCommitArgs& args) {
+    return cuda_result(granite_cuda_tree_commit(h_, &args));
+}
+
+Result<void> CudaCompute::paged_prefill_attention(const GraniteCudaPagedPrefillArgs& args) {
+    return cuda_result(granite_cuda_paged_prefill_attention(h_, &args));
+}
+
+// =================================================================== RoPECache (src/llm/rope.cpp)
+void RoPECache::initialize(int max_seq_len, int head_dim, float theta) {
+    max_seq_len_ = max_seq_len;
+    head_dim_ = head_dim;
+    const int half_dim = head_dim / 2;
+    cos_.assign(static_cast<size_t>(max_seq_len) * half_dim, 0.0f);
+    sin_.assign(cos_.size(), 0.0f);
+    // float arithmetic throughout, one pow per (position, pair) as the reference computes it
+    // (rope.cpp:13-20): the tables are part of the bit-exact contract of the rotation
+    for (int pos = 0; pos < max_seq_len; pos++)
+        for (int i = 0; i < half_dim; i++) {
+            const float freq = 1.0f / std::pow(theta, static_cast<float>(2 * i) / head_dim);
+            const float angle = static_cast<float>(pos) * freq;
+            cos_[static_cast<size_t>(pos) * half_dim + i] = std::cos(angle);
+            sin_[static_cast<size_t>(pos) * half_dim + i] = std::sin(angle);
+        }
+    if (d_cos_ && owner_) {  // re-initialised: the device copies are stale
+        granite_cuda_free(owner_, d_cos_);
+        granite_cuda_free(owner_, d_sin_);
+        d_cos_ = d_sin_ = nullptr;
+    }
+}
+
+RoPECache::~RoPECache() {
+    if (owner_ && d_cos_) {
+        granite_cuda_free(owner_, d_cos_);
+        granite_cuda_free(owner_, d_sin_);
+    }
+}
+
+Result<void> RoPECache::upload(granite_cuda_compute_t* compute) {
+    if (!is_initialized()) return Error(ErrorCode::InvalidState, "RoPE cache not initialized");
+    if (d_cos_ && owner_ == compute) return {};
+    if (!compute) return Error(ErrorCode::NullPointer, "RoPECache::upload: null compute object");
+    void *c = nullptr, *s = nullptr;
+    const size_t bytes = cos_.size() * sizeof(float);
+    int rc = granite_cuda_malloc(compute, bytes, &c);
+    if (!rc) rc = granite_cuda_malloc(compute, bytes, &s);
+    if (!rc) rc = granite_cuda_write_buffer(compute, c, cos_.data(), bytes);
+    if (!rc) rc = granite_cuda_write_buffer(compute, s, sin_.data(), bytes);
+    if (!rc) rc = granite_cuda_sync(compute);
+    if (rc) {
+        if (c) granite_cuda_free(compute, c);
+        if (s) granite_cuda_free(compute, s);
+        return cuda_error(rc);
+    }
+    d_cos_ = static_cast<float*>(c);
+    d_sin_ = static_cast<float*>(s);
+    owner_ = compute;
+    return {};
+}
+
+Result<void> RoPECache::apply(Tensor& q, Tensor& k, int start_pos, IComputeBackend* backend) {
+    if (!is_initialized()) return Error(ErrorCode::InvalidState, "RoPE cache not initialized");
+    if (!backend || backend->get_type() != BackendType::CUDA)
+        return Error(ErrorCode::BackendNotSupported, "RoPECache::apply needs the CUDA backend (no CPU fallback)");
+    const int seq_len = static_cast<int>(q.size(1));
+    const int num_heads_q = static_cast<int>(q.size(2)), num_heads_k = static_cast<int>(k.size(2));
+    if (start_pos < 0 || start_pos + seq_len > max_seq_len_)
+        return Error(ErrorCode::InvalidArgument, "RoPE position out of range: " + std::to_string(start_pos) + " + " +
+                                                     std::to_string(seq_len) + " > " + std::to_string(max_seq_len_));
+    auto* compute = static_cast<granite_cuda_compute_t*>(backend->get_native_device());
+    auto up = upload(compute);
+    if (!up.ok()) return up;
+    int rc = granite_cuda_rope_multihead(compute, static_cast<float*>(backend->get_native_buffer(q.buffer())),
+                                         static_cast<float*>(backend->get_native_buffer(k.buffer())), num_heads_q,
+                                         num_heads_k, seq_len, head_dim_, start_pos, d_cos_, d_sin_, max_seq_len_);
+    if (!rc) rc = granite_cuda_sync(compute);
+    return cuda_result(rc);
+}
+
 CudaCompute* get_cuda_compute(int device) {
     // one lazily created object per device (the reference keeps one global MetalCompute,
     // src/backend/metal/metal_compute.mm:2721-2745)
@@ -719,6 +809,173 @@ std::vector<int32_t> SpeculationTree::find_accepted_path(const std::vector<int32
     };
     dfs(0, 0);
     return best;
+}
+
+std::vector<int> SpeculationTree::find_accepted_nodes(const std::vector<int32_t>& target_choices) const {
+    if (nodes_.empty() || target_choices.empty()) return {};
+    // the same walk as find_accepted_path, recording nodes; the path that wins there is the one
+    // with the most tokens, and the closing token of a mismatch counts as a token but has no node
+    std::vector<int> best_nodes, cur;
+    size_t best_tokens = 0;
+    std::function<void(int, int)> dfs = [&](int node_idx, int pos) {
+        if (node_idx < 0 || pos >= static_cast<int>(target_choices.size())) {
+            if (cur.size() > best_tokens) {
+                best_tokens = cur.size();
+                best_nodes = cur;
+            }
+            return;
+        }
+        const Node& n = nodes_[node_idx];
+        if (n.token == target_choices[pos]) {
+            cur.push_back(node_idx);
+            if (n.children.empty()) {
+                if (cur.size() > best_tokens) {
+                    best_tokens = cur.size();
+                    best_nodes = cur;
+                }
+            } else {
+                for (int child : n.children) dfs(child, pos + 1);
+            }
+            cur.pop_back();
+        } else if (cur.size() + 1 > best_tokens) {
+            best_tokens = cur.size() + 1;
+            best_nodes = cur;
+        }
+    };
+    dfs(0, 0);
+    return best_nodes;
+}
+
+// =================================================================== PagedDecodeBatch
+PagedDecodeBatch::~PagedDecodeBatch() {
+    if (compute_ && compute_->is_initialized()) {
+        if (d_tables_) compute_->destroy_buffer(d_tables_);
+        if (d_lens_) compute_->destroy_buffer(d_lens_);
+        if (d_positions_) compute_->destroy_buffer(d_positions_);
+    }
+    if (h_staging_) granite_cuda_free_host(h_staging_);
+}
+
+Result<void> PagedDecodeBatch::initialize(PagedKVPool* pool, CudaCompute* compute, RoPECache* rope,
+                                          const ModelConfig& config, int max_batch, int max_blocks_per_seq) {
+    if (!pool || !compute || !rope) return Error(ErrorCode::NullPointer, "PagedDecodeBatch: null argument");
+    if (!pool->is_initialized() || !compute->is_initialized() || !rope->is_initialized())
+        return Error(ErrorCode::InvalidState, "PagedDecodeBatch: pool, compute object and RoPE tables must be initialized");
+    if (max_batch <= 0 || max_blocks_per_seq <= 0) return Error(ErrorCode::InvalidArgument, "PagedDecodeBatch: empty batch shape");
+    pool_ = pool;
+    compute_ = compute;
+    rope_ = rope;
+    config_ = config;
+    max_batch_ = max_batch;
+    max_blocks_ = max_blocks_per_seq;
+    auto up = rope->upload(compute->handle());
+    if (!up.ok()) return up;
+    d_tables_ = static_cast<int32_t*>(compute->create_buffer(static_cast<size_t>(max_batch) * max_blocks_per_seq * 4));
+    d_lens_ = static_cast<int32_t*>(compute->create_buffer(static_cast<size_t>(max_batch) * 4));
+    d_positions_ = static_cast<int32_t*>(compute->create_buffer(static_cast<size_t>(max_batch) * 4));
+    void* host = nullptr;
+    const size_t staging = (static_cast<size_t>(max_batch) * 2 + static_cast<size_t>(max_batch) * max_blocks_per_seq) * 4;
+    if (!d_tables_ || !d_lens_ || !d_positions_ || granite_cuda_malloc_host(staging, &host) != 0)
+        return Error(ErrorCode::OutOfMemory, "PagedDecodeBatch: allocation failed");
+    h_staging_ = static_cast<int32_t*>(host);
+    int rc = granite_cuda_memset(compute->handle(), d_tables_, 0, static_cast<size_t>(max_batch) * max_blocks_per_seq * 4);
+    return cuda_result(rc);
+}
+
+int PagedDecodeBatch::add_request(int slot) {
+    if (batch_size() >= max_batch_ || slot < 0 || slot >= pool_->num_slots()) return -1;
+    if (std::find(slots_.begin(), slots_.end(), slot) != slots_.end()) return -1;
+    slots_.push_back(slot);
+    synced_blocks_.push_back(0);  // the whole row goes up at the next step
+    return batch_size() - 1;
+}
+
+void PagedDecodeBatch::remove_request(int slot) {
+    auto it = std::find(slots_.begin(), slots_.end(), slot);
+    if (it == slots_.end()) return;
+    const size_t row = static_cast<size_t>(it - slots_.begin());
+    // keep the rows dense: the last row moves into the hole and is re-sent whole
+    slots_[row] = slots_.back();
+    synced_blocks_[row] = 0;
+    slots_.pop_back();
+    synced_blocks_.pop_back();
+}
+
+Result<std::vector<int>> PagedDecodeBatch::begin_step() {
+    if (!pool_) return Error(ErrorCode::InvalidState, "PagedDecodeBatch not initialized");
+    std::vector<int> failed;
+    for (size_t row = 0; row < slots_.size();) {
+        auto& cache = pool_->get_cache(slots_[row]);
+        if (cache.seq_len() + 1 > rope_->max_seq_len() || (cache.seq_len() / pool_->block_manager().block_size()) >= max_blocks_ ||
+            !cache.append_tokens(1)) {
+            failed.push_back(slots_[row]);
+            remove_request(slots_[row]);  // the row now holds another request (or none): do not advance
+            continue;
+        }
+        row++;
+    }
+    const int n = batch_size();
+    if (n == 0) return failed;
+    // the previous step's copies out of the pinned staging area must have left it
+    auto sr = compute_->sync_checked();
+    if (!sr.ok()) return sr.error();
+    int32_t* positions = h_staging_;
+    int32_t* lens = h_staging_ + max_batch_;
+    int32_t* rows = h_staging_ + 2 * static_cast<size_t>(max_batch_);
+    int rc = 0;
+    for (int row = 0; row < n && !rc; row++) {
+        const auto& cache = pool_->get_cache(slots_[row]);
+        lens[row] = cache.seq_len();
+        positions[row] = cache.seq_len() - 1;
+        const int have = cache.num_blocks();
+        if (have > max_blocks_) return Error(ErrorCode::BufferTooSmall, "PagedDecodeBatch: block table wider than max_blocks_per_seq");
+        if (have > synced_blocks_[row]) {  // only the entries the device has not seen
+            int32_t* stage = rows + static_cast<size_t>(row) * max_blocks_;
+            const int first = synced_blocks_[row];
+            std::copy(cache.block_table().begin() + first, cache.block_table().end(), stage + first);
+            rc = granite_cuda_write_buffer(compute_->handle(), d_tables_ + static_cast<size_t>(row) * max_blocks_ + first,
+                                           stage + first, static_cast<size_t>(have - first) * 4);
+            synced_blocks_[row] = have;
+        }
+    }
+    if (!rc) rc = granite_cuda_write_buffer(compute_->handle(), d_positions_, positions, static_cast<size_t>(n) * 4);
+    if (!rc) rc = granite_cuda_write_buffer(compute_->handle(), d_lens_, lens, static_cast<size_t>(n) * 4);
+    if (rc) return cuda_error(rc);
+    return failed;
+}
+
+Result<void> PagedDecodeBatch::attend(int layer, float* q, const float* k, const float* v, float* out, float scale) {
+    if (!pool_) return Error(ErrorCode::InvalidState, "PagedDecodeBatch not initialized");
+    const int n = batch_size();
+    if (n == 0) return {};
+    auto& bm = pool_->block_manager();
+    if (layer < 0 || layer >= bm.config().num_layers) return Error(ErrorCode::InvalidArgument, "PagedDecodeBatch: bad layer");
+    void* backend_k = bm.k_cache(layer).backend()->get_native_buffer(bm.k_cache(layer).buffer());
+    void* backend_v = bm.v_cache(layer).backend()->get_native_buffer(bm.v_cache(layer).buffer());
+    GraniteCudaRopeAppendArgs a{};
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.cos_table = rope_->device_cos();
+    a.sin_table = rope_->device_sin();
+    a.k_cache = backend_k;
+    a.v_cache = backend_v;
+    a.block_tables = d_tables_;
+    a.positions = d_positions_;
+    a.batch_size = static_cast<uint32_t>(n);
+    a.new_len = 1;
+    a.num_heads = static_cast<uint32_t>(config_.num_heads);
+    a.num_kv_heads = static_cast<uint32_t>(config_.num_kv_heads);
+    a.head_dim = static_cast<uint32_t>(config_.head_dim);
+    a.block_size = static_cast<uint32_t>(bm.block_size());
+    a.max_blocks_per_seq = static_cast<uint32_t>(max_blocks_);
+    a.num_blocks = static_cast<uint32_t>(bm.num_total_blocks());
+    a.table_len = static_cast<uint32_t>(rope_->max_seq_len());
+    auto r = compute_->rope_paged_kv_cache_append(a);
+    if (!r.ok()) return r;
+    return compute_->batched_paged_attention_decode(q, backend_k, backend_v, d_tables_, d_lens_, out, a.batch_size,
+                                                    a.num_heads, a.num_kv_heads, a.head_dim, a.block_size,
+                                                    a.max_blocks_per_seq, scale, a.num_blocks);
 }
 
 }  // namespace granite

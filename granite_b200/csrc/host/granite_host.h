@@ -271,10 +271,47 @@ public:
                                                 float* output, uint32_t batch_size, uint32_t num_heads,
                                                 uint32_t num_kv_heads, uint32_t head_dim, uint32_t block_size,
                                                 uint32_t max_blocks_per_seq, float scale, uint32_t num_blocks);
+    // The step before attention and the ones after verification (the "next" tier of the path):
+    // RoPE with host-built tables, RoPE fused with the paged cache write, the tree commit copy and
+    // chunked prefill over the paged cache.  Argument meaning as in granite_cuda.h.
+    Result<void> rope_multihead(float* q, float* k, uint32_t num_heads_q, uint32_t num_heads_k, uint32_t seq_len,
+                                uint32_t head_dim, uint32_t start_pos, const float* cos_table, const float* sin_table,
+                                uint32_t table_len);
+    Result<void> rope_paged_kv_cache_append(const GraniteCudaRopeAppendArgs& args);
+    Result<void> tree_commit(const GraniteCudaTreeCommitArgs& args);
+    Result<void> paged_prefill_attention(const GraniteCudaPagedPrefillArgs& args);
 private:
     granite_cuda_compute_t* h_ = nullptr;
 };
 CudaCompute* get_cuda_compute(int device = 0);
+
+// ------------------------------------------------------------------ RoPE tables (llm.h:173-197)
+class RoPECache {
+public:
+    RoPECache() = default;
+    ~RoPECache();
+    RoPECache(const RoPECache&) = delete;
+    RoPECache& operator=(const RoPECache&) = delete;
+    // cos/sin [max_seq_len, head_dim/2] on the host, in the reference's float arithmetic (src/llm/rope.cpp:5-22)
+    void initialize(int max_seq_len, int head_dim, float theta = 10000.0f);
+    // q [batch, seq_len, num_heads, head_dim], k [batch, seq_len, num_kv_heads, head_dim] fp32 device
+    // tensors of the CUDA backend, rotated in place (src/llm/rope.cpp:24-92; batch 1 as there)
+    Result<void> apply(Tensor& q, Tensor& k, int start_pos, IComputeBackend* backend);
+    const std::vector<float>& cos_cache() const { return cos_; }
+    const std::vector<float>& sin_cache() const { return sin_; }
+    bool is_initialized() const { return !cos_.empty(); }
+    int max_seq_len() const { return max_seq_len_; }
+    int head_dim() const { return head_dim_; }
+    // device copies of the tables, uploaded on first use through `compute`
+    Result<void> upload(granite_cuda_compute_t* compute);
+    const float* device_cos() const { return d_cos_; }
+    const float* device_sin() const { return d_sin_; }
+private:
+    std::vector<float> cos_, sin_;
+    int max_seq_len_ = 0, head_dim_ = 0;
+    float *d_cos_ = nullptr, *d_sin_ = nullptr;
+    granite_cuda_compute_t* owner_ = nullptr;
+};
 
 // ------------------------------------------------------------------ KV caches (llm.h:117-167, 888-1035)
 struct ModelConfig {
@@ -397,8 +434,48 @@ public:
     int max_depth() const;
     void clear() { nodes_.clear(); }
     std::vector<int32_t> find_accepted_path(const std::vector<int32_t>& target_choices) const;
+    // The node indices behind find_accepted_path's tokens, root first (the target's own closing
+    // token has no node): what the tree commit copies into the cache.
+    std::vector<int> find_accepted_nodes(const std::vector<int32_t>& target_choices) const;
 private:
     std::vector<Node> nodes_;
+};
+
+// ------------------------------------------------------------------ batched paged decode step
+// One decode step for every active request in one set of launches: what
+// BatchScheduler::process_batch_paged (src/llm/batch_scheduler.cpp:391-452) leaves as a TODO after
+// it has grown each request's PagedKVCache by one token.  Block tables, lengths and positions of
+// the batch live on the device; a step copies the two length arrays and only the table rows that
+// gained a block.
+class PagedDecodeBatch {
+public:
+    ~PagedDecodeBatch();
+    Result<void> initialize(PagedKVPool* pool, CudaCompute* compute, RoPECache* rope, const ModelConfig& config,
+                            int max_batch, int max_blocks_per_seq);
+    // rows of the batch are kept dense; returns the row, or -1 when full / already present
+    int add_request(int slot);
+    void remove_request(int slot);
+    int batch_size() const { return static_cast<int>(slots_.size()); }
+    const std::vector<int>& slots() const { return slots_; }
+    // Grows every active sequence by one token (PagedKVCache::append_tokens(1)) and brings the
+    // device arrays up to date.  Slots whose allocation failed are removed from the batch and
+    // returned (the reference marks such a request FAILED, batch_scheduler.cpp:431-435).
+    Result<std::vector<int>> begin_step();
+    // One layer of the step: q [B, Hq, D] (rotated in place), k, v [B, Hkv, D] fp32 -> the new
+    // token's K/V into `layer`'s pools, attention output [B, Hq, D] fp32.  Asynchronous.
+    Result<void> attend(int layer, float* q, const float* k, const float* v, float* out, float scale);
+    const int32_t* device_tables() const { return d_tables_; }
+    const int32_t* device_seq_lens() const { return d_lens_; }
+private:
+    PagedKVPool* pool_ = nullptr;
+    CudaCompute* compute_ = nullptr;
+    RoPECache* rope_ = nullptr;
+    ModelConfig config_;
+    int max_batch_ = 0, max_blocks_ = 0;
+    std::vector<int> slots_;            // row -> slot
+    std::vector<int> synced_blocks_;    // row -> table entries already on the device
+    int32_t *d_tables_ = nullptr, *d_lens_ = nullptr, *d_positions_ = nullptr;
+    int32_t* h_staging_ = nullptr;      // pinned: [max_batch] positions, [max_batch] lengths, [max_batch, max_blocks] rows
 };
 
 }  // namespace granite

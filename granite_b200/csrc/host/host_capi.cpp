@@ -345,4 +345,191 @@ int granite_host_paged_flow(int device, int batch, const int32_t* lens, int num_
     return 0;
 }
 
+// SpeculationTree::find_accepted_nodes on a tree built from (token, parent) pairs.
+int granite_host_find_accepted_nodes(const int32_t* parents, const int32_t* tokens, int n, const int32_t* targets,
+                                     int n_targets, int32_t* out, int32_t* n_out) {
+    SpeculationTree tree;
+    for (int i = 0; i < n; i++) tree.add_node(tokens[i], parents[i]);
+    auto nodes = tree.find_accepted_nodes(std::vector<int32_t>(targets, targets + n_targets));
+    *n_out = static_cast<int32_t>(nodes.size());
+    for (size_t i = 0; i < nodes.size(); i++) out[i] = nodes[i];
+    return 0;
+}
+
+// RoPECache::initialize on the host (runs anywhere): the tables [max_seq, head_dim/2].
+int granite_host_rope_table(int max_seq, int head_dim, float theta, float* cos_out, float* sin_out) {
+    RoPECache rope;
+    rope.initialize(max_seq, head_dim, theta);
+    std::memcpy(cos_out, rope.cos_cache().data(), rope.cos_cache().size() * sizeof(float));
+    std::memcpy(sin_out, rope.sin_cache().data(), rope.sin_cache().size() * sizeof(float));
+    return rope.is_initialized() ? 0 : 1;
+}
+
+// RoPECache::apply through the CUDA backend's tensors: q [1, seq, Hq, D], k [1, seq, Hk, D] in place.
+int granite_host_rope_apply(int device, float* q, float* k, int seq_len, int num_heads_q, int num_heads_k,
+                            int head_dim, int start_pos, int max_seq, float theta) {
+    auto be = create_cuda_backend(device);
+    auto init = be->initialize();
+    if (!init.ok()) return host_fail(init.error());
+    RoPECache rope;
+    Tensor none_q, none_k;
+    if (rope.apply(none_q, none_k, 0, be.get()).ok()) return 5001;  // not initialized yet: InvalidState
+    rope.initialize(max_seq, head_dim, theta);
+    auto qt = Tensor::allocate({1, seq_len, num_heads_q, head_dim}, DataType::FP32, be.get());
+    auto kt = Tensor::allocate({1, seq_len, num_heads_k, head_dim}, DataType::FP32, be.get());
+    if (!qt.ok() || !kt.ok()) return 5002;
+    Tensor tq = std::move(qt).take(), tk = std::move(kt).take();
+    if (!be->write_buffer(tq.buffer(), q, tq.size_bytes()).ok()) return 5003;
+    if (!be->write_buffer(tk.buffer(), k, tk.size_bytes()).ok()) return 5003;
+    auto r = rope.apply(tq, tk, start_pos, be.get());
+    int rc = 0;
+    if (!r.ok()) {
+        rc = host_fail(r.error());
+    } else {
+        if (!be->read_buffer(tq.buffer(), q, tq.size_bytes()).ok()) rc = 5004;
+        if (!be->read_buffer(tk.buffer(), k, tk.size_bytes()).ok()) rc = 5004;
+    }
+    be->destroy_buffer(tq.buffer());
+    be->destroy_buffer(tk.buffer());
+    return rc;
+}
+
+// A serving loop in miniature over PagedKVPool + RoPECache + PagedDecodeBatch: `batch` requests
+// (slot i = request i) are prefilled with lens0[i] prompt tokens, then decode together for
+// n_steps steps; request `remove_slot` leaves before step `remove_at` (its pages go back to the
+// pool and are handed out again).  Per step and slot the driver returns the attention output,
+// the rotated query, the block table and the length, and at the end both pools, so that the
+// caller can replay the whole run on the CPU checker.  Inputs per step are indexed by slot.
+int granite_host_decode_batch_flow(int device, int batch, const int32_t* lens0, int n_steps, int remove_slot,
+                                   int remove_at, int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                   int num_blocks, int max_blocks, int max_seq, const float* prompt_k,
+                                   const float* prompt_v, const float* step_q, const float* step_k,
+                                   const float* step_v, float* out, float* q_rot_out, int32_t* tables_out,
+                                   int32_t* lens_out, uint16_t* k_pool_out, uint16_t* v_pool_out) {
+    auto be = create_cuda_backend(device);
+    auto init = be->initialize();
+    if (!init.ok()) return host_fail(init.error());
+    CudaCompute compute;
+    auto ci = compute.initialize(device, be->get_native_queue());
+    if (!ci.ok()) return host_fail(ci.error());
+    ModelConfig cfg;
+    cfg.num_layers = 1;
+    cfg.num_heads = num_heads;
+    cfg.num_kv_heads = num_kv_heads;
+    cfg.head_dim = head_dim;
+    PagedKVPool pool;
+    auto pr = pool.initialize(cfg, batch, num_blocks * block_size, block_size, be.get());
+    if (!pr.ok()) return host_fail(pr.error());
+    void* kpool = be->get_native_buffer(pool.block_manager().k_cache(0).buffer());
+    void* vpool = be->get_native_buffer(pool.block_manager().v_cache(0).buffer());
+    const size_t pool_bytes = pool.block_manager().k_cache(0).size_bytes();
+    granite_cuda_memset(compute.handle(), kpool, 0, pool_bytes);
+    granite_cuda_memset(compute.handle(), vpool, 0, pool_bytes);
+    RoPECache rope;
+    rope.initialize(max_seq, head_dim);
+    auto up = rope.upload(compute.handle());
+    if (!up.ok()) return host_fail(up.error());
+
+    const size_t q_row = static_cast<size_t>(num_heads) * head_dim, kv_row = static_cast<size_t>(num_kv_heads) * head_dim;
+    auto* d_q = static_cast<float*>(compute.create_buffer(batch * q_row * 4));
+    auto* d_out = static_cast<float*>(compute.create_buffer(batch * q_row * 4));
+    auto* d_table = static_cast<int32_t*>(compute.create_buffer(static_cast<size_t>(max_blocks) * 4));
+
+    // prefill: each prompt's K/V goes through the fused RoPE + paged write, one sequence per call
+    size_t off = 0;
+    for (int b = 0; b < batch; b++) {
+        if (pool.acquire_slot() != b) return 6001;
+        auto& cache = pool.get_cache(b);
+        if (lens0[b] == 0) continue;
+        if (!cache.append_tokens(lens0[b])) return static_cast<int>(ErrorCode::OutOfMemory);
+        auto* d_k = static_cast<float*>(compute.create_buffer(lens0[b] * kv_row * 4));
+        auto* d_v = static_cast<float*>(compute.create_buffer(lens0[b] * kv_row * 4));
+        granite_cuda_write_buffer(compute.handle(), d_k, prompt_k + off * kv_row, lens0[b] * kv_row * 4);
+        granite_cuda_write_buffer(compute.handle(), d_v, prompt_v + off * kv_row, lens0[b] * kv_row * 4);
+        granite_cuda_write_buffer(compute.handle(), d_table, cache.block_table().data(), cache.block_table().size() * 4);
+        GraniteCudaRopeAppendArgs a{};
+        a.k = d_k;
+        a.v = d_v;
+        a.cos_table = rope.device_cos();
+        a.sin_table = rope.device_sin();
+        a.k_cache = kpool;
+        a.v_cache = vpool;
+        a.block_tables = d_table;
+        a.batch_size = 1;
+        a.new_len = static_cast<uint32_t>(lens0[b]);
+        a.num_kv_heads = static_cast<uint32_t>(num_kv_heads);
+        a.head_dim = static_cast<uint32_t>(head_dim);
+        a.block_size = static_cast<uint32_t>(block_size);
+        a.max_blocks_per_seq = static_cast<uint32_t>(cache.block_table().size());
+        a.num_blocks = static_cast<uint32_t>(pool.block_manager().num_total_blocks());
+        a.table_len = static_cast<uint32_t>(max_seq);
+        a.start_pos = 0;
+        auto ar = compute.rope_paged_kv_cache_append(a);
+        if (!ar.ok()) return host_fail(ar.error());
+        auto sr = compute.sync_checked();
+        if (!sr.ok()) return host_fail(sr.error());
+        compute.destroy_buffer(d_k);
+        compute.destroy_buffer(d_v);
+        off += lens0[b];
+    }
+
+    PagedDecodeBatch decode;
+    auto di = decode.initialize(&pool, &compute, &rope, cfg, batch, max_blocks);
+    if (!di.ok()) return host_fail(di.error());
+    for (int b = 0; b < batch; b++)
+        if (decode.add_request(b) != b) return 6002;
+    if (decode.add_request(0) != -1) return 6003;  // already present
+
+    std::vector<float> q_rows(batch * q_row), k_rows(batch * kv_row), v_rows(batch * kv_row), o_rows(batch * q_row);
+    auto* d_k1 = static_cast<float*>(compute.create_buffer(batch * kv_row * 4));
+    auto* d_v1 = static_cast<float*>(compute.create_buffer(batch * kv_row * 4));
+    const float scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+    for (int step = 0; step < n_steps; step++) {
+        if (step == remove_at && remove_slot >= 0) {
+            decode.remove_request(remove_slot);
+            pool.release_slot(remove_slot);
+        }
+        auto bs = decode.begin_step();
+        if (!bs.ok()) return host_fail(bs.error());
+        if (!bs.value().empty()) return static_cast<int>(ErrorCode::OutOfMemory);
+        const int n = decode.batch_size();
+        const auto& slots = decode.slots();
+        for (int row = 0; row < n; row++) {
+            const size_t src = static_cast<size_t>(step) * batch + slots[row];
+            std::memcpy(&q_rows[row * q_row], step_q + src * q_row, q_row * 4);
+            std::memcpy(&k_rows[row * kv_row], step_k + src * kv_row, kv_row * 4);
+            std::memcpy(&v_rows[row * kv_row], step_v + src * kv_row, kv_row * 4);
+        }
+        granite_cuda_write_buffer(compute.handle(), d_q, q_rows.data(), n * q_row * 4);
+        granite_cuda_write_buffer(compute.handle(), d_k1, k_rows.data(), n * kv_row * 4);
+        granite_cuda_write_buffer(compute.handle(), d_v1, v_rows.data(), n * kv_row * 4);
+        auto at = decode.attend(0, d_q, d_k1, d_v1, d_out, scale);
+        if (!at.ok()) return host_fail(at.error());
+        granite_cuda_read_buffer(compute.handle(), o_rows.data(), d_out, n * q_row * 4);
+        granite_cuda_read_buffer(compute.handle(), q_rows.data(), d_q, n * q_row * 4);
+        auto sr = compute.sync_checked();
+        if (!sr.ok()) return host_fail(sr.error());
+        for (int b = 0; b < batch; b++) {
+            lens_out[static_cast<size_t>(step) * batch + b] = -1;
+            for (int j = 0; j < max_blocks; j++) tables_out[(static_cast<size_t>(step) * batch + b) * max_blocks + j] = -1;
+        }
+        for (int row = 0; row < n; row++) {
+            const size_t dst = static_cast<size_t>(step) * batch + slots[row];
+            std::memcpy(out + dst * q_row, &o_rows[row * q_row], q_row * 4);
+            std::memcpy(q_rot_out + dst * q_row, &q_rows[row * q_row], q_row * 4);
+            const auto& cache = pool.get_cache(slots[row]);
+            lens_out[dst] = cache.seq_len();
+            std::copy(cache.block_table().begin(), cache.block_table().end(), tables_out + dst * max_blocks);
+        }
+    }
+    granite_cuda_read_buffer(compute.handle(), k_pool_out, kpool, pool_bytes);
+    granite_cuda_read_buffer(compute.handle(), v_pool_out, vpool, pool_bytes);
+    auto fin = compute.sync_checked();
+    if (!fin.ok()) return host_fail(fin.error());
+    for (void* p : {static_cast<void*>(d_q), static_cast<void*>(d_out), static_cast<void*>(d_table),
+                    static_cast<void*>(d_k1), static_cast<void*>(d_v1)})
+        compute.destroy_buffer(p);
+    return 0;
+}
+
 }  // extern "C"

@@ -304,6 +304,113 @@ int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTree
 int granite_cuda_build_tree_mask(granite_cuda_compute_t* c, const int32_t* parent_indices,
                                  uint64_t* masks, uint32_t batch_size, uint32_t num_nodes);
 
+/* ---- RoPE and the fused RoPE + paged cache write ---------------------------------------------
+ * The step immediately before attention (src/llm/transformer.mm:2975-2986: rope_multihead, then
+ * paged_kv_cache_append, then the attention kernel).  The rotation follows the CPU path the
+ * results are judged against: RoPECache (src/llm/rope.cpp:5-92) - cos/sin tables
+ * [table_len, head_dim/2] built once on the host with the reference's own float formula,
+ * adjacent pairs (2i, 2i+1), both products rounded separately - so rotated values are
+ * bit-identical to Granite's CPU arithmetic.  (MetalCompute::rope_multihead,
+ * include/granite/metal_compute.h:730-739, recomputes cos/sin per element on the device instead;
+ * it takes freq_base where these calls take the tables.) */
+
+/* Builds the tables on the host (rope.cpp:5-22) and uploads them; the two device arrays are
+ * released with granite_cuda_free. */
+int granite_cuda_rope_table_create(granite_cuda_compute_t* c, uint32_t max_seq_len, uint32_t head_dim,
+                                   float theta, float** cos_table, float** sin_table);
+
+/* MetalCompute::rope_multihead: q [seq_len, num_heads_q, head_dim] and k [seq_len, num_heads_k,
+ * head_dim] fp32, rotated in place for positions start_pos .. start_pos + seq_len - 1
+ * (kernel indexing of metal_shaders_util.h:596-635).  k may be NULL. */
+int granite_cuda_rope_multihead(granite_cuda_compute_t* c, float* q, float* k, uint32_t num_heads_q,
+                                uint32_t num_heads_k, uint32_t seq_len, uint32_t head_dim,
+                                uint32_t start_pos, const float* cos_table, const float* sin_table,
+                                uint32_t table_len);
+
+/* One launch for rope_multihead + paged_kv_cache_append of a batch of sequences: q is rotated in
+ * place; k is rotated, narrowed with the truncating cast (src/llm/math_ops.cpp:45-54) and
+ * stored, v is narrowed and stored, at positions positions[b] .. positions[b] + new_len - 1 of
+ * sequence b through row b of block_tables (addressing rule metal_compute.h:853-861).  k and v
+ * are not modified.  A position outside the RoPE table or the block table, or a table entry
+ * outside the pool, skips that token and is reported by granite_cuda_sync as InvalidArgument. */
+typedef struct {
+    float* q;                    /* [batch_size, new_len, num_heads, head_dim] fp32 or NULL */
+    const float* k;              /* [batch_size, new_len, num_kv_heads, head_dim] fp32 */
+    const float* v;
+    const float* cos_table;      /* [table_len, head_dim/2] */
+    const float* sin_table;
+    void* k_cache;               /* pool [num_blocks*block_size, num_kv_heads, head_dim] fp16 */
+    void* v_cache;
+    const int32_t* block_tables; /* device [batch_size, max_blocks_per_seq] */
+    const int32_t* positions;    /* device [batch_size] first new position per sequence; NULL: start_pos */
+    uint32_t batch_size;
+    uint32_t new_len;
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t block_size;
+    uint32_t max_blocks_per_seq;
+    uint32_t num_blocks;
+    uint32_t table_len;
+    uint32_t start_pos;
+} GraniteCudaRopeAppendArgs;
+
+int granite_cuda_rope_paged_kv_cache_append(granite_cuda_compute_t* c, const GraniteCudaRopeAppendArgs* args);
+
+/* ---- tree commit ---------------------------------------------------------------------------------
+ * After verification the accepted path's K/V rows are kept instead of being recomputed: row
+ * accepted[b][j] of the tree K/V of sequence b is copied to position cache_lens[b] + j of its
+ * paged cache, j < num_accepted[b]; the host then truncates the sequence to that length
+ * (the reference truncates the contiguous cache after verification,
+ * src/llm/speculative_runner.cpp:871-882).  Pure byte moves: bit-exact. */
+typedef struct {
+    const void* k_tree;          /* [batch_size, num_kv_heads, num_nodes, head_dim] fp16 */
+    const void* v_tree;
+    void* k_cache;               /* pool */
+    void* v_cache;
+    const int32_t* block_tables; /* device [batch_size, max_blocks_per_seq] */
+    const int32_t* cache_lens;   /* device [batch_size] committed length before the tree */
+    const int32_t* accepted;     /* device [batch_size, max_accepted] node indices, root first */
+    const int32_t* num_accepted; /* device [batch_size] */
+    uint32_t batch_size;
+    uint32_t num_nodes;
+    uint32_t max_accepted;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t block_size;
+    uint32_t max_blocks_per_seq;
+    uint32_t num_blocks;
+} GraniteCudaTreeCommitArgs;
+
+int granite_cuda_tree_commit(granite_cuda_compute_t* c, const GraniteCudaTreeCommitArgs* args);
+
+/* ---- chunked prefill over the paged cache --------------------------------------------------------
+ * Causal attention of a chunk of seq_q new tokens at positions start_pos .. start_pos + seq_q - 1
+ * against the sequence's paged cache, which already holds those tokens' K/V (the start_pos =
+ * chunk_start form of forward_prefill_raw, src/llm/transformer.mm:3467-3476, :3682-3692, with
+ * K/V read through the block table instead of a contiguous cache).  Same arithmetic and
+ * dtypes as granite_cuda_multihead_attention's prefill. */
+typedef struct {
+    const void* q;               /* [seq_q, num_heads, head_dim] */
+    const void* k_cache;         /* pool [num_blocks*block_size, num_kv_heads, head_dim] fp16 */
+    const void* v_cache;
+    const int32_t* block_table;  /* device [max_blocks_per_seq] of this sequence */
+    void* output;                /* [seq_q, num_heads, head_dim] */
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t seq_q;
+    uint32_t start_pos;
+    uint32_t head_dim;           /* 128 */
+    uint32_t block_size;         /* 16 */
+    uint32_t max_blocks_per_seq;
+    uint32_t num_blocks;
+    uint32_t q_dtype;            /* 0 fp32, 1 fp16 */
+    uint32_t out_dtype;
+    float scale;
+} GraniteCudaPagedPrefillArgs;
+
+int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const GraniteCudaPagedPrefillArgs* args);
+
 #ifdef __cplusplus
 }
 #endif

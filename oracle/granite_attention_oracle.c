@@ -388,3 +388,110 @@ void gro_sdpa_kt(const float* q, const float* kt, const float* v, float* out, in
     }
     free(scores);
 }
+
+/* ---- RoPE tables : src/llm/rope.cpp:5-22 -----------------------------------------------------
+ * cos/sin [max_seq, head_dim/2] in float arithmetic throughout: freq = 1 / pow(theta, 2i/head_dim),
+ * angle = pos * freq.  The reference calls the float overloads of std::pow / std::cos / std::sin. */
+void gro_rope_table(int max_seq, int head_dim, float theta, float* cos_out, float* sin_out) {
+    int half_dim = head_dim / 2;
+    for (int pos = 0; pos < max_seq; pos++)
+        for (int i = 0; i < half_dim; i++) {
+            float freq = 1.0f / powf(theta, (float)(2 * i) / head_dim);
+            float angle = (float)pos * freq;
+            cos_out[(size_t)pos * half_dim + i] = cosf(angle);
+            sin_out[(size_t)pos * half_dim + i] = sinf(angle);
+        }
+}
+
+/* ---- RoPE rotation : src/llm/rope.cpp:52-86 --------------------------------------------------
+ * x [seq_len, num_heads, head_dim] rotated in place: adjacent pairs (2i, 2i+1), position
+ * start_pos + s, products rounded separately (no fused multiply-add).  Returns -1 when a
+ * position falls outside the table (rope.cpp:34-38 rejects the call). */
+int gro_rope_apply(float* x, int seq_len, int num_heads, int head_dim, int start_pos,
+                   const float* cos_t, const float* sin_t, int table_len) {
+    int half_dim = head_dim / 2;
+    if (start_pos < 0 || start_pos + seq_len > table_len) return -1;
+    for (int s = 0; s < seq_len; s++) {
+        int pos = start_pos + s;
+        for (int h = 0; h < num_heads; h++) {
+            float* p = x + ((size_t)s * num_heads + h) * head_dim;
+            for (int i = 0; i < half_dim; i++) {
+                float c = cos_t[(size_t)pos * half_dim + i], sn = sin_t[(size_t)pos * half_dim + i];
+                float x0 = p[2 * i], x1 = p[2 * i + 1];
+                p[2 * i] = x0 * c - x1 * sn;
+                p[2 * i + 1] = x0 * sn + x1 * c;
+            }
+        }
+    }
+    return 0;
+}
+
+/* ---- RoPE + cache write of a batch of new tokens ----------------------------------------------
+ * The step before attention in the paged decode / prefill flow (src/llm/transformer.mm:2975-2986):
+ * rotate Q and K (rope.cpp:52-86), narrow K and V to fp16 with the truncating cast
+ * (transformer.mm:1681-1691 -> math_ops.cpp:45-54) and store them at the new positions through
+ * the block table (metal_compute.h:853-861).  q [batch, new_len, Hq, D] is rotated in place;
+ * k, v [batch, new_len, Hkv, D] are left untouched; sequence b's tokens take positions
+ * positions[b] .. positions[b] + new_len - 1.  Returns the number of tokens that could not be
+ * written (position outside the RoPE table, table entry outside the pool). */
+int gro_rope_paged_append(float* q, const float* k, const float* v, const float* cos_t,
+                          const float* sin_t, int table_len, uint16_t* k_pool, uint16_t* v_pool,
+                          const int32_t* block_tables, const int32_t* positions, int batch,
+                          int new_len, int num_heads, int num_kv_heads, int head_dim,
+                          int block_size, int max_blocks, int num_blocks) {
+    int bad = 0;
+    size_t krow = (size_t)num_kv_heads * head_dim;
+    float* kr = (float*)malloc(krow * sizeof(float));
+    for (int b = 0; b < batch; b++)
+        for (int s = 0; s < new_len; s++) {
+            int pos = positions[b] + s;
+            size_t row = (size_t)b * new_len + s;
+            int logical = pos / block_size;
+            if (pos < 0 || pos >= table_len || logical >= max_blocks) { bad++; continue; }
+            int32_t phys = block_tables[(size_t)b * max_blocks + logical];
+            if (phys < 0 || phys >= num_blocks) { bad++; continue; }
+            if (q) gro_rope_apply(q + row * num_heads * head_dim, 1, num_heads, head_dim, pos, cos_t, sin_t, table_len);
+            memcpy(kr, k + row * krow, krow * sizeof(float));
+            gro_rope_apply(kr, 1, num_kv_heads, head_dim, pos, cos_t, sin_t, table_len);
+            size_t dst = ((size_t)phys * block_size + pos % block_size) * krow;
+            for (size_t i = 0; i < krow; i++) {
+                k_pool[dst + i] = gro_fp32_to_fp16(kr[i]);
+                v_pool[dst + i] = gro_fp32_to_fp16(v[row * krow + i]);
+            }
+        }
+    free(kr);
+    return bad;
+}
+
+/* ---- tree commit ---------------------------------------------------------------------------------
+ * Keeps the accepted path of a verified tree: row accepted[b][j] of tree K/V
+ * [batch, Hkv, num_nodes, D] (fp16 bits) goes to position cache_lens[b] + j of sequence b's paged
+ * cache (addressing rule metal_compute.h:853-861); the caller then truncates the sequence to
+ * cache_lens[b] + num_accepted[b] as src/llm/speculative_runner.cpp:871-882 does for the
+ * contiguous cache.  Returns the number of rows that could not be written. */
+int gro_tree_commit(const uint16_t* k_tree, const uint16_t* v_tree, uint16_t* k_pool,
+                    uint16_t* v_pool, const int32_t* block_tables, const int32_t* cache_lens,
+                    const int32_t* accepted, const int32_t* num_accepted, int batch, int num_nodes,
+                    int max_accepted, int num_kv_heads, int head_dim, int block_size,
+                    int max_blocks, int num_blocks) {
+    int bad = 0;
+    for (int b = 0; b < batch; b++) {
+        int n_acc = num_accepted[b];
+        if (n_acc < 0 || n_acc > max_accepted) { bad++; continue; }
+        for (int j = 0; j < n_acc; j++) {
+            int node = accepted[(size_t)b * max_accepted + j];
+            int pos = cache_lens[b] + j;
+            int logical = pos / block_size;
+            if (node < 0 || node >= num_nodes || pos < 0 || logical >= max_blocks) { bad++; continue; }
+            int32_t phys = block_tables[(size_t)b * max_blocks + logical];
+            if (phys < 0 || phys >= num_blocks) { bad++; continue; }
+            for (int h = 0; h < num_kv_heads; h++) {
+                size_t src = (((size_t)b * num_kv_heads + h) * num_nodes + node) * head_dim;
+                size_t dst = (((size_t)phys * block_size + pos % block_size) * num_kv_heads + h) * head_dim;
+                memcpy(k_pool + dst, k_tree + src, (size_t)head_dim * 2);
+                memcpy(v_pool + dst, v_tree + src, (size_t)head_dim * 2);
+            }
+        }
+    }
+    return bad;
+}

@@ -54,6 +54,13 @@ _lib.gro_attention_tree.argtypes = [_f32p] * 5 + [_u8p, _f32p] + [C.c_int] * 6 +
 _lib.gro_paged_decode_batch.restype = C.c_int
 _lib.gro_paged_decode_batch.argtypes = [_f32p, _u16p, _u16p, _i32p, _i32p, _f32p] + [C.c_int] * 7 + [C.c_float, C.c_int, C.c_int]
 _lib.gro_sdpa_kt.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+_lib.gro_rope_table.argtypes = [C.c_int, C.c_int, C.c_float, _f32p, _f32p]
+_lib.gro_rope_apply.restype = C.c_int
+_lib.gro_rope_apply.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_int]
+_lib.gro_rope_paged_append.restype = C.c_int
+_lib.gro_rope_paged_append.argtypes = [C.c_void_p, _f32p, _f32p, _f32p, _f32p, C.c_int, _u16p, _u16p, _i32p, _i32p] + [C.c_int] * 8
+_lib.gro_tree_commit.restype = C.c_int
+_lib.gro_tree_commit.argtypes = [_u16p, _u16p, _u16p, _u16p, _i32p, _i32p, _i32p, _i32p] + [C.c_int] * 8
 
 
 def num_threads() -> int:
@@ -163,6 +170,54 @@ def sdpa_kt(q, kt, v, scale: float, causal_start_pos: int = -1):
     return out
 
 
+def rope_table(max_seq: int, head_dim: int, theta: float = 10000.0):
+    """cos, sin [max_seq, head_dim/2] as RoPECache::initialize builds them (src/llm/rope.cpp:5-22)."""
+    cos = np.empty((max_seq, head_dim // 2), np.float32)
+    sin = np.empty_like(cos)
+    _lib.gro_rope_table(max_seq, head_dim, theta, cos, sin)
+    return cos, sin
+
+
+def rope_apply(x: np.ndarray, start_pos: int, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """x [seq, heads, D] -> rotated copy (src/llm/rope.cpp:52-86)."""
+    out = np.ascontiguousarray(x, np.float32).copy()
+    seq, heads, d = out.shape
+    rc = _lib.gro_rope_apply(out, seq, heads, d, start_pos, np.ascontiguousarray(cos, np.float32),
+                             np.ascontiguousarray(sin, np.float32), cos.shape[0])
+    if rc:
+        raise ValueError("RoPE position out of range")
+    return out
+
+
+def rope_paged_append(q, k, v, cos, sin, k_pool, v_pool, tables, positions, block_size: int):
+    """q [B, new_len, Hq, D] (or None), k/v [B, new_len, Hkv, D] fp32; pools [num_blocks*bs, Hkv, D]
+    fp16 bits, updated in place.  Returns (rotated q, tokens that could not be written)."""
+    k = np.ascontiguousarray(k, np.float32)
+    v = np.ascontiguousarray(v, np.float32)
+    batch, new_len, hkv, d = k.shape
+    qr = None if q is None else np.ascontiguousarray(q, np.float32).copy()
+    hq = 0 if qr is None else qr.shape[2]
+    tables = np.ascontiguousarray(tables, np.int32)
+    assert k_pool.dtype == np.uint16 and k_pool.flags.c_contiguous and v_pool.flags.c_contiguous
+    bad = _lib.gro_rope_paged_append(None if qr is None else qr.ctypes.data_as(C.c_void_p), k, v,
+                                     np.ascontiguousarray(cos, np.float32), np.ascontiguousarray(sin, np.float32),
+                                     cos.shape[0], k_pool, v_pool, tables, np.ascontiguousarray(positions, np.int32),
+                                     batch, new_len, hq, hkv, d, block_size, tables.shape[1],
+                                     k_pool.shape[0] // block_size)
+    return qr, bad
+
+
+def tree_commit(k_tree, v_tree, k_pool, v_pool, tables, cache_lens, accepted, num_accepted, block_size: int) -> int:
+    """Tree K/V [B, Hkv, N, D] fp16 bits: accepted rows -> the paged pools (in place). Returns rows skipped."""
+    batch, hkv, n, d = k_tree.shape
+    tables = np.ascontiguousarray(tables, np.int32)
+    accepted = np.ascontiguousarray(accepted, np.int32)
+    return _lib.gro_tree_commit(np.ascontiguousarray(k_tree, np.uint16), np.ascontiguousarray(v_tree, np.uint16),
+                                k_pool, v_pool, tables, np.ascontiguousarray(cache_lens, np.int32), accepted,
+                                np.ascontiguousarray(num_accepted, np.int32), batch, n, accepted.shape[1], hkv, d,
+                                block_size, tables.shape[1], k_pool.shape[0] // block_size)
+
+
 # ------------------------------------------------------------------ the reference's own objects
 def ref_available() -> bool:
     return _REF.exists()
@@ -191,7 +246,24 @@ class Ref:
         r.ref_speculation_tree.argtypes = [_i32p, C.c_int, _i32p, _i32p, _i32p, _i32p, _i32p]
         r.ref_find_accepted_path.restype = C.c_int
         r.ref_find_accepted_path.argtypes = [_i32p, _i32p, C.c_int, _i32p, C.c_int, _i32p, _i32p]
+        r.ref_rope_table.restype = C.c_int
+        r.ref_rope_table.argtypes = [C.c_int, C.c_int, C.c_float, _f32p, _f32p]
+        r.ref_rope_apply.restype = C.c_int
+        r.ref_rope_apply.argtypes = [_f32p, _f32p] + [C.c_int] * 6 + [C.c_float]
         self._r = r
+
+    def rope_table(self, max_seq: int, head_dim: int, theta: float = 10000.0):
+        cos = np.empty((max_seq, head_dim // 2), np.float32)
+        sin = np.empty_like(cos)
+        self._r.ref_rope_table(max_seq, head_dim, theta, cos, sin)
+        return cos, sin
+
+    def rope_apply(self, q, k, start_pos: int, max_seq: int, theta: float = 10000.0):
+        """q [seq, Hq, D], k [seq, Hk, D] -> rotated copies through RoPECache::apply."""
+        q = np.ascontiguousarray(q, np.float32).copy()
+        k = np.ascontiguousarray(k, np.float32).copy()
+        rc = self._r.ref_rope_apply(q, k, q.shape[0], q.shape[1], k.shape[1], q.shape[2], start_pos, max_seq, theta)
+        return q, k, rc
 
     def fp16_to_fp32(self, h: int) -> float:
         return float(self._r.ref_fp16_to_fp32(h))

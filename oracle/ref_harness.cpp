@@ -159,6 +159,39 @@ int ref_kvcache_append(int num_kv_heads, int head_dim, int max_seq, const int32_
     return 0;
 }
 
+// RoPECache::initialize (src/llm/rope.cpp:5-22): the cos / sin tables [max_seq, head_dim/2].
+int ref_rope_table(int max_seq, int head_dim, float theta, float* cos_out, float* sin_out) {
+    RoPECache rope;
+    rope.initialize(max_seq, head_dim, theta);
+    std::memcpy(cos_out, rope.cos_cache().data(), rope.cos_cache().size() * sizeof(float));
+    std::memcpy(sin_out, rope.sin_cache().data(), rope.sin_cache().size() * sizeof(float));
+    return 0;
+}
+
+// RoPECache::apply (src/llm/rope.cpp:24-92) on q [1, seq, Hq, D] and k [1, seq, Hk, D], in place.
+int ref_rope_apply(float* q, float* k, int seq_len, int num_heads_q, int num_heads_k, int head_dim,
+                   int start_pos, int max_seq, float theta) {
+    auto* be = cpu_backend();
+    RoPECache rope;
+    rope.initialize(max_seq, head_dim, theta);
+    std::vector<int64_t> qs = {1, seq_len, num_heads_q, head_dim}, ks = {1, seq_len, num_heads_k, head_dim};
+    auto qt = Tensor::allocate(qs, DataType::FP32, be);
+    auto kt = Tensor::allocate(ks, DataType::FP32, be);
+    if (!qt.ok() || !kt.ok()) return -1;
+    Tensor tq = std::move(qt).take(), tk = std::move(kt).take();
+    std::memcpy(be->map_buffer(tq.buffer()).value(), q, tq.size_bytes());
+    std::memcpy(be->map_buffer(tk.buffer()).value(), k, tk.size_bytes());
+    auto r = rope.apply(tq, tk, start_pos, be);
+    int rc = r.ok() ? 0 : static_cast<int>(r.error().code());
+    if (rc == 0) {
+        std::memcpy(q, be->map_buffer(tq.buffer()).value(), tq.size_bytes());
+        std::memcpy(k, be->map_buffer(tk.buffer()).value(), tk.size_bytes());
+    }
+    be->destroy_buffer(tq.buffer());
+    be->destroy_buffer(tk.buffer());
+    return rc;
+}
+
 // Builds a SpeculationTree by add_node(token=i, parent=parents[i]) and returns its parent
 // array, node depths and BFS-flattened tokens.
 int ref_speculation_tree(const int32_t* parents, int n, int32_t* parents_out, int32_t* depths,

@@ -97,6 +97,35 @@ def ref_kvcache(ref):
                         k_out=k_out, v_out=v_out, final_len=np.array([final_len], np.int32))
 
 
+def ref_rope(ref):
+    """RoPECache tables and apply() outputs from the compiled reference (src/llm/rope.cpp)."""
+    rng = np.random.default_rng(19)
+    out = {}
+    # table samples: full small table, and rows of the large ones (first, odd, last positions)
+    cos, sin = ref.rope_table(48, 16, 10000.0)
+    out["t0_cfg"] = np.array([48, 16], np.int32)
+    out["t0_theta"] = np.array([10000.0], np.float32)
+    out["t0_cos"], out["t0_sin"] = cos.view(np.uint32), sin.view(np.uint32)
+    for i, (max_seq, d, theta) in enumerate([(4096, 128, 10000.0), (2048, 64, 500000.0)], start=1):
+        cos, sin = ref.rope_table(max_seq, d, theta)
+        rows = np.array([0, 1, 2, 3, 17, 255, 1000, max_seq - 1], np.int32)
+        out[f"t{i}_cfg"] = np.array([max_seq, d], np.int32)
+        out[f"t{i}_theta"] = np.array([theta], np.float32)
+        out[f"t{i}_rows"] = rows
+        out[f"t{i}_cos"], out[f"t{i}_sin"] = cos[rows].view(np.uint32), sin[rows].view(np.uint32)
+    # apply(): q [seq, Hq, D], k [seq, Hk, D] at a start position
+    for i, (seq, hq, hk, d, start, max_seq) in enumerate([(3, 4, 2, 16, 5, 48), (2, 32, 8, 128, 4000, 4096)]):
+        q = rng.standard_normal((seq, hq, d), dtype=np.float32)
+        k = rng.standard_normal((seq, hk, d), dtype=np.float32)
+        qr, kr, rc = ref.rope_apply(q, k, start, max_seq)
+        assert rc == 0
+        out[f"a{i}_cfg"] = np.array([seq, hq, hk, d, start, max_seq], np.int32)
+        out[f"a{i}_q"], out[f"a{i}_k"] = q.view(np.uint32), k.view(np.uint32)
+        out[f"a{i}_q_out"], out[f"a{i}_k_out"] = qr.view(np.uint32), kr.view(np.uint32)
+    out["range_error_code"] = np.array([ref.rope_apply(np.zeros((3, 1, 16), np.float32), np.zeros((3, 1, 16), np.float32), 46, 48)[2]], np.int32)
+    np.savez_compressed(HERE / "ref_rope.npz", **out)
+
+
 def ref_spec_tree(ref):
     out = {}
     for i, (seed, n) in enumerate([(1004, 64), (5, 16), (6, 1), (8, 33)]):
@@ -193,6 +222,7 @@ if __name__ == "__main__":
     ref_paged_pool(ref)
     ref_kvcache(ref)
     ref_spec_tree(ref)
+    ref_rope(ref)
     kat_sdpa()
     oracle_small_cases()
     for p in sorted(HERE.glob("*.npz")):

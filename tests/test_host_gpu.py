@@ -26,6 +26,9 @@ def _lib():
                                                 _u16p, _u16p, _i32p, _i32p]
     lib.granite_host_paged_flow.argtypes = [C.c_int, C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                             _f32p, _f32p, _f32p, _f32p, _i32p, C.c_int, _u16p, _u16p, C.c_int]
+    lib.granite_host_rope_apply.argtypes = [C.c_int, _f32p, _f32p] + [C.c_int] * 6 + [C.c_float]
+    lib.granite_host_decode_batch_flow.argtypes = [C.c_int, C.c_int, _i32p] + [C.c_int] * 10 + [_f32p] * 7 + \
+        [_i32p, _i32p, _u16p, _u16p]
     return lib
 
 
@@ -197,3 +200,90 @@ def test_batched_paged_append_then_decode(compute):
     assert np.array_equal(k.cpu().numpy().view(np.uint16), kp)
     ref, _ = pyoracle.paged_decode_batch(case.q, kp, vp, case.tables.clip(0), lens, 16)
     assert_attention_close(out.cpu().numpy(), ref, "append + decode")
+
+
+def test_rope_cache_apply_through_backend_tensors():
+    """RoPECache::apply (src/llm/rope.cpp:24-92) on CUDA-backend tensors against the reference's outputs."""
+    lib = _lib()
+    g = np.load(GOLD / "ref_rope.npz")
+    for i in range(2):
+        seq, hq, hk, d, start, max_seq = (int(x) for x in g[f"a{i}_cfg"])
+        q = g[f"a{i}_q"].view(np.float32).copy()
+        k = g[f"a{i}_k"].view(np.float32).copy()
+        rc = lib.granite_host_rope_apply(0, q.reshape(-1), k.reshape(-1), seq, hq, hk, d, start, max_seq, 10000.0)
+        assert rc == 0, (rc, lib.granite_host_last_error())
+        assert np.array_equal(q.view(np.uint32), g[f"a{i}_q_out"])
+        assert np.array_equal(k.view(np.uint32), g[f"a{i}_k_out"])
+    q = np.zeros((3, 1, 16), np.float32)
+    rc = lib.granite_host_rope_apply(0, q.reshape(-1), q.copy().reshape(-1), 3, 1, 1, 16, 46, 48, 10000.0)
+    assert rc == int(g["range_error_code"][0])  # InvalidArgument, as the reference answers
+    assert b"RoPE position out of range: 46 + 3 > 48" in lib.granite_host_last_error()
+
+
+@pytest.mark.parametrize("lens0,n_steps,remove_slot,remove_at", [([5, 0, 31, 16, 100], 40, 2, 7), ([300] * 3, 20, -1, 0),
+                                                                ([1], 33, -1, 0)])
+def test_batched_decode_loop_replays_on_the_cpu_checker(lens0, n_steps, remove_slot, remove_at):
+    """PagedKVPool + RoPECache + PagedDecodeBatch over several decode steps, one request leaving on
+    the way: every step's rotated queries and cache bytes bit-exact, every output within tolerance."""
+    from oracle import pyoracle
+    lib = _lib()
+    batch, hq, hkv, d, bs = len(lens0), 32, 8, 128, 16
+    max_seq = 512
+    max_blocks = max_seq // bs
+    num_blocks = sum((n + n_steps + bs - 1) // bs for n in lens0) + 2
+    rng = np.random.default_rng(batch * 7 + n_steps)
+    lens0 = np.array(lens0, np.int32)
+    prompt_k = rng.standard_normal((max(int(lens0.sum()), 1), hkv, d), dtype=np.float32)
+    prompt_v = rng.standard_normal(prompt_k.shape, dtype=np.float32)
+    step_q = rng.standard_normal((n_steps, batch, hq, d), dtype=np.float32)
+    step_k = rng.standard_normal((n_steps, batch, hkv, d), dtype=np.float32)
+    step_v = rng.standard_normal((n_steps, batch, hkv, d), dtype=np.float32)
+    out = np.full((n_steps, batch, hq, d), np.nan, np.float32)
+    q_rot = np.full_like(out, np.nan)
+    tables = np.zeros((n_steps, batch, max_blocks), np.int32)
+    lens = np.zeros((n_steps, batch), np.int32)
+    k_pool = np.zeros((num_blocks * bs, hkv, d), np.uint16)
+    v_pool = np.zeros_like(k_pool)
+    rc = lib.granite_host_decode_batch_flow(0, batch, lens0, n_steps, remove_slot, remove_at, hq, hkv, d, bs, num_blocks,
+                                            max_blocks, max_seq, prompt_k.reshape(-1), prompt_v.reshape(-1),
+                                            step_q.reshape(-1), step_k.reshape(-1), step_v.reshape(-1), out.reshape(-1),
+                                            q_rot.reshape(-1), tables.reshape(-1), lens.reshape(-1), k_pool.reshape(-1),
+                                            v_pool.reshape(-1))
+    assert rc == 0, (rc, lib.granite_host_last_error())
+
+    # replay on the CPU checker with the block tables the page manager handed out
+    cos, sin = pyoracle.rope_table(max_seq, d)
+    ck = np.zeros_like(k_pool)
+    cv = np.zeros_like(v_pool)
+    off = 0
+    for b in range(batch):
+        n = int(lens0[b])
+        if n:
+            tab = np.where(tables[0, b] < 0, 0, tables[0, b])[None]
+            _, bad = pyoracle.rope_paged_append(None, prompt_k[off:off + n][None], prompt_v[off:off + n][None], cos, sin,
+                                                ck, cv, tab, np.zeros(1, np.int32), bs)
+            assert bad == 0
+        off += n
+    for step in range(n_steps):
+        active = [b for b in range(batch) if lens[step, b] >= 0]
+        expect_active = [b for b in range(batch) if not (b == remove_slot and step >= remove_at)]
+        assert active == expect_active
+        for b in active:
+            assert lens[step, b] == lens0[b] + step + 1
+            tab = np.where(tables[step, b] < 0, 0, tables[step, b])[None]
+            qr, bad = pyoracle.rope_paged_append(step_q[step, b][None, None], step_k[step, b][None, None],
+                                                 step_v[step, b][None, None], cos, sin, ck, cv, tab,
+                                                 np.array([lens[step, b] - 1], np.int32), bs)
+            assert bad == 0
+            assert np.array_equal(qr.reshape(hq, d).view(np.uint32), q_rot[step, b].view(np.uint32))
+            ref, bad = pyoracle.paged_decode_batch(qr.reshape(1, hq, d), ck, cv, tab, lens[step, b:b + 1], bs)
+            assert bad == 0
+            assert_attention_close(out[step, b][None], ref, f"step {step} slot {b}")
+    # pages the departed request gave back were handed out again and overwritten; everything
+    # that is live at the end must hold the checker's bytes
+    live = np.zeros(num_blocks * bs, bool)
+    for b in range(batch):
+        if lens[-1, b] >= 0:
+            for pos in range(int(lens[-1, b])):
+                live[tables[-1, b, pos // bs] * bs + pos % bs] = True
+    assert np.array_equal(k_pool[live], ck[live]) and np.array_equal(v_pool[live], cv[live])

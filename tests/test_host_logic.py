@@ -8,6 +8,7 @@ import numpy as np
 
 GOLD = Path(__file__).resolve().parent / "golden"
 _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 
 
 def _lib():
@@ -18,6 +19,8 @@ def _lib():
                                                    _i32p, C.c_int, _i32p, _i32p]
     lib.granite_host_speculation_tree.argtypes = [_i32p, C.c_int, _i32p, _i32p, _i32p, _i32p, _i32p]
     lib.granite_host_find_accepted_path.argtypes = [_i32p, _i32p, C.c_int, _i32p, C.c_int, _i32p, _i32p]
+    lib.granite_host_find_accepted_nodes.argtypes = [_i32p, _i32p, C.c_int, _i32p, C.c_int, _i32p, _i32p]
+    lib.granite_host_rope_table.argtypes = [C.c_int, C.c_int, C.c_float, _f32p, _f32p]
     return lib
 
 
@@ -91,3 +94,37 @@ def test_speculation_tree_matches_reference():
         out, n_out = np.zeros(len(targets) + 1, np.int32), np.zeros(1, np.int32)
         lib.granite_host_find_accepted_path(parents, tokens, len(parents), targets, len(targets), out, n_out)
         assert np.array_equal(out[: int(n_out[0])], g[f"ap_path{i}"])
+
+
+def test_accepted_nodes_are_the_nodes_behind_the_reference_path():
+    """find_accepted_nodes must name the nodes whose tokens open the reference's accepted path: the
+    path is those tokens, optionally closed by the target's own choice at the first mismatch."""
+    lib = _lib()
+    g = np.load(GOLD / "ref_spec_tree.npz")
+    for i in range(6):
+        parents = np.ascontiguousarray(g[f"ap_parents{i}"], np.int32)
+        tokens = np.ascontiguousarray(g[f"ap_tokens{i}"], np.int32)
+        targets = np.ascontiguousarray(g[f"ap_targets{i}"], np.int32)
+        path = g[f"ap_path{i}"]
+        nodes, n_nodes = np.zeros(len(parents) + 1, np.int32), np.zeros(1, np.int32)
+        lib.granite_host_find_accepted_nodes(parents, tokens, len(parents), targets, len(targets), nodes, n_nodes)
+        nodes = nodes[: int(n_nodes[0])]
+        assert len(path) - 1 <= len(nodes) <= len(path)
+        assert np.array_equal(tokens[nodes], path[: len(nodes)])
+        if len(nodes):
+            assert nodes[0] == 0 and all(parents[nodes[j]] == nodes[j - 1] for j in range(1, len(nodes)))
+        if len(nodes) < len(path):  # closed by the target's choice where the tree disagreed
+            assert path[-1] == targets[len(nodes)]
+
+
+def test_rope_tables_of_the_host_mirror_match_reference():
+    lib = _lib()
+    g = np.load(GOLD / "ref_rope.npz")
+    for i in range(3):
+        max_seq, d = (int(x) for x in g[f"t{i}_cfg"])
+        cos = np.zeros((max_seq, d // 2), np.float32)
+        sin = np.zeros_like(cos)
+        assert lib.granite_host_rope_table(max_seq, d, float(g[f"t{i}_theta"][0]), cos.reshape(-1), sin.reshape(-1)) == 0
+        rows = g[f"t{i}_rows"] if f"t{i}_rows" in g else np.arange(max_seq)
+        assert np.array_equal(cos[rows].view(np.uint32), g[f"t{i}_cos"])
+        assert np.array_equal(sin[rows].view(np.uint32), g[f"t{i}_sin"])

@@ -127,6 +127,58 @@ def test_synthetic_tree_respects_limits():
     assert pyoracle.tree_mask(p).sum(1).max() - 1 <= 8
 
 
+def test_rope_tables_and_rotation_match_reference():
+    """RoPECache::initialize / apply of the compiled reference (src/llm/rope.cpp:5-92), bit for bit."""
+    g = np.load(GOLD / "ref_rope.npz")
+    for i in range(3):
+        max_seq, d = (int(x) for x in g[f"t{i}_cfg"])
+        cos, sin = pyoracle.rope_table(max_seq, d, float(g[f"t{i}_theta"][0]))
+        rows = g[f"t{i}_rows"] if f"t{i}_rows" in g else np.arange(max_seq)
+        assert np.array_equal(cos[rows].view(np.uint32), g[f"t{i}_cos"])
+        assert np.array_equal(sin[rows].view(np.uint32), g[f"t{i}_sin"])
+    for i in range(2):
+        seq, hq, hk, d, start, max_seq = (int(x) for x in g[f"a{i}_cfg"])
+        cos, sin = pyoracle.rope_table(max_seq, d)
+        q = g[f"a{i}_q"].view(np.float32)
+        k = g[f"a{i}_k"].view(np.float32)
+        assert np.array_equal(pyoracle.rope_apply(q, start, cos, sin).view(np.uint32), g[f"a{i}_q_out"])
+        assert np.array_equal(pyoracle.rope_apply(k, start, cos, sin).view(np.uint32), g[f"a{i}_k_out"])
+    assert int(g["range_error_code"][0]) == 16  # InvalidArgument, rope.cpp:34-38
+    with pytest.raises(ValueError):
+        pyoracle.rope_apply(np.zeros((3, 1, 16), np.float32), 46, *pyoracle.rope_table(48, 16))
+
+
+def test_rope_paged_append_is_rotation_then_truncation_then_scatter():
+    rng = np.random.default_rng(5)
+    batch, new_len, hq, hkv, d, bs, nblocks, max_blocks = 3, 2, 4, 2, 16, 4, 12, 4
+    cos, sin = pyoracle.rope_table(16, d)
+    q = rng.standard_normal((batch, new_len, hq, d), dtype=np.float32)
+    k = rng.standard_normal((batch, new_len, hkv, d), dtype=np.float32)
+    v = rng.standard_normal((batch, new_len, hkv, d), dtype=np.float32)
+    tables = rng.permutation(nblocks).astype(np.int32).reshape(batch, max_blocks)
+    positions = np.array([0, 3, 9], np.int32)
+    kp = np.zeros((nblocks * bs, hkv, d), np.uint16)
+    vp = np.zeros_like(kp)
+    qr, bad = pyoracle.rope_paged_append(q, k, v, cos, sin, kp, vp, tables, positions, bs)
+    assert bad == 0
+    written = np.zeros(nblocks * bs, bool)
+    for b in range(batch):
+        for s in range(new_len):
+            pos = int(positions[b]) + s
+            row = tables[b, pos // bs] * bs + pos % bs
+            written[row] = True
+            kr = pyoracle.rope_apply(k[b, s:s + 1], pos, cos, sin)[0]
+            assert np.array_equal(qr[b, s], pyoracle.rope_apply(q[b, s:s + 1], pos, cos, sin)[0])
+            assert [pyoracle.fp32_to_fp16(float(x)) for x in kr.reshape(-1)] == kp[row].reshape(-1).tolist()
+            assert [pyoracle.fp32_to_fp16(float(x)) for x in v[b, s].reshape(-1)] == vp[row].reshape(-1).tolist()
+    assert not kp[~written].any() and not vp[~written].any()
+    # a position outside the table, or a table entry outside the pool, skips the token and is counted
+    tables_bad = tables.copy()
+    tables_bad[1, 0] = nblocks
+    _, bad = pyoracle.rope_paged_append(q, k, v, cos, sin, kp, vp, tables_bad, np.array([0, 3, 15], np.int32), bs)
+    assert bad == 1 + 1  # sequence 1's first token (bad entry), sequence 2's second token (position 16)
+
+
 @pytest.mark.skipif(not pyoracle.ref_available(), reason="oracle/_ref not built (needs the reference checkout)")
 def test_live_reference_objects_agree_with_goldens():
     ref = pyoracle.Ref()
