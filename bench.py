@@ -317,6 +317,85 @@ def measure_tree(compute, dev, reps: int = 200):
             "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind}
 
 
+def measure_decode_step_write(compute, dev, reps: int = 200):
+    """The cache write of one decode step for 64 sequences (Hq 32, Hkv 8, D 128): RoPE on Q and K plus
+    the paged K/V store, as one fused launch and as the reference's two calls
+    (rope_multihead, then paged_kv_cache_append; src/llm/transformer.mm:2975-2986)."""
+    import torch
+    from granite_b200 import synth
+    batch, hq, hkv, d = 64, 32, 8, 128
+    case = synth.paged_case(2024, batch, 1024, 8192, hq, hkv, d, device=dev, spare_blocks=batch)
+    tables = torch.from_numpy(np.where(case.tables < 0, 0, case.tables).astype(np.int32)).to(dev)
+    positions = torch.from_numpy((case.seq_lens - 1).astype(np.int32)).to(dev)
+    max_seq = 8192
+    cos_p, sin_p = compute.rope_table_create(max_seq, d)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    q = torch.randn((batch, 1, hq, d), device=dev, generator=gen)
+    k = torch.randn((batch, 1, hkv, d), device=dev, generator=gen)
+    v = torch.randn((batch, 1, hkv, d), device=dev, generator=gen)
+
+    def fused(i):
+        compute.rope_paged_kv_cache_append(q, k, v, cos_p, sin_p, case.k_pool, case.v_pool, tables, positions, batch, 1,
+                                           hq, hkv, d, synth.PAGE, case.max_blocks, case.num_blocks, max_seq)
+
+    def unfused(i):
+        # positions differ per sequence, so the unfused pair rotates at one common position; the
+        # bytes moved are the same, which is what is timed
+        compute.rope_multihead(q, k, hq, hkv, batch, d, 1000, cos_p, sin_p, max_seq)
+        compute.paged_kv_cache_append(k, v, case.k_pool, case.v_pool, tables, hkv, d, 0, 0, synth.PAGE,
+                                      num_blocks=case.num_blocks, table_len=case.max_blocks, positions=positions,
+                                      batch_size=batch)
+
+    for i in range(5):
+        fused(i)
+        unfused(i)
+    compute.sync()
+    ms_fused = region_ms_per_launch(dev, fused, reps)
+    ms_unfused = region_ms_per_launch(dev, unfused, reps)
+    compute.destroy_buffer(cos_p)
+    compute.destroy_buffer(sin_p)
+    nbytes = batch * (hq * d * 4 * 2 + 2 * hkv * d * 4 + 2 * hkv * d * 2) + batch * 8
+    return {"workload": "decode_step_cache_write_b64", "kernel": "rope_paged_kv_append", "kernel_ms": ms_fused,
+            "unfused_two_launch_ms": ms_unfused, "launches": reps, "algorithmic_bytes": nbytes,
+            "bound": "launch latency (2.9 MB moved)", "gbs": nbytes / ms_fused / 1e6}
+
+
+def measure_paged_prefill(compute, dev, reps: int = 200):
+    """The prefill configuration (2048 tokens, Hq 32, Hkv 8) with K/V read through the block table
+    instead of a contiguous cache: what paging costs the tensor-bound kernel."""
+    import torch
+    from granite_b200 import synth
+    seq, hq, hkv, d = 2048, 32, 8, 128
+    cases = [synth.paged_case(4000 + i, 1, 0, 0, hq, hkv, d, seq_lens=np.array([seq], np.int32), device=dev, spare_blocks=512)
+             for i in range(4)]
+    tables = [torch.from_numpy(np.where(c.tables[0] < 0, 0, c.tables[0]).astype(np.int32)).to(dev) for c in cases]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    qs = [torch.randn((seq, hq, d), device=dev, generator=gen).half() for _ in range(4)]
+    out = torch.zeros((seq, hq, d), device=dev, dtype=torch.float16)
+
+    def step(i):
+        c = cases[i % 4]
+        compute.paged_prefill_attention(qs[i % 4], c.k_pool, c.v_pool, tables[i % 4], out, hq, hkv, seq, 0, d, synth.PAGE,
+                                        c.max_blocks, c.num_blocks, 1.0 / float(np.sqrt(d)), q_dtype=1, out_dtype=1)
+
+    for i in range(5):
+        step(i)
+    compute.sync()
+    ms = region_ms_per_launch(dev, step, reps)
+    flops = 4 * d * hq * seq * (seq + 1) // 2
+    burst, sustained, kind = tensor_peak()
+    tf = flops / ms / 1e9
+    return {"workload": "paged_prefill_s2048", "kernel": "paged_prefill_fa", "kernel_ms": ms, "launches": reps,
+            "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst, "frac": tf / burst,
+            "frac_of_sustained": tf / sustained, "peak_kind": kind}
+
+
+SECONDARY = {"prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
+             "paged_prefill": measure_paged_prefill}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,8 +406,8 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
-    ap.add_argument("--only", default="", choices=["", "prefill", "tree"],
-                    help="run just one of the secondary tensor-bound workloads (profiling captures)")
+    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "step_write", "paged_prefill"],
+                    help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
     args = ap.parse_args()
@@ -355,7 +434,7 @@ def main():
 
     if args.only:
         compute = g.CudaCompute(dev.index, torch.cuda.current_stream().cuda_stream)
-        fn = measure_prefill if args.only == "prefill" else measure_tree
+        fn = SECONDARY[args.only]
         print(json.dumps(fn(compute, dev, max(args.steps, 1))), flush=True)
         compute.shutdown()
         return 0
@@ -512,7 +591,9 @@ def main():
 
     secondary = None
     if world == 1 and not strong and args.sequences == 0:
-        secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev)}
+        secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev),
+                     "decode_step_cache_write": measure_decode_step_write(compute, dev),
+                     "paged_prefill": measure_paged_prefill(compute, dev)}
 
     if rank == 0:
         line = {
