@@ -257,3 +257,69 @@ def test_chunked_prefill_rejects_a_chunk_beyond_the_table(compute):
                                         case.max_blocks * synth.PAGE - 16, d, synth.PAGE, case.max_blocks, case.num_blocks,
                                         0.1)
     assert e.value.code == ErrorCode.InvalidArgument
+
+
+def test_verify_commit_then_decode(compute):
+    """The speculative step end to end: verify a tree against the paged prefix, keep an accepted
+    path with the commit copy, and decode the next token over the grown cache - the committed rows
+    must serve exactly as if they had been appended one by one."""
+    import torch
+    from oracle import pyoracle
+    from test_tree_verify import _tree_inputs
+    batch, n, hq, hkv, d = 4, 64, 32, 8, 128
+    rng = np.random.default_rng(21)
+    cache_lens = np.array([100, 16, 333, 0], np.int32)
+    max_acc = 8
+    case = synth.paged_case(55, batch, 0, 0, hq, hkv, d, seq_lens=cache_lens + max_acc, spare_blocks=2)
+    tables = np.where(case.tables < 0, 0, case.tables).astype(np.int32)
+    q, kt, vt, parents = _tree_inputs(9, batch, n, hq, hkv)
+    k_np = case.k_pool.view(np.uint16).copy()
+    v_np = case.v_pool.view(np.uint16).copy()
+    kd = torch.from_numpy(k_np.view(np.float16)).to(DEV)
+    vd = torch.from_numpy(v_np.view(np.float16)).to(DEV)
+    td = torch.from_numpy(tables).to(DEV)
+    ktd, vtd = torch.from_numpy(kt).to(DEV), torch.from_numpy(vt).to(DEV)
+    out = torch.zeros((batch, hq, n, d), device=DEV)
+    compute.attention_tree(torch.from_numpy(q).to(DEV), kd, vd, ktd, vtd, torch.from_numpy(parents).to(DEV), out, hq, hkv,
+                           n, 0, d, 1.0 / np.sqrt(d), batch_size=batch, block_tables=td, max_blocks_per_seq=case.max_blocks,
+                           num_blocks=case.num_blocks, cache_lens=torch.from_numpy(cache_lens).to(DEV))
+    # accepted path per sequence: a root-to-node chain of the tree (what find_accepted_nodes returns)
+    accepted = np.full((batch, max_acc), -1, np.int32)
+    num_acc = np.zeros(batch, np.int32)
+    for b in range(batch):
+        node = int(rng.integers(0, n))
+        chain = []
+        while node >= 0:
+            chain.append(node)
+            node = int(parents[b, node])
+        chain = chain[::-1][:max_acc]
+        accepted[b, :len(chain)] = chain
+        num_acc[b] = len(chain)
+    compute.tree_commit(ktd, vtd, kd, vd, td, torch.from_numpy(cache_lens).to(DEV), torch.from_numpy(accepted).to(DEV),
+                        torch.from_numpy(num_acc).to(DEV), batch, n, max_acc, hkv, d, synth.PAGE, case.max_blocks,
+                        case.num_blocks)
+    new_lens = (cache_lens + num_acc).astype(np.int32)
+    q1 = rng.standard_normal((batch, hq, d), dtype=np.float32)
+    out1 = torch.zeros((batch, hq, d), device=DEV)
+    compute.batched_paged_attention_decode(torch.from_numpy(q1).to(DEV), kd, vd, td, torch.from_numpy(new_lens).to(DEV), out1,
+                                           batch, hq, hkv, d, synth.PAGE, case.max_blocks, 1.0 / np.sqrt(d),
+                                           num_blocks=case.num_blocks)
+    compute.sync()
+    # checker: the same commit on the host copies, then decode; and the verification itself per sequence
+    assert pyoracle.tree_commit(kt.view(np.uint16), vt.view(np.uint16), k_np, v_np, tables, cache_lens, accepted, num_acc,
+                                synth.PAGE) == 0
+    assert np.array_equal(kd.cpu().numpy().view(np.uint16), k_np)
+    ref1, bad = pyoracle.paged_decode_batch(q1, k_np, v_np, tables, new_lens, synth.PAGE)
+    assert bad == 0
+    assert_attention_close(out1.cpu().numpy(), ref1, "decode after commit")
+    # the last accepted node's verification output equals plain causal attention over prefix + path
+    got = out.cpu().numpy()
+    for b in range(batch):
+        if num_acc[b] == 0:
+            continue
+        last = int(accepted[b, num_acc[b] - 1])
+        rows_k, _ = pyoracle.paged_gather(k_np, tables[b], int(new_lens[b]), synth.PAGE)
+        rows_v, _ = pyoracle.paged_gather(v_np, tables[b], int(new_lens[b]), synth.PAGE)
+        ref = pyoracle.attention(q[b, :, last][None, None], pyoracle.f16_bits_to_f32(rows_k), pyoracle.f16_bits_to_f32(rows_v),
+                                 int(new_lens[b]) - 1)
+        assert_attention_close(got[b, :, last], ref[0, 0], f"sequence {b}: tree output of the path's last node")
