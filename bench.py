@@ -217,7 +217,7 @@ def region_ms_per_launch(dev, step, reps: int) -> float:
 
 
 def measure_prefill(compute, dev, reps: int = 200):
-    """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (BASELINE.json configs[1]); the
+    """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (the prefill benchmark configuration); the
     kernel's own event-timed duration, rotating over 4 input sets."""
     import torch
     from granite_b200 import synth
@@ -260,7 +260,7 @@ def measure_prefill(compute, dev, reps: int = 200):
 
 def measure_tree(compute, dev, reps: int = 200):
     """Tree verification: 16 sequences x (4096-token paged prefix + 64-node tree), Hq 32, Hkv 8
-    (BASELINE.json configs[3]); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
+    (the tree-verification benchmark configuration); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
     import torch
     from granite_b200 import synth
     cfg = synth.CONFIGS["tree_verify_b16"]

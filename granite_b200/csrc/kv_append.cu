@@ -5,7 +5,7 @@
 // (src/backend/metal/kernels/metal_shaders_attention.h:102-132, :2142-2176; wrappers
 // MetalCompute::kv_cache_append / paged_kv_cache_append, include/granite/metal_compute.h:787-797,
 // :887-898).  Source layouts are the kernels' own: [new_len, H, D] for the contiguous cache,
-// [H, new_len, D] for the paged pool.  The narrowing follows the CPU path the results are judged
+// [H, new_len, D] for the paged pool.  The narrowing follows the CPU path the results are checked
 // against - truncation of the mantissa, flush of results below the normal range to signed zero,
 // clamp to infinity (src/llm/math_ops.cpp:45-54, used at src/llm/transformer.mm:1681-1691) - so
 // the cache bytes are bit-identical to what Granite's CPU attention would read.  (The Metal

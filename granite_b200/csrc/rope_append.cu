@@ -4,7 +4,7 @@
 // rotated K through HBM instead of three launches
 // (rope_multihead -> paged_kv_cache_append, src/llm/transformer.mm:2975-2986).
 //
-// Arithmetic follows the CPU path results are judged against (src/llm/rope.cpp:52-86): tables of
+// Arithmetic follows the CPU path results are checked against (src/llm/rope.cpp:52-86): tables of
 // cos/sin per (position, pair) built on the host, adjacent pairs (2i, 2i+1), both products of each
 // output rounded separately (__fmul_rn / __fsub_rn / __fadd_rn keep the compiler from fusing them),
 // then the truncating fp32 -> fp16 cast of src/llm/math_ops.cpp:45-54 for what goes into the cache.

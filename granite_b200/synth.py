@@ -115,7 +115,7 @@ def tree_parents(seed: int, num_nodes: int = 64, max_children: int = 4, max_dept
     return parents
 
 
-# Shapes of the benchmark configurations (BASELINE.json "configs", in order).
+# Shapes of the benchmark configurations.
 CONFIGS = {
     "decode_contiguous_ctx512": dict(seed=1001, batch=1, ctx=512, num_heads=32, num_kv_heads=8, head_dim=128),
     "prefill_causal_s2048": dict(seed=1002, seq=2048, num_heads=32, num_kv_heads=8, head_dim=128),

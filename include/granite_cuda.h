@@ -307,7 +307,7 @@ int granite_cuda_build_tree_mask(granite_cuda_compute_t* c, const int32_t* paren
 /* ---- RoPE and the fused RoPE + paged cache write ---------------------------------------------
  * The step immediately before attention (src/llm/transformer.mm:2975-2986: rope_multihead, then
  * paged_kv_cache_append, then the attention kernel).  The rotation follows the CPU path the
- * results are judged against: RoPECache (src/llm/rope.cpp:5-92) - cos/sin tables
+ * results are checked against: RoPECache (src/llm/rope.cpp:5-92) - cos/sin tables
  * [table_len, head_dim/2] built once on the host with the reference's own float formula,
  * adjacent pairs (2i, 2i+1), both products rounded separately - so rotated values are
  * bit-identical to Granite's CPU arithmetic.  (MetalCompute::rope_multihead,
