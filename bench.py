@@ -475,7 +475,31 @@ def main():
     if strong and world > 1:
         rows = sharding.padded_rows(plan)  # ranks own different numbers of sequences
         outs = [torch.zeros((rows, Hq, D), device=dev) for _ in range(2)]
-    gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)] if world > 1 else None
+    # Output gather across the ranks: every rank pushes its rows into every rank's gathered buffer with
+    # peer stores over NVLink (symmetric memory), on a side stream so that the push of step i runs
+    # beside the decode kernel of step i + 1.  NCCL's all-gather is the fall-back where symmetric
+    # memory cannot be set up.
+    gathered, peer_ptrs, gather_mode = None, None, "none"
+    side = torch.cuda.Stream(device=dev) if world > 1 else None
+    if world > 1:
+        try:
+            import torch.distributed._symmetric_memory as symm
+            gathered = [symm.empty((world * rows, Hq, D), dtype=torch.float32, device=dev) for _ in range(2)]
+            handles = [symm.rendezvous(t, dist.group.WORLD) for t in gathered]
+            peer_ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
+            gather_mode = "peer stores over NVLink (symmetric memory), overlapped with the next step"
+        except Exception as exc:  # noqa: BLE001 - any failure means: use the collective library
+            print(f"[bench] symmetric memory unavailable ({exc!r}); gathering with NCCL", file=sys.stderr)
+            gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
+            peer_ptrs = None
+            gather_mode = "NCCL all-gather per step"
+        flags = torch.tensor([1 if peer_ptrs else 0], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same route
+        if int(flags.item()) == 0 and peer_ptrs is not None:
+            gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
+            peer_ptrs, gather_mode = None, "NCCL all-gather per step"
+    push_done = [None, None]
+    row_bytes = rows * Hq * D * 4
 
     def decode(q, tables, lens, out):
         compute.batched_paged_attention_decode(q, case.k_pool, case.v_pool, tables, lens, out, B, Hq, Hkv,
@@ -486,8 +510,18 @@ def main():
 
     def step(i):
         out = outs[i & 1]
+        if push_done[i & 1] is not None:
+            stream.wait_event(push_done[i & 1])  # the push of step i - 2 has read this buffer
         decode(q_d, tables_d, lens_d, out)
-        if world > 1:
+        if world > 1 and peer_ptrs is not None:
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            side.wait_event(ready)
+            compute.push_rows(out, peer_ptrs[i & 1], rank * row_bytes, row_bytes, stream=side.cuda_stream)
+            done = torch.cuda.Event()
+            done.record(side)
+            push_done[i & 1] = done
+        elif world > 1:
             # the gather is ordered after this step's kernels and before the next step's: a
             # persistent one-CTA-per-SM decode kernel must not share SMs with an NCCL kernel
             dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True).wait()
@@ -516,11 +550,21 @@ def main():
     for w in pending:
         w.wait()
     pending.clear()
+    for ev in push_done:
+        if ev is not None:
+            stream.wait_event(ev)  # the last pushes end inside the timed region
     e1.record(stream)
     barrier()
     clocks = sampler.stop()
     compute.sync()
     ms_total = e0.elapsed_time(e1)
+    gather_ok = None
+    if world > 1 and peer_ptrs is not None:
+        # outside the timed region: what the peers stored here must be what NCCL would have gathered
+        last = (args.steps - 1) & 1
+        expect = torch.empty_like(gathered[last])
+        dist.all_gather_into_tensor(expect, outs[last])
+        gather_ok = bool(torch.equal(expect, gathered[last]))
     kstats = compute.get_kernel_timing_stats()
     compute.enable_kernel_timing(False)
     if world > 1:
@@ -606,7 +650,8 @@ def main():
                        "page": synth.PAGE, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
                        "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
                        "l2": f"inputs larger than L2 ({case.total_tokens * Hkv * D * 4 / 1e9:.1f} GB of K/V per GPU per step, no reuse)",
-                       "sharding": "by sequence; NCCL all-gather of outputs per step" if world > 1 else "single GPU"},
+                       "sharding": f"by sequence; output gather: {gather_mode}" if world > 1 else "single GPU",
+                       **({"gather_verified": gather_ok} if gather_ok is not None else {})},
             "hbm_frac_of_measured_peak": value / n_gpus / peak,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,

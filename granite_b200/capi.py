@@ -183,6 +183,8 @@ _sig("granite_cuda_rope_multihead", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
 _sig("granite_cuda_rope_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(RopeAppendArgs))
 _sig("granite_cuda_tree_commit", C.c_int, C.c_void_p, C.POINTER(TreeCommitArgs))
 _sig("granite_cuda_paged_prefill_attention", C.c_int, C.c_void_p, C.POINTER(PagedPrefillArgs))
+_sig("granite_cuda_push_rows", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_uint32,
+     C.c_uint64, C.c_uint64)
 _sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
      C.c_void_p)
 
@@ -367,6 +369,12 @@ class CudaCompute:
                              num_kv_heads, seq_q, start_pos, head_dim, block_size, max_blocks_per_seq, num_blocks,
                              q_dtype, out_dtype, scale)
         check(lib.granite_cuda_paged_prefill_attention(self._h, C.byref(a)))
+
+    def push_rows(self, src, dst_ptrs, dst_offset_bytes: int, nbytes: int, stream: int | None = None) -> None:
+        """Stores `nbytes` bytes of `src` at every address in `dst_ptrs` (+ offset): local or peer-mapped buffers."""
+        arr = (C.c_void_p * len(dst_ptrs))(*[_ptr(d) for d in dst_ptrs])
+        check(lib.granite_cuda_push_rows(self._h, C.c_void_p(stream or 0), C.c_void_p(_ptr(src)), arr, len(dst_ptrs),
+                                         dst_offset_bytes, nbytes))
 
     def build_tree_mask(self, parent_indices, masks, batch_size, num_nodes) -> None:
         check(lib.granite_cuda_build_tree_mask(self._h, C.c_void_p(_ptr(parent_indices)),

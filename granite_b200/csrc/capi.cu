@@ -419,6 +419,13 @@ int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const Granit
     return launch_paged_prefill(c, *args);
 }
 
+int granite_cuda_push_rows(granite_cuda_compute_t* c, void* stream, const void* src, void* const* dst_ptrs,
+                           uint32_t n_dst, uint64_t dst_offset_bytes, uint64_t bytes) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "push_rows: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_push_rows(c, static_cast<cudaStream_t>(stream), src, dst_ptrs, n_dst, dst_offset_bytes, bytes);
+}
+
 int granite_cuda_attention_tree(granite_cuda_compute_t* c, const GraniteCudaTreeAttentionArgs* args) {
     if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null argument");
     GB_CUDA_TRY(cudaSetDevice(c->device));

@@ -159,6 +159,24 @@ __global__ void tree_commit_kernel(TreeCommitParams p) {
     }
 }
 
+constexpr int kMaxPushDst = 16;
+struct PushParams {
+    const uint4* src;
+    uint4* dst[kMaxPushDst];
+    int n_dst;
+    size_t n_vec;
+};
+
+// Every 16-byte piece of the source is read once and stored to each destination (local or a peer
+// GPU's memory mapped into this process): consecutive threads write consecutive pieces, so every
+// store instruction of a warp is 512 contiguous bytes on the link.
+__global__ void push_rows_kernel(PushParams p) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = p.src[i];
+        for (int r = 0; r < p.n_dst; r++) p.dst[r][i] = v;
+    }
+}
+
 unsigned grid_for(size_t total, int sm_count) {
     size_t blocks = (total + 255) / 256;
     const size_t cap = (size_t)sm_count * 8;
@@ -258,6 +276,37 @@ int launch_tree_commit(granite_cuda_compute* c, const GraniteCudaTreeCommitArgs&
     const size_t total = (size_t)a.batch_size * a.max_accepted * a.num_kv_heads * p.row_vecs;
     LaunchScope t(c, "tree_commit");
     tree_commit_kernel<<<grid_for(total, c->sm_count), 256, 0, c->stream>>>(p);
+    GB_CUDA_TRY(cudaGetLastError());
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int launch_push_rows(granite_cuda_compute* c, cudaStream_t stream, const void* src, void* const* dst_ptrs, uint32_t n_dst,
+                     uint64_t dst_offset_bytes, uint64_t bytes) {
+    if (!src || !dst_ptrs) return fail(GRANITE_CUDA_NULL_POINTER, "push_rows: null buffer");
+    if (n_dst == 0 || bytes == 0) return GRANITE_CUDA_SUCCESS;
+    if (n_dst > (uint32_t)kMaxPushDst) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "push_rows: at most 16 destinations");
+    if ((reinterpret_cast<uintptr_t>(src) | dst_offset_bytes | bytes) & 15)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "push_rows: source, offset and size must be 16-byte aligned");
+    PushParams p{};
+    p.src = static_cast<const uint4*>(src);
+    p.n_dst = (int)n_dst;
+    p.n_vec = bytes / 16;
+    for (uint32_t r = 0; r < n_dst; r++) {
+        if (!dst_ptrs[r]) return fail(GRANITE_CUDA_NULL_POINTER, "push_rows: null destination");
+        if (reinterpret_cast<uintptr_t>(dst_ptrs[r]) & 15)
+            return fail(GRANITE_CUDA_INVALID_ARGUMENT, "push_rows: destinations must be 16-byte aligned");
+        p.dst[r] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst_ptrs[r]) + dst_offset_bytes);
+    }
+    // a small grid without shared memory: it fits on SMs beside a persistent attention CTA
+    size_t blocks = (p.n_vec + 255) / 256;
+    if (blocks > 64) blocks = 64;
+    cudaStream_t st = stream ? stream : c->stream;
+    if (st == c->stream) {
+        LaunchScope t(c, "push_rows");
+        push_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+    } else {
+        push_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);  // timed by the caller's own events
+    }
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }

@@ -411,6 +411,19 @@ typedef struct {
 
 int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const GraniteCudaPagedPrefillArgs* args);
 
+/* ---- output gather over NVLink peer memory ---------------------------------------------------------
+ * Sequences are sharded across GPUs with no exchange inside attention; what follows the path is a
+ * gather of the per-GPU output rows.  This call pushes `bytes` bytes from `src` (this GPU) to
+ * dst_ptrs[r] + dst_offset_bytes for every r < n_dst with plain 16-byte stores - the destinations are
+ * peer-mapped buffers of the other GPUs of the box (symmetric memory, CUDA IPC or cuMemMap; one of
+ * them may be local).  No collective library, no multicast, nothing waits on another GPU: ordering
+ * towards a consumer on the destination GPU is the caller's (an event, a flag, a barrier).
+ * stream NULL = the compute object's stream; any other stream lets the push overlap the next step.
+ * src, every destination and bytes must be 16-byte aligned; n_dst <= 16.  No reference counterpart
+ * (the reference runs on one GPU). */
+int granite_cuda_push_rows(granite_cuda_compute_t* c, void* stream, const void* src, void* const* dst_ptrs,
+                           uint32_t n_dst, uint64_t dst_offset_bytes, uint64_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

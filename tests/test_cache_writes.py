@@ -323,3 +323,22 @@ def test_verify_commit_then_decode(compute):
         ref = pyoracle.attention(q[b, :, last][None, None], pyoracle.f16_bits_to_f32(rows_k), pyoracle.f16_bits_to_f32(rows_v),
                                  int(new_lens[b]) - 1)
         assert_attention_close(got[b, :, last], ref[0, 0], f"sequence {b}: tree output of the path's last node")
+
+
+def test_push_rows_copies_to_every_destination(compute):
+    """The output gather's push kernel, with local buffers standing in for the peers' memory."""
+    import torch
+    src = torch.randn((64, 32, 128), device=DEV)
+    dsts = [torch.full((4 * 64, 32, 128), float("nan"), device=DEV) for _ in range(3)]
+    nbytes = src.numel() * 4
+    compute.push_rows(src, dsts, 2 * nbytes, nbytes)
+    compute.sync()
+    for d in dsts:
+        assert torch.equal(d[128:192], src)
+        assert torch.isnan(d[:128]).all() and torch.isnan(d[192:]).all()
+    with pytest.raises(GraniteCudaError) as e:
+        compute.push_rows(src, dsts, 8, nbytes)  # offset not 16-byte aligned
+    assert e.value.code == ErrorCode.InvalidArgument
+    with pytest.raises(GraniteCudaError) as e:
+        compute.push_rows(src, [dsts[0]] * 17, 0, nbytes)
+    assert e.value.code == ErrorCode.InvalidArgument
