@@ -6,8 +6,9 @@ One step = one batched paged decode call (plan + split-KV kernel + merge) over o
 synthetic sequences whose K/V pages already live in HBM.  Workload at N = 1: 64 sequences, context
 lengths uniform in [1024, 32768], page 16, shuffled block table, Hq 32 / Hkv 8 / D 128, fp16 K/V,
 fp32 Q and output.  At N > 1 every rank owns its own batch of that shape (sequences are
-independent: sharded by sequence, no collective inside attention); the per-rank outputs are
-all-gathered with NCCL each step.  Prints ONE JSON line (rank 0).
+independent: sharded by sequence, no collective inside attention); every step the per-rank outputs
+are gathered on every rank by peer stores over NVLink (granite_cuda_push_rows into symmetric
+memory, beside the next step's kernel; NCCL all-gather as the fall-back).  Prints ONE JSON line (rank 0).
 
 --impl reference times Granite's CPU attention arithmetic (oracle/, a restatement of
 src/llm/transformer.mm:1779-1840 over pages fetched by the rule of metal_compute.h:853-861, with
