@@ -393,7 +393,31 @@ def measure_paged_prefill(compute, dev, reps: int = 200):
             "frac_of_sustained": tf / sustained, "peak_kind": kind}
 
 
-SECONDARY = {"prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
+def measure_single_decode(compute, dev, reps: int = 200):
+    """One sequence, one new token, 512 tokens of contiguous fp16 cache (Hq 32, Hkv 8, D 128): the
+    reference's own CPU-runnable case.  2 MB of traffic: the figure is launch latency, not bandwidth."""
+    import torch
+    hq, hkv, d, ctx = 32, 8, 128, 512
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1001)
+    q = torch.randn((hq, d), device=dev, generator=gen)
+    k = torch.randn((hkv, ctx, d), device=dev, generator=gen).half()
+    v = torch.randn((hkv, ctx, d), device=dev, generator=gen).half()
+    out = torch.zeros((hq, d), device=dev)
+
+    def step(i):
+        compute.multihead_attention(q, k, v, out, hq, hkv, 1, ctx, d, 1.0 / float(np.sqrt(d)), ctx)
+
+    for i in range(5):
+        step(i)
+    compute.sync()
+    ms = region_ms_per_launch(dev, step, reps)
+    nbytes = 2 * hkv * ctx * d * 2 + hq * d * 4 * 2
+    return {"workload": "decode_contiguous_ctx512", "kernels": "decode_plan + contiguous_decode_splitkv + decode_merge",
+            "call_ms": ms, "launches": reps, "algorithmic_bytes": nbytes, "bound": "launch latency (three dependent kernels)"}
+
+
+SECONDARY = {"single_decode": measure_single_decode, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
              "paged_prefill": measure_paged_prefill}
 
 
@@ -407,7 +431,7 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
-    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "step_write", "paged_prefill"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "step_write", "paged_prefill", "single_decode"],
                     help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
@@ -638,7 +662,8 @@ def main():
     if world == 1 and not strong and args.sequences == 0:
         secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev),
                      "decode_step_cache_write": measure_decode_step_write(compute, dev),
-                     "paged_prefill": measure_paged_prefill(compute, dev)}
+                     "paged_prefill": measure_paged_prefill(compute, dev),
+                     "single_sequence_decode": measure_single_decode(compute, dev)}
 
     if rank == 0:
         line = {

@@ -487,10 +487,20 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
 }
 
 // ------------------------------------------------------------------------------------ merge
-// grid (batch, num_heads), 128 threads (one per output dim).  Combines the partials of a
-// sequence that was cut by CTA range boundaries:  out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c.
-__global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
-    const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
+// grid (batch, num_heads), 256 threads.  Combines the partials of a sequence that was cut by CTA
+// range boundaries:  out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c.  A single long sequence is cut
+// by every CTA (a batch of one leaves as many partials as there are SMs), so the partials are
+// spread over the block: one thread per partial for the maxima and weights, one warp per eighth
+// of the partials (a lane per four output dims) for the weighted sum.
+constexpr int kMergeThreads = 256;
+constexpr int kMaxMergeParts = 256;  // >= the largest grid the decode kernel is launched with
+__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParams p) {
+    __shared__ float s_w[kMaxMergeParts];
+    __shared__ int s_slot[kMaxMergeParts];
+    __shared__ float s_red[kMergeThreads / 32];
+    __shared__ float s_red2[kMergeThreads / 32];
+    __shared__ float4 s_acc[kMergeThreads / 32][32];
+    const int b = blockIdx.x, hq = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int total = p.page_prefix[p.batch];
     if (total == 0) return;
     const int s0 = p.page_prefix[b], s1 = p.page_prefix[b + 1];
@@ -507,25 +517,62 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
     };
     const int c_lo = cta_of(A), c_hi = cta_of(B - 1);
     if (c_lo == c_hi) return;  // whole sequence inside one range: already final
+    const int n = min(c_hi - c_lo + 1, kMaxMergeParts);
     // The first contributing range may hold the sequence as its second partial (slot 1); every
     // later one starts inside the sequence, so the sequence is its first segment (slot 0).
     // Ranges in between can be empty when there are fewer pages than CTAs: those wrote nothing.
-    const int slot_lo = 2 * c_lo + (range_start(T, p.n_ctas, c_lo) >= A ? 0 : 1);
-    float M = p.part_ml[(size_t)slot_lo * p.num_heads + hq].x;
-    for (int c = c_lo + 1; c <= c_hi; c++) {
-        if (range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
-        M = fmaxf(M, p.part_ml[(size_t)(2 * c) * p.num_heads + hq].x);
+    float m_own = -INFINITY, l_own = 0.f;
+    int slot_own = -1;
+    if (tid < n) {
+        const int c = c_lo + tid;
+        const bool empty = tid > 0 && range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1);
+        if (!empty) {
+            slot_own = tid == 0 ? 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1) : 2 * c;
+            const float2 ml = p.part_ml[(size_t)slot_own * p.num_heads + hq];
+            m_own = ml.x;
+            l_own = ml.y;
+        }
     }
-    float acc = 0.f, L = 0.f;
-    for (int c = c_lo; c <= c_hi; c++) {
-        if (c != c_lo && range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1)) continue;
-        const int slot = c == c_lo ? slot_lo : 2 * c;
-        const float2 ml = p.part_ml[(size_t)slot * p.num_heads + hq];
-        const float w = fast_exp2(ml.x - M);
-        acc += w * p.part_o[((size_t)slot * p.num_heads + hq) * kHeadDim + d];
-        L += w * ml.y;
+    float M = m_own;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+    if (lane == 0) s_red[warp] = M;
+    __syncthreads();
+    M = s_red[0];
+#pragma unroll
+    for (int w = 1; w < kMergeThreads / 32; w++) M = fmaxf(M, s_red[w]);
+    const float w_own = slot_own >= 0 ? fast_exp2(m_own - M) : 0.f;
+    if (tid < n) {
+        s_w[tid] = w_own;
+        s_slot[tid] = slot_own;
     }
-    p.out[((size_t)b * p.num_heads + hq) * kHeadDim + d] = acc / L;
+    float L = w_own * l_own;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) L += __shfl_xor_sync(0xffffffffu, L, sh);
+    if (lane == 0) s_red2[warp] = L;
+    __syncthreads();
+    L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMergeThreads / 32; w++) L += s_red2[w];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = warp; i < n; i += kMergeThreads / 32) {
+        const int slot = s_slot[i];
+        if (slot < 0) continue;
+        const float w = s_w[i];
+        const float4 o = *(reinterpret_cast<const float4*>(p.part_o + ((size_t)slot * p.num_heads + hq) * kHeadDim) + lane);
+        acc.x += w * o.x;
+        acc.y += w * o.y;
+        acc.z += w * o.z;
+        acc.w += w * o.w;
+    }
+    s_acc[warp][lane] = acc;
+    __syncthreads();
+    if (tid < kHeadDim) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; w++) sum += reinterpret_cast<const float*>(&s_acc[w][0])[tid];
+        p.out[((size_t)b * p.num_heads + hq) * kHeadDim + tid] = sum / L;
+    }
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -576,7 +623,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.n_head_tiles = hkv / tile_heads;
     p.heads_per_warp = heads_per_warp;
     p.active_warps = subs_active * tile_heads;
-    p.n_ctas = c->sm_count;
+    p.n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds one partial per thread
     p.contiguous = contiguous ? 1 : 0;
     p.max_seq = (int)max_seq;
     p.scale_log2 = a.scale * 1.4426950408889634f;
@@ -629,7 +676,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     }
     {
         LaunchScope t(c, "decode_merge");
-        decode_merge_kernel<<<dim3(p.batch, p.num_heads), 128, 0, c->stream>>>(p);
+        decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, c->stream>>>(p);
     }
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
@@ -824,7 +871,7 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
         paged_decode_kernel<1><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
     else
         paged_decode_kernel<2><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
-    decode_merge_kernel<<<dim3(p.batch, p.num_heads), 128, 0, st>>>(p);
+    decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, st>>>(p);
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }
