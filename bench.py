@@ -452,6 +452,7 @@ def main():
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
     ap.add_argument("--only", default="", choices=["", "prefill", "tree", "step_write", "paged_prefill", "single_decode"],
                     help="run just one of the secondary workloads (profiling captures)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (profiling captures)")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
     args = ap.parse_args()
@@ -678,7 +679,7 @@ def main():
                          f"best of 2, {secs:.2f} s each"}
 
     secondary = None
-    if world == 1 and not strong and args.sequences == 0:
+    if world == 1 and not strong and args.sequences == 0 and not args.no_secondary:
         secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev),
                      "decode_step_cache_write": measure_decode_step_write(compute, dev),
                      "paged_prefill": measure_paged_prefill(compute, dev),
