@@ -183,6 +183,7 @@ _sig("granite_cuda_rope_multihead", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
 _sig("granite_cuda_rope_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(RopeAppendArgs))
 _sig("granite_cuda_tree_commit", C.c_int, C.c_void_p, C.POINTER(TreeCommitArgs))
 _sig("granite_cuda_paged_prefill_attention", C.c_int, C.c_void_p, C.POINTER(PagedPrefillArgs))
+_sig("granite_cuda_selftest_bounded_wait", C.c_int, C.c_void_p, C.c_uint64, C.c_void_p)
 _sig("granite_cuda_push_rows", C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_uint32,
      C.c_uint64, C.c_uint64)
 _sig("granite_cuda_batched_paged_attention_decode_static", C.c_int, C.POINTER(PagedDecodeArgs), C.c_void_p,
@@ -369,6 +370,9 @@ class CudaCompute:
                              num_kv_heads, seq_q, start_pos, head_dim, block_size, max_blocks_per_seq, num_blocks,
                              q_dtype, out_dtype, scale)
         check(lib.granite_cuda_paged_prefill_attention(self._h, C.byref(a)))
+
+    def selftest_bounded_wait(self, limit_cycles: int, released_early) -> None:
+        check(lib.granite_cuda_selftest_bounded_wait(self._h, limit_cycles, C.c_void_p(_ptr(released_early))))
 
     def push_rows(self, src, dst_ptrs, dst_offset_bytes: int, nbytes: int, stream: int | None = None) -> None:
         """Stores `nbytes` bytes of `src` at every address in `dst_ptrs` (+ offset): local or peer-mapped buffers."""

@@ -419,6 +419,12 @@ int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const Granit
     return launch_paged_prefill(c, *args);
 }
 
+int granite_cuda_selftest_bounded_wait(granite_cuda_compute_t* c, uint64_t limit_cycles, int32_t* released_early) {
+    if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "selftest: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    return launch_bounded_wait_selftest(c, limit_cycles, released_early);
+}
+
 int granite_cuda_push_rows(granite_cuda_compute_t* c, void* stream, const void* src, void* const* dst_ptrs,
                            uint32_t n_dst, uint64_t dst_offset_bytes, uint64_t bytes) {
     if (!c) return fail(GRANITE_CUDA_NULL_POINTER, "push_rows: null argument");

@@ -119,6 +119,7 @@ int launch_rope_multihead(granite_cuda_compute* c, float* q, float* k, uint32_t 
 int launch_rope_paged_append(granite_cuda_compute* c, const GraniteCudaRopeAppendArgs& a);
 int launch_tree_commit(granite_cuda_compute* c, const GraniteCudaTreeCommitArgs& a);
 int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a);
+int launch_bounded_wait_selftest(granite_cuda_compute* c, uint64_t limit_cycles, int* released_early_dev);
 int launch_push_rows(granite_cuda_compute* c, cudaStream_t stream, const void* src, void* const* dst_ptrs, uint32_t n_dst,
                      uint64_t dst_offset_bytes, uint64_t bytes);
 }  // namespace gb200

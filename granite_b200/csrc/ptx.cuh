@@ -45,14 +45,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets one timed-out role release the others early.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit = kWaitCycleLimit) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycleLimit) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             return false;
         }

@@ -9,6 +9,7 @@
 // output rounded separately (__fmul_rn / __fsub_rn / __fadd_rn keep the compiler from fusing them),
 // then the truncating fp32 -> fp16 cast of src/llm/math_ops.cpp:45-54 for what goes into the cache.
 #include "compute_internal.h"
+#include "ptx.cuh"
 
 namespace gb200 {
 
@@ -177,6 +178,28 @@ __global__ void push_rows_kernel(PushParams p) {
     }
 }
 
+// The bounded wait every pipeline role uses, exercised on purpose: thread 0 waits on a barrier
+// that nothing will ever arrive at and gives up after `limit_cycles`; a second waiter with the full
+// limit must be released early by the abort flag the first one raises.  Ends by itself.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles, int* released_early) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) != 0) return;
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(&bar, 0, &abort_flag, threadIdx.x == 0 ? limit_cycles : kWaitCycleLimit);
+    if (threadIdx.x == 0) {
+        if (!ok) atomicOr(status, kStatusTimeout);
+    } else {
+        *released_early = (!ok && clock64() - t0 < 4 * limit_cycles + 1000000) ? 1 : 0;
+    }
+}
+
 unsigned grid_for(size_t total, int sm_count) {
     size_t blocks = (total + 255) / 256;
     const size_t cap = (size_t)sm_count * 8;
@@ -276,6 +299,16 @@ int launch_tree_commit(granite_cuda_compute* c, const GraniteCudaTreeCommitArgs&
     const size_t total = (size_t)a.batch_size * a.max_accepted * a.num_kv_heads * p.row_vecs;
     LaunchScope t(c, "tree_commit");
     tree_commit_kernel<<<grid_for(total, c->sm_count), 256, 0, c->stream>>>(p);
+    GB_CUDA_TRY(cudaGetLastError());
+    return GRANITE_CUDA_SUCCESS;
+}
+
+int launch_bounded_wait_selftest(granite_cuda_compute* c, uint64_t limit_cycles, int* released_early_dev) {
+    if (!released_early_dev) return fail(GRANITE_CUDA_NULL_POINTER, "selftest: null buffer");
+    if (limit_cycles == 0 || limit_cycles > 200000000ull)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "selftest: limit must be in [1, 2e8] cycles (about 0.1 s)");
+    LaunchScope t(c, "bounded_wait_selftest");
+    bounded_wait_selftest_kernel<<<1, 64, 0, c->stream>>>(c->d_status, (long long)limit_cycles, released_early_dev);
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }

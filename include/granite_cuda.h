@@ -424,6 +424,16 @@ int granite_cuda_paged_prefill_attention(granite_cuda_compute_t* c, const Granit
 int granite_cuda_push_rows(granite_cuda_compute_t* c, void* stream, const void* src, void* const* dst_ptrs,
                            uint32_t n_dst, uint64_t dst_offset_bytes, uint64_t bytes);
 
+/* ---- self-test of the bounded device waits -------------------------------------------------------
+ * Every wait inside the kernels (on an mbarrier fed by TMA, by the tensor pipe or by another role)
+ * gives up after a cycle limit, raises the status word and releases the other roles through an
+ * abort flag, so that a lost signal ends as an error code and never as a hung GPU.  This call runs
+ * that mechanism on purpose: one thread waits on a barrier nothing arrives at and expires after
+ * limit_cycles (<= 2e8, about 0.1 s); a second waiter must leave early through the abort flag
+ * (*released_early, device int, is set to 1).  The next granite_cuda_sync returns Timeout and clears
+ * the status; the compute object stays usable.  No reference counterpart. */
+int granite_cuda_selftest_bounded_wait(granite_cuda_compute_t* c, uint64_t limit_cycles, int32_t* released_early);
+
 #ifdef __cplusplus
 }
 #endif

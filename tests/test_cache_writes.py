@@ -342,3 +342,25 @@ def test_push_rows_copies_to_every_destination(compute):
     with pytest.raises(GraniteCudaError) as e:
         compute.push_rows(src, [dsts[0]] * 17, 0, nbytes)
     assert e.value.code == ErrorCode.InvalidArgument
+
+
+def test_an_expired_device_wait_ends_as_an_error_code(compute):
+    """The safety net under every pipeline: a wait whose signal never comes expires, the status word
+    reaches the host as Timeout, a second waiter leaves through the abort flag, and the same compute
+    object goes on working."""
+    import torch
+    released = torch.zeros(1, dtype=torch.int32, device=DEV)
+    compute.selftest_bounded_wait(2_000_000, released)  # about one millisecond
+    with pytest.raises(GraniteCudaError) as e:
+        compute.sync()
+    assert e.value.code == ErrorCode.Timeout
+    assert int(released.item()) == 1
+    compute.sync()  # cleared
+    src = torch.arange(1024, dtype=torch.float32, device=DEV)
+    dst = torch.zeros_like(src)
+    compute.push_rows(src, [dst], 0, 4096)
+    compute.sync()
+    assert torch.equal(src, dst)
+    with pytest.raises(GraniteCudaError) as e:
+        compute.selftest_bounded_wait(10**10, released)  # limits above 0.1 s are refused
+    assert e.value.code == ErrorCode.InvalidArgument
