@@ -13,8 +13,8 @@
 //                         lives in the paged pool (block table) as well as in a contiguous cache.
 //
 // One pipeline serves both.  A work item is one or two 128-row query tiles that share every K/V
-// tile (prefill: the two query heads of a GQA pair at one query block; tree: the four query heads
-// of a group, 2 heads x 64 node slots per tile) and the K/V tiles they may see.  CTAs are
+// tile (prefill: one query head at one query block; tree: the four query heads of a group, 2 heads x
+// 64 node slots per tile) and the K/V tiles they may see.  CTAs are
 // persistent, one per SM, and run their items back to back.  A "virtual step" is (K/V tile j,
 // query tile t); S of consecutive virtual steps alternates between two TMEM buffers, so the score
 // MMAs of the next virtual step run while the softmax of the current one is still working.
@@ -26,11 +26,14 @@
 //               "hi" part of P, warp 3 the "lo" part (P from TMEM, V from shared memory,
 //               MN-major).  A single thread cannot issue 128x128x16 instructions fast enough to
 //               keep the tensor pipe busy; three can.
-//   warps 4-11  softmax: both warpgroups work on the same 128 rows, the first on key columns
-//               0-63 of the tile, the second on 64-127; row maxima and sums are exchanged through
-//               shared memory.  thread = query row; S is read with tcgen05.ld, P is written back
-//               over S as fp16 hi + lo (P keeps ~22 bits, as the fp32 reference does); the
-//               running maximum is only raised when it grows by more than 2^8 (lazy rescale of O)
+//   warps 4-11  softmax: the two warps that may touch a TMEM lane quarter take 16 of its 32 rows
+//               each and read S in the 16-lane fragment shape of tcgen05.ld, which spreads a row's
+//               128 columns over the four threads of a quad: row maxima and sums are two shuffles,
+//               nothing goes through shared memory and no warp waits for another inside a step.
+//               P is written back over S as fp16 hi + lo (P keeps ~22 bits, as the fp32 reference
+//               does); the running maximum is only raised when it grows by more than 2^8 (lazy
+//               rescale of O).  With one tile per item O alternates between the two accumulators and
+//               a finished item is read out behind the next item's first MMAs.
 // TMEM (512 columns): S[0] | S[1] | O[0] | O[1], 128 fp32 columns each.
 #include <cstdio>
 #include <cstring>
@@ -82,9 +85,8 @@ struct TcSmem {
     uint64_t s_full[2], s_free[2], p_ready[2], o_final;
     uint32_t tmem_base;
     int abort_flag;
-    float xchg[2][2][kT];  // [virtual-step parity][warpgroup][row]: row maxima / sums between the warpgroups
 };
-static_assert(sizeof(TcSmem) <= 3072, "barriers and exchange slots must fit beside seven 32 KB tiles");
+static_assert(sizeof(TcSmem) <= 3072, "the barriers must fit beside seven 32 KB tiles");
 
 struct TcItem {
     int head0;      // first query head of the item
@@ -133,9 +135,6 @@ __global__ void tree_mask_kernel(const int32_t* parents, unsigned long long* mas
     masks[idx] = ancestor_word(p, i, n);
 }
 
-__device__ __forceinline__ void softmax_group_sync() {
-    asm volatile("bar.sync 1, 256;" ::: "memory");  // the two softmax warpgroups only
-}
 
 // kTree:   tree verification (else causal prefill).   kPaged: tree prefix in the paged pool.
 // kSplitQ: queries given as fp16 hi + lo arrays (fp32 queries): S = Q_hi K^T + Q_lo K^T; one tile only.
@@ -148,7 +147,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     static_assert(!(kSplitQ && kTiles == 2), "split queries take both query slots");
     constexpr int kQSlots = kSplitQ ? 2 : kTiles;
     constexpr int kStages = kQSlots == 1 ? 3 : 2;
-    // barriers and exchange slots first, then the 1024-byte aligned tiles (128-byte swizzle atoms)
+    // barriers first, then the 1024-byte aligned tiles (128-byte swizzle atoms)
     extern __shared__ __align__(16) uint8_t smem_raw[];
     TcSmem* sh = reinterpret_cast<TcSmem*>(smem_raw);
     uint8_t* q_smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + sizeof(TcSmem) + 1023) & ~uintptr_t(1023));
@@ -451,12 +450,12 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             if (part == 0) FA_TRACE(1, vs, 1);
                             tc_fence_after_sync();
                             const uint32_t d = tmem + 2 * kT + (t + o_sel) * kT;
-                            // P: each 64-column half of S_b became 32 columns of hi + 32 of lo (8 columns per
-                            // 16 keys); V MN-major: 16 keys = 2 KB further per step, second 64 dims via LBO
+                            // P: hi in columns 0-63 of S_b, lo in 64-127, 8 columns per 16 keys;
+                            // V MN-major: 16 keys = 2 KB further per step, second 64 dims via LBO
 #pragma unroll
                             for (int ks = 0; ks < 8; ks++) {
                                 if (ks < nks) {
-                                    const uint32_t a = tmem + b * kT + (ks >> 2) * 64 + (ks & 3) * 8 + part * 32;
+                                    const uint32_t a = tmem + b * kT + part * 64 + ks * 8;
                                     umma_ts_words(d, a, v_lo + ks * (2048 >> 4), kDescHiSw128, idesc_pv, 1u);
                                 }
                             }
@@ -478,109 +477,96 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     } else {
         setmaxnreg_inc<224>();
         // ------------------------------------------------------------------ softmax + epilogue
-        // Both warpgroups work on every virtual step, the first on key columns 0-63, the second on
-        // 64-127; row maxima and sums go through shared memory.  (Giving each warpgroup a whole tile
-        // of its own - 128 columns per thread, no exchange - measured 35 % slower.)
-        constexpr bool kColSplit = true;
-        constexpr int kChunks = 2;   // 32-column chunks of S per thread
+        // Rows are split, not columns: the two warps that may touch a TMEM lane quarter take 16 of
+        // its 32 rows each, and read S in the 16-lane fragment shape, which spreads a row's 128
+        // columns over the four threads of a quad.  Row maxima and sums are then two shuffles inside
+        // the quad - no shared memory, no barrier between the warps, and every warp overwrites only
+        // rows it has itself read.  Each thread works on two rows (g and g + 8 of its 16) x 32 columns.
         const int wg = (warp - 4) >> 2;
         const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
-        const int row = quarter * 32 + lane;     // query row inside the tile
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-        const int col0 = kColSplit ? wg * 64 : 0;  // first S / O column of this thread
-        const int node = row & (kNodeSlots - 1); // tree: node slot of this row
+        const int tq = lane & 3;                 // position in the quad: columns 8i + 2 tq + {0, 1}
+        const int row_of[2] = {quarter * 32 + wg * 16 + (lane >> 2), quarter * 32 + wg * 16 + (lane >> 2) + 8};
+        const uint32_t frag_base = tmem + (static_cast<uint32_t>(quarter * 32 + wg * 16) << 16);
+        const int row = quarter * 32 + lane;     // 0..127 over the first warpgroup: work index for clearing a V tail
         bool ok = true;
         int vs = 0, kvs = 0, items_done = 0;     // virtual steps, K/V steps, items handled so far
 
         // Read-out of a finished item.  With one tile per item it is deferred: the item's O stays in
-        // its accumulator while the next item starts in the other one, and one 32-column chunk is
+        // its accumulator while the next item starts in the other one, and one 64-column half is
         // written after each of the next item's first softmax steps, behind the MMAs of those steps.
         constexpr bool kDefer = kTiles == 1;
+        constexpr int kHalves = 2;
         struct Readout {
-            int chunks_left;     // 0: nothing pending
+            int halves_left;     // 0: nothing pending
             uint32_t phase;      // o_final parity of the item
-            uint32_t o_addr;     // this thread's first O column in TMEM
-            float inv;           // 1 / row sum
-            bool store;          // this row is a live output row
-            size_t base;         // element offset of this thread's first output value
-            int rows_in_quad;    // prefill, fp16 output: live rows among the four of this lane's quad
-            size_t quad_base;    // same path: element offset of the quad's first row, at this lane's 8 columns
+            uint32_t o_frag;     // the item's O accumulator, this warp's 16 lanes
+            float inv[2];        // 1 / row sum of the thread's two rows
+            bool store[2];       // the row is a live output row
+            size_t base[2];      // element offset of the row's first output value
         } pend;
-        pend.chunks_left = 0;
-        auto readout_chunk = [&](Readout& e) {
-            const int ch = kChunks - e.chunks_left;
-            if (ch == 0) {
+        pend.halves_left = 0;
+        auto readout_half = [&](Readout& e) {
+            const int h = kHalves - e.halves_left;
+            if (h == 0) {
                 if (ok) ok = mbar_wait(&sh->o_final, e.phase, abort_flag);
                 tc_fence_after_sync();
             }
-            e.chunks_left--;
+            e.halves_left--;
             if (!ok) return;
             uint32_t rr[32];
             __syncwarp();
-            tmem_ld32(e.o_addr + ch * 32, rr);
+            tmem_ld_16x256b_x8(e.o_frag + h * 64, rr);
             tmem_wait_ld();
             if (!kTree && p.out_fp16) {
-                // four 16-byte pieces per row; a 4 x 4 exchange inside each quad of lanes makes every
-                // store instruction write 64 contiguous bytes per row instead of 16
-                uint4 x[4];
+                // a thread holds pairs of columns; a 4 x 4 exchange inside the quad turns four pairs of
+                // one 8-column group into one 16-byte piece per lane: the quad then writes 64
+                // contiguous bytes of a row per store instruction
 #pragma unroll
-                for (int v = 0; v < 4; v++) {
-                    x[v].x = pack_half2(__uint_as_float(rr[v * 8 + 0]) * e.inv, __uint_as_float(rr[v * 8 + 1]) * e.inv);
-                    x[v].y = pack_half2(__uint_as_float(rr[v * 8 + 2]) * e.inv, __uint_as_float(rr[v * 8 + 3]) * e.inv);
-                    x[v].z = pack_half2(__uint_as_float(rr[v * 8 + 4]) * e.inv, __uint_as_float(rr[v * 8 + 5]) * e.inv);
-                    x[v].w = pack_half2(__uint_as_float(rr[v * 8 + 6]) * e.inv, __uint_as_float(rr[v * 8 + 7]) * e.inv);
+                for (int r = 0; r < 2; r++) {
+#pragma unroll
+                    for (int blk = 0; blk < 2; blk++) {
+                        uint32_t v[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            v[i] = pack_half2(__uint_as_float(rr[4 * (4 * blk + i) + 2 * r]) * e.inv[r],
+                                              __uint_as_float(rr[4 * (4 * blk + i) + 2 * r + 1]) * e.inv[r]);
+                        quad_transpose(v, lane);  // now: columns 8 (4 blk + tq) .. + 7 of the row
+                        if (e.store[r])
+                            *reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + e.base[r] + h * 64 + 8 * (4 * blk + tq)) =
+                                make_uint4(v[0], v[1], v[2], v[3]);
+                    }
                 }
-                auto swap4 = [&](uint4 give, int mask) {
-                    uint4 got;
-                    got.x = __shfl_xor_sync(0xffffffffu, give.x, mask);
-                    got.y = __shfl_xor_sync(0xffffffffu, give.y, mask);
-                    got.z = __shfl_xor_sync(0xffffffffu, give.z, mask);
-                    got.w = __shfl_xor_sync(0xffffffffu, give.w, mask);
-                    return got;
-                };
-                const bool i0 = lane & 1, i1 = lane & 2;
-                uint4 z[4], y[4];
-                // stage 1 (lane ^ 1): z[u + w] = piece u + i0 of the row with low bit w
-#pragma unroll
-                for (int u = 0; u < 4; u += 2) {
-                    const uint4 got = swap4(i0 ? x[u] : x[u + 1], 1);
-                    z[u] = i0 ? got : x[u];
-                    z[u + 1] = i0 ? x[u + 1] : got;
-                }
-                // stage 2 (lane ^ 2): y[s] = piece (lane & 3) of row s of the quad
-#pragma unroll
-                for (int w = 0; w < 2; w++) {
-                    const uint4 got = swap4(i1 ? z[w] : z[2 + w], 2);
-                    y[w] = i1 ? got : z[w];
-                    y[2 + w] = i1 ? z[2 + w] : got;
-                }
-                __half* outp = static_cast<__half*>(p.out) + e.quad_base + ch * 32;
-#pragma unroll
-                for (int sr = 0; sr < 4; sr++)
-                    if (sr < e.rows_in_quad) *reinterpret_cast<uint4*>(outp + (size_t)sr * p.num_heads * kT) = y[sr];
-            } else if (e.store) {
+            } else {
                 float* outp = kTree ? p.tree_out : static_cast<float*>(p.out);
-                float4* dst = reinterpret_cast<float4*>(outp + e.base + ch * 32);
 #pragma unroll
-                for (int v = 0; v < 8; v++)
-                    dst[v] = make_float4(__uint_as_float(rr[v * 4 + 0]) * e.inv, __uint_as_float(rr[v * 4 + 1]) * e.inv,
-                                         __uint_as_float(rr[v * 4 + 2]) * e.inv, __uint_as_float(rr[v * 4 + 3]) * e.inv);
+                for (int r = 0; r < 2; r++)
+                    if (e.store[r]) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++)  // a quad writes 32 contiguous bytes of the row
+                            *reinterpret_cast<float2*>(outp + e.base[r] + h * 64 + 8 * i + 2 * tq) =
+                                make_float2(__uint_as_float(rr[4 * i + 2 * r]) * e.inv[r], __uint_as_float(rr[4 * i + 2 * r + 1]) * e.inv[r]);
+                    }
             }
         };
 
         for (int r = 0; r < n_rounds; r++) {
             const TcItem it = item_of(r);
             if (!it.valid) continue;
-            // prefill: the last key this row may see; tree: the row's ancestor word
-            const int q_pos = it.q0 + row;
-            const int last_visible = kTree ? it.cache_len - 1 : min(p.start_pos + q_pos, p.seq_kv - 1);
-            unsigned long long anc = 1ull;
-            if (kTree && node < N) {
-                const int32_t* par = p.parents + (size_t)it.b * N;
-                if (par[node] < -1 || par[node] >= N) atomicOr(p.status, kStatusBadParent);
-                anc = ancestor_word(par, node, N);
+            // prefill: the last key a row may see; tree: the row's ancestor word, pre-shifted to this
+            // thread's first column
+            int last_visible[2];
+            unsigned long long anc[2] = {1ull >> (2 * tq), 1ull >> (2 * tq)};  // rows past the last node see column 0 only
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                last_visible[q] = kTree ? it.cache_len - 1 : min(p.start_pos + it.q0 + row_of[q], p.seq_kv - 1);
+                const int node = row_of[q] & (kNodeSlots - 1);
+                if (kTree && node < N) {
+                    const int32_t* par = p.parents + (size_t)it.b * N;
+                    if (par[node] < -1 || par[node] >= N) atomicOr(p.status, kStatusBadParent);
+                    anc[q] = ancestor_word(par, node, N) >> (2 * tq);
+                }
             }
-            float m_used_t[kTiles], l_run_t[kTiles];  // running maximum and sum of this row, per query tile
+            float m_used_t[kTiles][2], l_run_t[kTiles][2];  // running maximum and (per-thread part of the) sum, per tile and row
             const int o_sel = kDefer ? (items_done & 1) : 0;  // accumulator of this item (see the output MMAs)
             {
                 // O starts at zero so that every output MMA can accumulate
@@ -589,10 +575,13 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 for (int c = 0; c < 32; c++) z[c] = 0u;
 #pragma unroll
                 for (int t = 0; t < kTiles; t++) {
-                    m_used_t[t] = -INFINITY;
-                    l_run_t[t] = 0.f;
 #pragma unroll
-                    for (int ch = 0; ch < kChunks; ch++) tmem_st32(lane_base + 2 * kT + (t + o_sel) * kT + col0 + ch * 32, z);
+                    for (int q = 0; q < 2; q++) {
+                        m_used_t[t][q] = -INFINITY;
+                        l_run_t[t][q] = 0.f;
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; h++) tmem_st_16x256b_x8(frag_base + 2 * kT + (t + o_sel) * kT + h * 64, z);  // own rows only
                 }
                 tmem_wait_st();
             }
@@ -602,114 +591,126 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 // prefill: the diagonal tile and a ragged last tile; tree prefix: a ragged last tile
                 const bool need_mask = kTree ? (!tree_step && k0 + kT > it.cache_len)
                                              : ((k0 + kT - 1 > p.start_pos + it.q0) || (k0 + kT > p.seq_kv));
-                const int limit = last_visible - k0 - col0;                    // own column c is visible iff c <= limit
-                const bool has_cols = !(tree_step && kColSplit && wg == 1);   // the tree tile has 64 key columns only
-                // not unrolled: the two tiles of an item share one copy of the softmax code, which
-                // otherwise outgrows the instruction cache (measured: +20 % per step when unrolled)
+                // not unrolled: the two tiles of an item share one copy of the softmax code
 #pragma unroll 1
                 for (int t = 0; t < kTiles; t++, vs++) {
-                    float m_used = (kTiles == 2 && t) ? m_used_t[kTiles - 1] : m_used_t[0];
-                    float l_run = (kTiles == 2 && t) ? l_run_t[kTiles - 1] : l_run_t[0];
+                    const int ti = (kTiles == 2 && t) ? kTiles - 1 : 0;
+                    float m_used[2] = {m_used_t[ti][0], m_used_t[ti][1]};
+                    float l_run[2] = {l_run_t[ti][0], l_run_t[ti][1]};
                     const int b = vs & 1;
-                    const uint32_t s_addr = lane_base + b * kT + col0;
-                    const uint32_t o_addr = lane_base + 2 * kT + (t + o_sel) * kT + col0;
+                    const uint32_t s_frag = frag_base + b * kT;
+                    const uint32_t o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
                     if (warp == 4) FA_TRACE(2, vs, 0);
                     if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
                     if (warp == 4) FA_TRACE(2, vs, 1);
-                    if (!ok) {  // keep the barrier count intact so nobody is left waiting
-                        if (kColSplit) softmax_group_sync();
-                        continue;
-                    }
+                    if (!ok) continue;  // a role gave up: nothing below synchronises with another warp
                     tc_fence_after_sync();
-                    // this thread's scores into registers: all loads in flight, one wait
-                    uint32_t x[kChunks][32];
-                    if (has_cols) {
-#pragma unroll
-                        for (int ch = 0; ch < kChunks; ch++)
-                            if (!(tree_step && ch >= 2)) tmem_ld32(s_addr + ch * 32, x[ch]);
-                        tmem_wait_ld();
-                    }
-                    if (warp == 4) FA_TRACE(6, vs, 0);
+                    // the two rows' scores: x[h][4i + 2q + e] = row q, column 64 h + 8 i + 2 tq + e
+                    uint32_t x[2][32];
+                    tmem_ld_16x256b_x8(s_frag, x[0]);
+                    if (!tree_step) tmem_ld_16x256b_x8(s_frag + 64, x[1]);  // the tree tile has 64 key columns only
+                    tmem_wait_ld();
                     if (tree_step) {
 #pragma unroll
-                        for (int ch = 0; ch < kChunks; ch++)
+                        for (int i = 0; i < 8; i++)
 #pragma unroll
-                            for (int c = 0; c < 32; c++)
-                                if (!has_cols || ch >= 2 || !((anc >> (ch * 32 + c)) & 1ull)) x[ch][c] = kNegInf;
+                            for (int q = 0; q < 2; q++)
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {
+                                    if (!((anc[q] >> (8 * i + e)) & 1ull)) x[0][4 * i + 2 * q + e] = kNegInf;
+                                    x[1][4 * i + 2 * q + e] = kNegInf;
+                                }
                     } else if (need_mask) {
 #pragma unroll
-                        for (int ch = 0; ch < kChunks; ch++)
+                        for (int q = 0; q < 2; q++) {
+                            const int limit = last_visible[q] - k0 - 2 * tq;  // own column 64 h + 8 i + e is visible iff <= limit
 #pragma unroll
-                            for (int c = 0; c < 32; c++)
-                                if (ch * 32 + c > limit) x[ch][c] = kNegInf;
-                    }
-                    float mx;
-                    {
-                        float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+                            for (int h = 0; h < 2; h++)
 #pragma unroll
-                        for (int ch = 0; ch < kChunks; ch++)
+                                for (int i = 0; i < 8; i++)
 #pragma unroll
-                            for (int c = 0; c < 32; c += 2) {
-                                const int k = (kChunks == 4) ? ch : ch * 2 + ((c >> 1) & 1);
-                                mm[k] = max3(mm[k], __uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1]));
-                            }
-                        mx = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+                                    for (int e = 0; e < 2; e++)
+                                        if (64 * h + 8 * i + e > limit) x[h][4 * i + 2 * q + e] = kNegInf;
+                        }
                     }
-                    if (kColSplit) {
-                        // the other warpgroup holds the other 64 columns of the same row
-                        sh->xchg[b][wg][row] = mx;
-                        softmax_group_sync();
-                        mx = fmaxf(mx, sh->xchg[b][wg ^ 1][row]);
+                    float mx[2];
+#pragma unroll
+                    for (int q = 0; q < 2; q++) {
+                        float mm[2] = {-INFINITY, -INFINITY};  // independent chains
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                                mm[h] = max3(mm[h], __uint_as_float(x[h][4 * i + 2 * q]), __uint_as_float(x[h][4 * i + 2 * q + 1]));
+                        float m = fmaxf(mm[0], mm[1]);
+                        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                        mx[q] = m * p.scale_log2;
                     }
-                    mx *= p.scale_log2;
                     if (warp == 4) FA_TRACE(6, vs, 1);
                     if (j == 0) {
-                        m_used = mx;
+                        m_used[0] = mx[0];
+                        m_used[1] = mx[1];
                     } else {
-                        const bool grow = mx > m_used + kLazyLog2;
-                        if (__any_sync(0xffffffffu, grow)) {
+                        const bool grow0 = mx[0] > m_used[0] + kLazyLog2, grow1 = mx[1] > m_used[1] + kLazyLog2;
+                        if (__any_sync(0xffffffffu, grow0 || grow1)) {
                             // O_t must be quiescent: wait until both halves of its previous output MMA are done
                             ok = mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag);
                             tc_fence_after_sync();
-                            const float alpha = grow ? fast_exp2(m_used - mx) : 1.0f;
-                            if (grow) m_used = mx;
-                            l_run *= alpha;
+                            const float alpha0 = grow0 ? fast_exp2(m_used[0] - mx[0]) : 1.0f;
+                            const float alpha1 = grow1 ? fast_exp2(m_used[1] - mx[1]) : 1.0f;
+                            if (grow0) m_used[0] = mx[0];
+                            if (grow1) m_used[1] = mx[1];
+                            l_run[0] *= alpha0;
+                            l_run[1] *= alpha1;
                             uint32_t rr[32];
 #pragma unroll 1
-                            for (int ch = 0; ch < kChunks; ch++) {
-                                tmem_ld32(o_addr + ch * 32, rr);
+                            for (int h = 0; h < 2; h++) {
+                                tmem_ld_16x256b_x8(o_frag + h * 64, rr);
                                 tmem_wait_ld();
 #pragma unroll
-                                for (int c = 0; c < 32; c++) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * alpha);
-                                tmem_st32(o_addr + ch * 32, rr);
+                                for (int i = 0; i < 8; i++) {
+                                    rr[4 * i + 0] = __float_as_uint(__uint_as_float(rr[4 * i + 0]) * alpha0);
+                                    rr[4 * i + 1] = __float_as_uint(__uint_as_float(rr[4 * i + 1]) * alpha0);
+                                    rr[4 * i + 2] = __float_as_uint(__uint_as_float(rr[4 * i + 2]) * alpha1);
+                                    rr[4 * i + 3] = __float_as_uint(__uint_as_float(rr[4 * i + 3]) * alpha1);
+                                }
+                                tmem_st_16x256b_x8(o_frag + h * 64, rr);
                             }
                         }
                     }
-                    if (has_cols) {
-                        // P = 2^(s*scale - m): each 64-column half of S becomes 32 columns of fp16 hi
-                        // followed by 32 columns of lo
-                        uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};  // independent partial sums, packed pairs of fp32
+                    {
+                        // P = 2^(s*scale - m) as fp16 hi + lo: a pair of neighbouring keys is one 32-bit
+                        // column, hi in columns 0-63 of the S buffer, lo in 64-127.  Every warp has read
+                        // all of its rows' scores before it overwrites them.
                         const uint64_t scale2 = f32x2(p.scale_log2, p.scale_log2);
-                        const uint64_t neg_m2 = f32x2(-m_used, -m_used);
+                        const uint64_t neg_m2[2] = {f32x2(-m_used[0], -m_used[0]), f32x2(-m_used[1], -m_used[1])};
+                        uint64_t ls[2][2] = {{0ull, 0ull}, {0ull, 0ull}};  // [row][chain] partial sums, packed pairs
 #pragma unroll
-                        for (int ch = 0; ch < kChunks; ch++) {
-                            if (tree_step && ch >= 2) continue;
+                        for (int h = 0; h < 2; h++) {
+                            if (tree_step && h == 1) continue;
                             uint32_t hi[16], lo[16];
 #pragma unroll
-                            for (int c = 0; c < 32; c += 2) {
-                                // masked scores are -inf: exp2 gives exactly 0
-                                float t0, t1;
-                                f32x2_get(fma_f32x2(f32x2(__uint_as_float(x[ch][c]), __uint_as_float(x[ch][c + 1])), scale2, neg_m2), t0, t1);
-                                const uint64_t pp = f32x2(fast_exp2(t0), fast_exp2(t1));
-                                ls[(c >> 1) & 3] = add_f32x2(ls[(c >> 1) & 3], pp);
-                                split_hi_lo_x2(pp, hi[c >> 1], lo[c >> 1]);
-                            }
-                            tmem_st16(s_addr + (ch >> 1) * 64 + (ch & 1) * 16, hi);
-                            tmem_st16(s_addr + (ch >> 1) * 64 + 32 + (ch & 1) * 16, lo);
+                            for (int i = 0; i < 8; i++)
+#pragma unroll
+                                for (int q = 0; q < 2; q++) {
+                                    // masked scores are -inf: exp2 gives exactly 0
+                                    float t0, t1;
+                                    f32x2_get(fma_f32x2(f32x2(__uint_as_float(x[h][4 * i + 2 * q]), __uint_as_float(x[h][4 * i + 2 * q + 1])),
+                                                        scale2, neg_m2[q]), t0, t1);
+                                    const uint64_t pp = f32x2(fast_exp2(t0), fast_exp2(t1));
+                                    ls[q][i & 1] = add_f32x2(ls[q][i & 1], pp);
+                                    split_hi_lo_x2(pp, hi[2 * i + q], lo[2 * i + q]);
+                                }
+                            tmem_st_16x128b_x8(s_frag + 32 * h, hi);
+                            tmem_st_16x128b_x8(s_frag + 64 + 32 * h, lo);
                         }
-                        float la, lb;
-                        f32x2_get(add_f32x2(add_f32x2(ls[0], ls[1]), add_f32x2(ls[2], ls[3])), la, lb);
-                        l_run += la + lb;
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            float la, lb;
+                            f32x2_get(add_f32x2(ls[q][0], ls[q][1]), la, lb);
+                            l_run[q] += la + lb;
+                        }
                     }
                     if (t == 0 && wg == 0 && need_mask && k0 + kT > (kTree ? it.cache_len : p.seq_kv)) {
                         // keys past the live length carry P = 0, but their V rows may hold anything (even
@@ -728,62 +729,51 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     __syncwarp();
                     if (warp == 4) FA_TRACE(6, vs, 2);
                     tmem_wait_st();
-                    if (warp == 4) FA_TRACE(6, vs, 3);
                     tc_fence_before_sync();
                     mbar_arrive(&sh->p_ready[b]);
-                    if (kTiles == 2 && t) {
-                        m_used_t[kTiles - 1] = m_used;
-                        l_run_t[kTiles - 1] = l_run;
-                    } else {
-                        m_used_t[0] = m_used;
-                        l_run_t[0] = l_run;
+#pragma unroll
+                    for (int q = 0; q < 2; q++) {
+                        m_used_t[ti][q] = m_used[q];
+                        l_run_t[ti][q] = l_run[q];
                     }
                     if (warp == 4) FA_TRACE(2, vs, 2);
-                    if (kDefer && pend.chunks_left > 0) readout_chunk(pend);  // behind the MMAs of this step
+                    if (kDefer && pend.halves_left > 0) readout_half(pend);  // behind the MMAs of this step
                     if (warp == 4) FA_TRACE(2, vs, 3);
                 }
             }
-            while (kDefer && pend.chunks_left > 0) readout_chunk(pend);  // an item shorter than the read-out
-            // row sums of the two column halves, through the exchange slot the last step did not use
-            // (its readers all passed that step's barrier)
-            float l_total_t[kTiles];
-            if (kTiles == 2) softmax_group_sync();  // both slots were in use by the last two virtual steps
-            const int xs = kTiles == 2 ? 0 : (vs & 1);
-#pragma unroll
-            for (int t = 0; t < kTiles; t++) sh->xchg[xs ^ t][wg][row] = l_run_t[t];
-            softmax_group_sync();
-#pragma unroll
-            for (int t = 0; t < kTiles; t++) l_total_t[t] = l_run_t[t] + sh->xchg[xs ^ t][wg ^ 1][row];
-            softmax_group_sync();  // the slots are reused by the next item's first steps
+            while (kDefer && pend.halves_left > 0) readout_half(pend);  // an item shorter than the read-out
 #pragma unroll
             for (int t = 0; t < kTiles; t++) {
                 Readout e;
-                e.chunks_left = kChunks;
+                e.halves_left = kHalves;
                 e.phase = items_done & 1;
-                e.o_addr = lane_base + 2 * kT + (t + o_sel) * kT + col0;
-                e.inv = 1.0f / l_total_t[t];
-                e.rows_in_quad = 0;
-                e.quad_base = 0;
-                if (kTree) {
-                    const int head = it.head0 + 2 * t + (row >> 6);
-                    e.store = node < N && head < (it.kvh + 1) * p.group;
-                    e.base = (((size_t)it.b * p.num_heads + head) * N + node) * kT + col0;
-                } else {
-                    e.store = row < it.rows_here;
-                    e.base = ((size_t)q_pos * p.num_heads + it.head0 + t) * kT + col0;
-                    const int quad_row = row & ~3;
-                    e.rows_in_quad = it.rows_here - quad_row;  // may be <= 0 or > 4
-                    e.quad_base = ((size_t)(it.q0 + quad_row) * p.num_heads + it.head0 + t) * kT + col0 + (lane & 3) * 8;
+                e.o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    // the row's sum: the quad's four partial sums
+                    float l = l_run_t[t][q];
+                    l += __shfl_xor_sync(0xffffffffu, l, 1);
+                    l += __shfl_xor_sync(0xffffffffu, l, 2);
+                    e.inv[q] = 1.0f / l;
+                    if (kTree) {
+                        const int node = row_of[q] & (kNodeSlots - 1);
+                        const int head = it.head0 + 2 * t + (row_of[q] >> 6);
+                        e.store[q] = node < N && head < (it.kvh + 1) * p.group;
+                        e.base[q] = (((size_t)it.b * p.num_heads + head) * N + node) * kT;
+                    } else {
+                        e.store[q] = row_of[q] < it.rows_here;
+                        e.base[q] = ((size_t)(it.q0 + row_of[q]) * p.num_heads + it.head0 + t) * kT;
+                    }
                 }
                 if (kDefer) {
                     pend = e;
                 } else {
-                    while (e.chunks_left > 0) readout_chunk(e);
+                    while (e.halves_left > 0) readout_half(e);
                 }
             }
             items_done++;
         }  // items
-        while (kDefer && pend.chunks_left > 0) readout_chunk(pend);
+        while (kDefer && pend.halves_left > 0) readout_half(pend);
         if (!ok && lane == 0) atomicOr(p.status, kStatusTimeout);
     }
 

@@ -243,6 +243,60 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// Fragment-shaped TMEM access: 16 lanes per instruction, a row's columns spread over the four
+// threads of a quad exactly like an mma.m16n8 accumulator.  With T = thread index in the warp:
+//   16x256b.x8 (64 columns): register 4i+e   = lane T/4,     column 8i + 2(T%4) + e   (e = 0, 1)
+//                            register 4i+2+e = lane T/4 + 8, same column
+//   16x128b.x8 (32 columns): register 2i     = lane T/4,     column 4i + T%4
+//                            register 2i+1   = lane T/4 + 8, same column
+// The lane field of taddr selects the first of the 16 lanes (a multiple of 16 inside the warp's
+// 32-lane quarter).
+#define GB_R8(a, o) "=r"(a[o]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), "=r"(a[o + 7])
+#define GB_I8(a, o) "r"(a[o]), "r"(a[o + 1]), "r"(a[o + 2]), "r"(a[o + 3]), "r"(a[o + 4]), "r"(a[o + 5]), "r"(a[o + 6]), "r"(a[o + 7])
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : GB_R8(r, 0), GB_R8(r, 8), GB_R8(r, 16), GB_R8(r, 24)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), GB_I8(r, 0), GB_I8(r, 8), GB_I8(r, 16), GB_I8(r, 24)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), GB_I8(r, 0), GB_I8(r, 8)
+        : "memory");
+}
+#undef GB_R8
+#undef GB_I8
+// 4 x 4 exchange of 32-bit words inside a quad of lanes: in, lane q holds v[i] = element (i, q);
+// out, lane q holds element (q, s) in v[s].
+__device__ __forceinline__ void quad_transpose(uint32_t (&v)[4], int lane) {
+    const bool i0 = lane & 1, i1 = lane & 2;
+    uint32_t z[4];
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, i0 ? v[u] : v[u + 1], 1);
+        z[u] = i0 ? got : v[u];
+        z[u + 1] = i0 ? v[u + 1] : got;
+    }
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, i1 ? z[w] : z[2 + w], 2);
+        v[w] = i1 ? got : z[w];
+        v[2 + w] = i1 ? z[2 + w] : got;
+    }
+}
 // Register budget of the calling warpgroup (all four warps must execute it): the softmax
 // warpgroups take registers that the producer / MMA warpgroup gives up.
 template <int N>
