@@ -201,19 +201,25 @@ def hold_queue(dev, ms: float = 8.0):
     torch.cuda._sleep(int(ms * 1.9e6))
 
 
-def region_ms_per_launch(dev, step, reps: int) -> float:
+def region_ms_per_launch(dev, step, reps: int, clocks: dict | None = None) -> float:
     """Average duration of `reps` launches issued back to back behind a queue-holding kernel, one
     CUDA event pair around the whole region on the launching stream (an event pair around every
-    single launch adds the front-end's gap between dependent operations to each of them)."""
+    single launch adds the front-end's gap between dependent operations to each of them).  With
+    `clocks` given, SM clock and throttle reasons are sampled during the region and stored there."""
     import torch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
+    sampler = ClockSampler(dev.index if dev.index is not None else 0, 0.001) if clocks is not None else None
     hold_queue(dev)
+    if sampler:
+        sampler.start()
     e0.record()
     for i in range(reps):
         step(i)
     e1.record()
     e1.synchronize()
+    if sampler:
+        clocks.update(sampler.stop())
     return e0.elapsed_time(e1) / reps
 
 
@@ -247,12 +253,13 @@ def measure_prefill(compute, dev, reps: int = 200):
     st = compute.get_kernel_timing_stats()
     compute.enable_kernel_timing(False)
     ms_each = st["prefill_causal_fa"][0] / st["prefill_causal_fa"][1]
-    ms = region_ms_per_launch(dev, step, reps)
+    clocks = {}
+    ms = region_ms_per_launch(dev, step, reps, clocks)
     flops = 4 * d * hq * seq * (seq + 1) // 2
     burst, sustained, kind = tensor_peak()
     tf = flops / ms / 1e9
     return {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms,
-            "kernel_ms_timed_singly": ms_each, "launches": reps,
+            "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
             "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst,
             "frac": tf / burst, "frac_of_sustained": tf / sustained, "peak_kind": kind,
             "note": "unmasked half of the causal square counted only; P enters the PV product as fp16 hi+lo "
@@ -296,7 +303,8 @@ def measure_tree(compute, dev, reps: int = 200):
     st = compute.get_kernel_timing_stats()
     compute.enable_kernel_timing(False)
     ms_each = st["tree_verify"][0] / st["tree_verify"][1]
-    ms = region_ms_per_launch(dev, step, reps)
+    clocks = {}
+    ms = region_ms_per_launch(dev, step, reps, clocks)
     visible = 0
     for b in range(batch):  # self + ancestors of every node
         for i in range(n):
@@ -312,7 +320,7 @@ def measure_tree(compute, dev, reps: int = 200):
     tf = flops / ms / 1e9
     gbs = nbytes / ms / 1e6
     return {"workload": "tree_verify_b16", "kernel": "tree_verify", "kernel_ms": ms,
-            "kernel_ms_timed_singly": ms_each, "launches": reps,
+            "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
             "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
             "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
             "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind}
