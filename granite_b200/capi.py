@@ -82,7 +82,7 @@ class AttentionArgs(C.Structure):
         ("num_heads", C.c_uint32), ("num_kv_heads", C.c_uint32), ("seq_q", C.c_uint32),
         ("seq_kv", C.c_uint32), ("head_dim", C.c_uint32), ("max_seq", C.c_uint32),
         ("q_dtype", C.c_uint32), ("out_dtype", C.c_uint32), ("scale", C.c_float),
-        ("start_pos", C.c_uint32),
+        ("start_pos", C.c_uint32), ("batch_size", C.c_uint32),
     ]
 
 
@@ -306,9 +306,9 @@ class CudaCompute:
                                             scale, num_blocks=num_blocks, seq_len=seq_len)
 
     def multihead_attention(self, Q, K, V, output, num_heads, num_kv_heads, seq_q, seq_kv, head_dim,
-                            scale, max_seq=0, *, q_dtype=0, out_dtype=0, start_pos=0) -> None:
+                            scale, max_seq=0, *, q_dtype=0, out_dtype=0, start_pos=0, batch_size=1) -> None:
         a = AttentionArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), num_heads, num_kv_heads, seq_q,
-                          seq_kv, head_dim, max_seq, q_dtype, out_dtype, scale, start_pos)
+                          seq_kv, head_dim, max_seq, q_dtype, out_dtype, scale, start_pos, batch_size)
         check(lib.granite_cuda_multihead_attention(self._h, C.byref(a)))
 
     def attention_tree(self, Q, K_cache, V_cache, K_tree, V_tree, parent_indices, output, num_heads,

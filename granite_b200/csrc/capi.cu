@@ -327,7 +327,7 @@ int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCud
         d.k_cache = a->k;
         d.v_cache = a->v;
         d.output = static_cast<float*>(a->output);
-        d.batch_size = 1;
+        d.batch_size = a->batch_size ? a->batch_size : 1;
         d.num_heads = a->num_heads;
         d.num_kv_heads = a->num_kv_heads;
         d.head_dim = a->head_dim;

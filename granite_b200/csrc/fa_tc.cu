@@ -184,7 +184,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     // (round r left to right when even, right to left when odd), which keeps the summed causal work
     // per CTA within about one K/V step of the mean.  Tree: equal items, same dealing.
     const int n_items = kTree ? p.batch * p.num_kv_heads * p.units_per_kvh
-                              : p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
+                              : p.n_qblocks * p.batch * p.num_kv_heads * p.units_per_kvh;
     const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
     auto item_of = [&](int r) {
         TcItem it;
@@ -210,7 +210,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             it.q0 = 0;
             it.rows_here = kT;
         } else {
-            it.b = 0;
+            // pp = qblock_rank * batch + b: the heaviest query blocks of every sequence come first
+            it.b = pp % p.batch;
+            pp /= p.batch;
             it.head0 = it.kvh * p.group + unit * kTiles;  // one head per tile
             it.q0 = (p.n_qblocks - 1 - pp) * kT;
             it.rows_here = min(kT, p.seq_q - it.q0);
@@ -284,10 +286,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             } else {
                                 for (int t = 0; t < kTiles; t++)
                                     tma_load_2d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full,
-                                                (it.head0 + t) * kT + c * 64, it.q0);
+                                                (it.head0 + t) * kT + c * 64, it.b * p.seq_q + it.q0);
                                 if (kSplitQ)
                                     tma_load_2d(q_smem + kTileBytes + c * kChunkBytes, &qlomap, &sh->q_full,
-                                                it.head0 * kT + c * 64, it.q0);
+                                                it.head0 * kT + c * 64, it.b * p.seq_q + it.q0);
                             }
                         }
                     }
@@ -346,7 +348,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         } else if (lane < 2) {
                             // contiguous cache [.., max rows, 128]: one 128-row box per chunk
                             const int y = kTree ? (it.b * p.num_kv_heads + it.kvh) * p.cache_stride + j * kT
-                                                : it.kvh * p.max_seq + j * kT;
+                                                : (it.b * p.num_kv_heads + it.kvh) * p.max_seq + j * kT;
                             tma_load_2d(dst + c * kChunkBytes, is_v ? &vmap : &kmap, full, c * 64, y);
                         }
                     }
@@ -762,7 +764,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         e.base[q] = (((size_t)it.b * p.num_heads + head) * N + node) * kT;
                     } else {
                         e.store[q] = row_of[q] < it.rows_here;
-                        e.base[q] = ((size_t)(it.q0 + row_of[q]) * p.num_heads + it.head0 + t) * kT;
+                        e.base[q] = (((size_t)it.b * p.seq_q + it.q0 + row_of[q]) * p.num_heads + it.head0 + t) * kT;
                     }
                 }
                 if (kDefer) {
@@ -881,13 +883,18 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     const uint32_t max_seq = a.max_seq ? a.max_seq : a.seq_kv;
     if (a.seq_kv == 0 || a.seq_kv > max_seq) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: seq_kv must be in [1, max_seq]");
 
+    const uint32_t batch = a.batch_size ? a.batch_size : 1;
+    if ((uint64_t)batch * a.seq_q >= (1ull << 31) || (uint64_t)batch * a.num_kv_heads * max_seq >= (1ull << 31))
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: batch * rows exceeds the tensor-map coordinate range");
+
     const bool split_q = a.q_dtype == 0;
     const void *q16 = a.q, *q16_lo = a.q;
     if (split_q) {
-        int rc = split_queries(c, a.q, (size_t)a.seq_q * a.num_heads * kT, &q16, &q16_lo);
+        int rc = split_queries(c, a.q, (size_t)batch * a.seq_q * a.num_heads * kT, &q16, &q16_lo);
         if (rc) return rc;
     }
     TcParams p{};
+    p.batch = (int)batch;
     p.num_heads = (int)a.num_heads;
     p.num_kv_heads = (int)a.num_kv_heads;
     p.group = (int)(a.num_heads / a.num_kv_heads);
@@ -903,15 +910,16 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     p.n_qblocks = (p.seq_q + kT - 1) / kT;
     p.start_pos = (int)a.start_pos;
 
-    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
-    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
-    const uint64_t kv_rows = (uint64_t)a.num_kv_heads * max_seq;
+    const uint64_t q_rows = (uint64_t)batch * a.seq_q;
+    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, q_rows, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, q_rows, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const uint64_t kv_rows = (uint64_t)batch * a.num_kv_heads * max_seq;
     const CUtensorMap* kmap = c->tensor_map_2d(a.k, kT, kv_rows, kT * 2, 64, kT, 128);
     const CUtensorMap* vmap = c->tensor_map_2d(a.v, kT, kv_rows, kT * 2, 64, kT, 128);
     if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
     TcKernel kern = split_q ? fa_tc_kernel<false, false, true, 1> : fa_tc_kernel<false, false, false, 1>;
-    const int n_items = p.n_qblocks * p.num_kv_heads * p.units_per_kvh;
+    const int n_items = p.n_qblocks * p.batch * p.num_kv_heads * p.units_per_kvh;
     return launch_tc(c, kern, "prefill_causal_fa", n_items, split_q ? 2 : tiles, qmap, qlomap, kmap, vmap, kmap, vmap, p);
 }
 

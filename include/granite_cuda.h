@@ -161,10 +161,14 @@ int granite_cuda_batched_paged_attention_decode_static(const GraniteCudaPagedDec
  *             fp16 of which the first seq_kv rows per head are live.
  * seq_q  > 1: causal prefill (metal_compute.mm:2333-2375). q/out [seq_q, num_heads, head_dim];
  *             k/v [num_kv_heads, max_seq, head_dim] fp16, keys [0, seq_kv) live.
- *             q_dtype / out_dtype: 0 = fp32 (the reference's layout), 1 = fp16.  fp32 Q is
- *             rounded to fp16 once for the tensor cores, as the Metal kernel does
- *             (metal_shaders_attention.h:1505-1507); accumulation is fp32.
- * max_seq == 0 means seq_kv, as in the reference (metal_compute.mm:2260). */
+ *             q_dtype / out_dtype: 0 = fp32 (the reference's layout), 1 = fp16.  fp32 Q reaches
+ *             the tensor cores as an fp16 hi + lo pair, so nothing of it is rounded away;
+ *             accumulation is fp32.
+ * max_seq == 0 means seq_kv, as in the reference (metal_compute.mm:2260).
+ * batch_size > 1 (beyond the reference, which handles one sequence per call): a leading batch
+ * dimension on every buffer - q/out [batch, seq_q, num_heads, head_dim] (decode: [batch, num_heads,
+ * head_dim]), k/v [batch, num_kv_heads, max_seq, head_dim] - with the same seq_q, seq_kv and
+ * start_pos for every sequence. */
 typedef struct {
     const void* q;
     const void* k;
@@ -182,6 +186,7 @@ typedef struct {
     uint32_t start_pos; /* prefill only: query i sits at position start_pos + i and sees keys
                            <= that position (chunked prefill, src/llm/transformer.mm:3682-3692);
                            the reference wrapper passes 0 */
+    uint32_t batch_size; /* 0 or 1: one sequence */
 } GraniteCudaAttentionArgs;
 
 int granite_cuda_multihead_attention(granite_cuda_compute_t* c,

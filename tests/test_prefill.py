@@ -90,3 +90,28 @@ def test_prefill_full_config_slice(compute):
     assert_attention_close(got[:, 28:32], ref7, "config slice, KV head 7")
     # causality as a size-independent property: the first row attends to key 0 only
     assert_attention_close(got[0], np.repeat(v[:, 0].astype(np.float32), hq // hkv, axis=0), "row 0 equals V[0]")
+
+
+@pytest.mark.parametrize("batch,seq_q,seq_kv,max_seq,start_pos,q_fp16", [(3, 200, 200, 200, 0, True), (2, 128, 300, 384, 172, False),
+                                                                       (5, 1, 77, 128, 0, False)])
+def test_batched_sequences(compute, batch, seq_q, seq_kv, max_seq, start_pos, q_fp16):
+    """A leading batch dimension on every buffer (beyond the reference, which takes one sequence per
+    call): every sequence must come out as if it had been run alone.  seq_q == 1 is the decode path."""
+    import torch
+    dev = "cuda:0"
+    hq, hkv, d = 8, 2, 128
+    cases = [_case(40 + b, seq_q, seq_kv, max_seq, hq, hkv) for b in range(batch)]
+    q = np.stack([c[0] for c in cases])
+    k = np.stack([c[1] for c in cases])
+    v = np.stack([c[2] for c in cases])
+    decode = seq_q == 1
+    qd = torch.from_numpy(q.astype(np.float16) if q_fp16 else q).to(dev)
+    out = torch.full((batch, seq_q, hq, d), float("nan"), device=dev)
+    compute.multihead_attention(qd, torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev), out, hq, hkv, seq_q, seq_kv,
+                                d, 1.0 / np.sqrt(d), max_seq, q_dtype=int(q_fp16), out_dtype=0,
+                                start_pos=0 if decode else start_pos, batch_size=batch)
+    compute.sync()
+    got = out.cpu().numpy()
+    for b in range(batch):
+        ref = _oracle(q[b], k[b], v[b], seq_kv, seq_kv - 1 if decode else start_pos, q_fp16)
+        assert_attention_close(got[b], ref, f"sequence {b} of {batch}")
