@@ -559,8 +559,6 @@ def main():
                                                D, synth.PAGE, case.max_blocks, scale,
                                                num_blocks=case.num_blocks)
 
-    pending = []
-
     def step(i):
         out = outs[i & 1]
         if push_done[i & 1] is not None:
@@ -587,9 +585,6 @@ def main():
     # ---- resident-input throughput ("value")
     for i in range(args.warmup):
         step(i)
-    for w in pending:
-        w.wait()
-    pending.clear()
     barrier()
     compute.enable_kernel_timing(True)
     compute.reset_kernel_timing()
@@ -600,9 +595,6 @@ def main():
     e0.record(stream)
     for i in range(args.steps):
         step(i)
-    for w in pending:
-        w.wait()
-    pending.clear()
     for ev in push_done:
         if ev is not None:
             stream.wait_event(ev)  # the last pushes end inside the timed region
@@ -611,6 +603,19 @@ def main():
     clocks = sampler.stop()
     compute.sync()
     ms_total = e0.elapsed_time(e1)
+    # the same steps without the output gather (max over ranks), to show what the gather costs
+    ms_no_gather = None
+    if world > 1:
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ea.record(stream)
+        for i in range(args.steps):
+            decode(q_d, tables_d, lens_d, outs[i & 1])
+        eb.record(stream)
+        barrier()
+        t = torch.tensor([ea.elapsed_time(eb) / args.steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_no_gather = float(t.item())
     gather_ok = None
     if world > 1 and peer_ptrs is not None:
         # outside the timed region: what the peers stored here must be what NCCL would have gathered
@@ -716,7 +721,8 @@ def main():
                        "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
                        "l2": f"inputs larger than L2 ({case.total_tokens * Hkv * D * 4 / 1e9:.1f} GB of K/V per GPU per step, no reuse)",
                        "sharding": f"by sequence; output gather: {gather_mode}" if world > 1 else "single GPU",
-                       **({"gather_verified": gather_ok} if gather_ok is not None else {})},
+                       **({"gather_verified": gather_ok} if gather_ok is not None else {}),
+                       **({"ms_per_step_without_gather": ms_no_gather} if ms_no_gather is not None else {})},
             "hbm_frac_of_measured_peak": value / n_gpus / peak,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
