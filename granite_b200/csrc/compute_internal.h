@@ -119,6 +119,11 @@ int launch_rope_multihead(granite_cuda_compute* c, float* q, float* k, uint32_t 
 int launch_rope_paged_append(granite_cuda_compute* c, const GraniteCudaRopeAppendArgs& a);
 int launch_tree_commit(granite_cuda_compute* c, const GraniteCudaTreeCommitArgs& a);
 int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a);
+// plain fp32 kernel for head dims, page sizes and head counts outside the tuned kernels' shapes
+int launch_generic_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a, bool contiguous, uint32_t max_seq);
+int launch_generic_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a);
+int launch_generic_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a);
+int launch_generic_tree(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a);
 int launch_bounded_wait_selftest(granite_cuda_compute* c, uint64_t limit_cycles, int* released_early_dev);
 int launch_push_rows(granite_cuda_compute* c, cudaStream_t stream, const void* src, void* const* dst_ptrs, uint32_t n_dst,
                      uint64_t dst_offset_bytes, uint64_t bytes);

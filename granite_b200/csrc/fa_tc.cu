@@ -876,7 +876,7 @@ static int split_queries(granite_cuda_compute* c, const void* q, size_t n, const
 
 int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     if (!a.q || !a.k || !a.v || !a.output) return fail(GRANITE_CUDA_NULL_POINTER, "prefill: null buffer");
-    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: head_dim must be 128");
+    if (a.head_dim != kT) return launch_generic_prefill(c, a);  // the plain kernel takes the other head dims
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: num_heads must be a multiple of num_kv_heads");
     if (a.q_dtype > 1 || a.out_dtype > 1) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: dtype must be 0 (fp32) or 1 (fp16)");
@@ -928,9 +928,9 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
 int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a) {
     if (!a.q || !a.k_cache || !a.v_cache || !a.block_table || !a.output)
         return fail(GRANITE_CUDA_NULL_POINTER, "paged_prefill_attention: null buffer");
-    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: head_dim must be 128");
-    if (a.block_size != (uint32_t)kPageRows || a.num_blocks == 0 || a.max_blocks_per_seq == 0)
-        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: block_size must be 16 and the pool non-empty");
+    if (a.head_dim != kT || a.block_size != (uint32_t)kPageRows) return launch_generic_paged_prefill(c, a);
+    if (a.num_blocks == 0 || a.max_blocks_per_seq == 0)
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: empty pool or table");
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: num_heads must be a multiple of num_kv_heads");
     if (a.q_dtype > 1 || a.out_dtype > 1)
@@ -993,7 +993,8 @@ int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* 
 int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a) {
     if (!a.q || !a.k_tree || !a.v_tree || !a.parent_indices || !a.output)
         return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null buffer");
-    if (a.head_dim != kT) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: head_dim must be 128");
+    if (a.head_dim != kT || (a.block_tables != nullptr && a.block_size != (uint32_t)kPageRows))
+        return launch_generic_tree(c, a);  // the plain kernel takes the other head dims and page sizes
     if (a.num_nodes == 0 || a.num_nodes > (uint32_t)kNodeSlots)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: num_nodes must be in [1, 64]");
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)

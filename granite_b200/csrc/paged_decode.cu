@@ -582,23 +582,22 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
                         bool contiguous, uint32_t max_seq) {
     if (!a.q || !a.k_cache || !a.v_cache || !a.output || (!contiguous && !a.block_tables))
         return fail(GRANITE_CUDA_NULL_POINTER, "paged decode: null buffer");
-    if (a.head_dim != kHeadDim)
-        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: head_dim must be 128");
-    if (!contiguous && a.block_size != kPageTokens)
-        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: block_size must be 16");
     if (a.batch_size == 0) return GRANITE_CUDA_SUCCESS;
     if (a.num_kv_heads == 0 || a.num_heads == 0 || a.num_heads % a.num_kv_heads != 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_heads must be a multiple of num_kv_heads");
+    // shapes outside this kernel's tiling (head_dim 128, 16-token pages, 1, 2, 4 or 8k KV heads, at
+    // most 16 query heads per consumer warp) run on the plain kernel
+    if (a.head_dim != kHeadDim || (!contiguous && a.block_size != kPageTokens))
+        return launch_generic_decode(c, a, contiguous, max_seq);
     const int hkv = (int)a.num_kv_heads;
     int tile_heads;
     if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
     else if (hkv % 8 == 0) tile_heads = 8;
-    else return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_kv_heads must be 1, 2, 4 or a multiple of 8");
+    else return launch_generic_decode(c, a, contiguous, max_seq);
     const int group = (int)(a.num_heads / a.num_kv_heads);
     const int warps_per_head = kConsumerWarps / tile_heads;
     const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
-    if (heads_per_warp > 16)
-        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: more than 16 query heads per consumer warp");
+    if (heads_per_warp > 16) return launch_generic_decode(c, a, contiguous, max_seq);
     const int nt = heads_per_warp <= 8 ? 1 : 2;
     const int subs_active = (group + heads_per_warp - 1) / heads_per_warp;
     if (contiguous) {

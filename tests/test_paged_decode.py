@@ -107,7 +107,8 @@ def test_unsupported_shapes_are_rejected(compute):
     import torch
     import granite_b200 as g
     t = torch.zeros(16, device="cuda:0")
-    for kw in (dict(head_dim=64), dict(block_size=32), dict(num_kv_heads=3)):
+    # (head_dim 64, 32-token pages or 3 KV heads are not errors: the plain kernel takes them)
+    for kw in (dict(head_dim=100), dict(head_dim=512), dict(num_kv_heads=5), dict(block_size=0)):
         args = dict(batch_size=1, num_heads=32, num_kv_heads=8, head_dim=128, block_size=16)
         args.update(kw)
         with pytest.raises(g.GraniteCudaError) as ei:
