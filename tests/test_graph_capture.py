@@ -69,3 +69,33 @@ def test_decode_prefill_and_tree_calls_replay_from_a_graph():
     for got, want, what in ((out_pre, direct[1], "prefill replay"), (out_tree, direct[2], "tree replay")):
         assert_attention_close(got.float().cpu().numpy(), want.float().cpu().numpy(), what)
     compute.shutdown()
+
+
+def test_two_compute_objects_on_two_streams():
+    """One compute object per stream (the reference's one-object-one-queue model, per GPU thread): calls
+    enqueued from two objects interleave on the device without sharing scratch or status."""
+    import torch
+    import granite_b200 as g
+    from oracle import pyoracle
+    hq, hkv, d = 32, 8, 128
+    streams = [torch.cuda.Stream(device=DEV) for _ in range(2)]
+    objs = [g.CudaCompute(0, s.cuda_stream) for s in streams]
+    cases = [synth.paged_case(70 + i, 7, 1, 4000, hq, hkv, d, device=DEV) for i in range(2)]
+    outs = [torch.zeros((c.batch, hq, d), device=DEV) for c in cases]
+    tabs = [torch.from_numpy(c.tables).to(DEV) for c in cases]
+    lens = [torch.from_numpy(c.seq_lens).to(DEV) for c in cases]
+    torch.cuda.synchronize()
+    for _ in range(5):
+        for o, c, out, t, l in zip(objs, cases, outs, tabs, lens):
+            o.batched_paged_attention_decode(c.q, c.k_pool, c.v_pool, t, l, out, c.batch, hq, hkv, d, synth.PAGE, c.max_blocks,
+                                             1.0 / np.sqrt(d), num_blocks=c.num_blocks)
+    for o in objs:
+        o.sync()
+    for c, out in zip(cases, outs):
+        ref, bad = pyoracle.paged_decode_batch(c.q.cpu().numpy(), c.k_pool.cpu().numpy().view(np.uint16),
+                                               c.v_pool.cpu().numpy().view(np.uint16), np.where(c.tables < 0, 0, c.tables),
+                                               c.seq_lens, synth.PAGE)
+        assert bad == 0
+        assert_attention_close(out.cpu().numpy(), ref, "two objects")
+    for o in objs:
+        o.shutdown()
