@@ -45,3 +45,35 @@ def test_error_codes_follow_the_reference_enum_order():
     # include/granite/error.h:16-57
     assert [g.ErrorCode.Success, g.ErrorCode.OutOfMemory, g.ErrorCode.Timeout, g.ErrorCode.InvalidArgument,
             g.ErrorCode.NotImplemented] == [0, 4, 12, 16, 25]
+
+
+def test_ctypes_structures_match_the_header(tmp_path):
+    """Every argument struct of the C ABI, as the header lays it out (compiled with the host C
+    compiler), against the ctypes mirror the tests and the benchmark pass: same size, same field
+    offsets."""
+    import shutil
+    import subprocess
+    import granite_b200.capi as capi
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    pairs = {"GraniteCudaPagedDecodeArgs": capi.PagedDecodeArgs, "GraniteCudaAttentionArgs": capi.AttentionArgs,
+             "GraniteCudaTreeAttentionArgs": capi.TreeAttentionArgs, "GraniteCudaKvAppendArgs": capi.KvAppendArgs,
+             "GraniteCudaPagedKvAppendArgs": capi.PagedKvAppendArgs, "GraniteCudaRopeAppendArgs": capi.RopeAppendArgs,
+             "GraniteCudaTreeCommitArgs": capi.TreeCommitArgs, "GraniteCudaPagedPrefillArgs": capi.PagedPrefillArgs,
+             "GraniteCudaKernelTiming": capi.KernelTiming}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "granite_cuda.h"', "int main(void) {"]
+    for cname, cls in pairs.items():
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'  printf("{cname}.{fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-std=c11", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, cls in pairs.items():
+        assert int(out[cname]) == ctypes.sizeof(cls), cname
+        for fname, _ in cls._fields_:
+            assert int(out[f"{cname}.{fname}"]) == getattr(cls, fname).offset, f"{cname}.{fname}"
