@@ -266,13 +266,13 @@ def measure_prefill(compute, dev, reps: int = 200):
                     "(two MMAs) to keep the CPU path's precision, which the flop count does not credit"}
 
 
-def measure_tree(compute, dev, reps: int = 200):
+def measure_tree(compute, dev, reps: int = 200, nodes: int = 0):
     """Tree verification: 16 sequences x (4096-token paged prefix + 64-node tree), Hq 32, Hkv 8
     (the tree-verification benchmark configuration); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
     import torch
     from granite_b200 import synth
     cfg = synth.CONFIGS["tree_verify_b16"]
-    batch, n, hq, hkv, L, d = cfg["batch"], cfg["nodes"], cfg["num_heads"], cfg["num_kv_heads"], cfg["prefix"], 128
+    batch, n, hq, hkv, L, d = cfg["batch"], nodes or cfg["nodes"], cfg["num_heads"], cfg["num_kv_heads"], cfg["prefix"], 128
     cases = [synth.paged_case(cfg["seed"] + i, batch, 0, 0, hq, hkv, seq_lens=np.full(batch, L, np.int32), device=dev)
              for i in range(3)]
     tables = [torch.from_numpy(c.tables).to(dev) for c in cases]
@@ -319,7 +319,7 @@ def measure_tree(compute, dev, reps: int = 200):
     hbm, hkind = measured_peaks()
     tf = flops / ms / 1e9
     gbs = nbytes / ms / 1e6
-    return {"workload": "tree_verify_b16", "kernel": "tree_verify", "kernel_ms": ms,
+    return {"workload": "tree_verify_b16" if n == cfg["nodes"] else f"tree_verify_b16_n{n}", "kernel": "tree_verify", "kernel_ms": ms,
             "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
             "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
             "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
@@ -444,7 +444,12 @@ def measure_single_decode(compute, dev, reps: int = 200):
             "bound": "launch latency (three dependent kernels)"}
 
 
-SECONDARY = {"single_decode": measure_single_decode, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
+def measure_tree16(compute, dev, reps: int = 200):
+    """The tree configuration with 16-node trees: four query heads share a 128-row tile."""
+    return measure_tree(compute, dev, reps, nodes=16)
+
+
+SECONDARY = {"single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
              "paged_prefill": measure_paged_prefill}
 
 
@@ -458,7 +463,7 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
-    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "step_write", "paged_prefill", "single_decode"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "tree16", "step_write", "paged_prefill", "single_decode"],
                     help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (profiling captures)")
     ap.add_argument("--sequences", type=int, default=0,

@@ -77,6 +77,7 @@ struct TcParams {
     const int32_t* tables;      // [batch, max_blocks] (paged) or nullptr
     const int32_t* cache_lens;  // [batch] or nullptr
     int batch, num_nodes, cache_len, cache_stride, max_blocks, num_blocks;
+    int slot_shift;             // tree: a tile is (128 >> slot_shift) query heads x (1 << slot_shift) node slots
     unsigned long long* trace;  // timeline hook, only used in GB_FA_TRACE builds
 };
 
@@ -197,7 +198,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         pp /= p.num_kv_heads;
         if (kTree) {
             it.b = pp;
-            it.head0 = it.kvh * p.group + unit * 2 * kTiles;  // two heads per tile
+            it.head0 = it.kvh * p.group + unit * (kT >> p.slot_shift) * kTiles;  // 128 / slots heads per tile
             int len = p.cache_lens ? p.cache_lens[it.b] : p.cache_len;
             const int cap = kPaged ? p.max_blocks * kPageRows : p.cache_stride;
             if (len < 0 || len > cap) {
@@ -277,10 +278,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         mbar_arrive_expect_tx(&sh->q_full, kQSlots * kTileBytes);
                         for (int c = 0; c < 2; c++) {
                             if (kTree) {
-                                // Q [batch*Hq, N, 128]: a box is 64 halfs x 64 nodes x 2 heads (16 KB)
+                                // Q [batch*Hq, N, 128]: a box is 64 halfs x node slots x heads per tile (16 KB)
                                 const int z0 = it.b * p.num_heads + it.head0;
                                 for (int t = 0; t < kTiles; t++)
-                                    tma_load_3d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full, c * 64, 0, z0 + 2 * t);
+                                    tma_load_3d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full, c * 64, 0, z0 + (kT >> p.slot_shift) * t);
                                 if (kSplitQ)
                                     tma_load_3d(q_smem + kTileBytes + c * kChunkBytes, &qlomap, &sh->q_full, c * 64, 0, z0);
                             } else {
@@ -561,7 +562,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 2; q++) {
                 last_visible[q] = kTree ? it.cache_len - 1 : min(p.start_pos + it.q0 + row_of[q], p.seq_kv - 1);
-                const int node = row_of[q] & (kNodeSlots - 1);
+                const int node = row_of[q] & ((1 << p.slot_shift) - 1);
                 if (kTree && node < N) {
                     const int32_t* par = p.parents + (size_t)it.b * N;
                     if (par[node] < -1 || par[node] >= N) atomicOr(p.status, kStatusBadParent);
@@ -758,8 +759,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     l += __shfl_xor_sync(0xffffffffu, l, 2);
                     e.inv[q] = 1.0f / l;
                     if (kTree) {
-                        const int node = row_of[q] & (kNodeSlots - 1);
-                        const int head = it.head0 + 2 * t + (row_of[q] >> 6);
+                        const int node = row_of[q] & ((1 << p.slot_shift) - 1);
+                        const int head = it.head0 + (kT >> p.slot_shift) * t + (row_of[q] >> p.slot_shift);
                         e.store[q] = node < N && head < (it.kvh + 1) * p.group;
                         e.base[q] = (((size_t)it.b * p.num_heads + head) * N + node) * kT;
                     } else {
@@ -1020,8 +1021,14 @@ int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionAr
     p.num_heads = (int)a.num_heads;
     p.num_kv_heads = (int)a.num_kv_heads;
     p.group = (int)(a.num_heads / a.num_kv_heads);
-    const int tiles = (!split_q && p.group % 4 == 0) ? 2 : 1;  // two heads per tile; two tiles share the K/V tiles
-    p.units_per_kvh = (p.group + 2 * tiles - 1) / (2 * tiles);
+    // A 128-row tile holds heads x node slots.  Small trees leave room for more heads per tile: as many
+    // as the node count allows (16, 32 or 64 slots), but no more than the GQA group has.
+    int slot_shift = a.num_nodes <= 16 ? 4 : a.num_nodes <= 32 ? 5 : 6;
+    while (slot_shift < 6 && (kT >> slot_shift) >= 2 * p.group) slot_shift++;
+    const int heads_per_tile = kT >> slot_shift, slots = 1 << slot_shift;
+    p.slot_shift = slot_shift;
+    const int tiles = (!split_q && p.group % (2 * heads_per_tile) == 0) ? 2 : 1;  // two tiles share the K/V tiles
+    p.units_per_kvh = (p.group + heads_per_tile * tiles - 1) / (heads_per_tile * tiles);
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = c->d_status;
     p.tree_out = a.output;
@@ -1035,11 +1042,11 @@ int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionAr
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
 
-    // Q / tree K / tree V as [heads, nodes, 128]: box = 64 halfs x 64 nodes x 2 heads (Q) or 1 head (K/V)
+    // Q / tree K / tree V as [heads, nodes, 128]: box = 64 halfs x node slots x heads per tile (Q), 64 nodes x 1 head (K/V)
     const uint64_t qz = (uint64_t)a.batch_size * a.num_heads;
     const uint64_t node_pitch = (uint64_t)a.num_nodes * kT * 2;
-    const CUtensorMap* qmap = c->tensor_map_3d(q16, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, kNodeSlots, 2, 128);
-    const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, kNodeSlots, 2, 128);
+    const CUtensorMap* qmap = c->tensor_map_3d(q16, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, slots, heads_per_tile, 128);
+    const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, slots, heads_per_tile, 128);
     const uint64_t tz = (uint64_t)a.batch_size * a.num_kv_heads;
     const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);
     const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);

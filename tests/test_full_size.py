@@ -82,3 +82,39 @@ def test_long_context_shard(compute):
     out = _decode(compute, case, case.k_pool, case.v_pool, torch.from_numpy(case.tables).to(DEV)).cpu().numpy()
     for b in (0, 1):
         assert_attention_close(out[b], _oracle_rows(case, b), f"maximum length, sequence {b}")
+
+
+def test_long_prefill_and_long_tree_prefix(compute):
+    """Many K/V steps per work item (every ring slot and barrier phase wraps dozens of times): the last
+    128 query rows of an 8192-token prefill against the CPU checker, and a tree over a 40 000-token
+    paged prefix."""
+    import torch
+    from oracle import pyoracle
+    import test_prefill as TP
+    import test_tree_verify as TT
+    hq, hkv, d, seq = 8, 2, 128, 8192
+    q, k, v = TP._case(77, seq, seq, seq, hq, hkv)
+    got = TP._run(compute, q, k, v, seq, 0, True, False)
+    assert np.isfinite(got).all()
+    tail = slice(seq - 128, seq)
+    qq = q.astype(np.float16).astype(np.float32)[tail]
+    ref = pyoracle.attention(qq[None], pyoracle.cache_to_fp32(k.view(np.uint16), seq), pyoracle.cache_to_fp32(v.view(np.uint16), seq),
+                             start_pos=seq - 128)[0]
+    assert_attention_close(got[tail], ref, "prefill 8192, last query block")
+    assert_attention_close(got[0], np.repeat(v[:, 0].astype(np.float32), hq // hkv, axis=0), "row 0 equals V[0]")
+
+    n, prefix = 64, 40000
+    case = synth.paged_case(5, 1, 0, 0, hq, hkv, d, seq_lens=np.array([prefix], np.int32), device=DEV)
+    qt, kt, vt, parents = TT._tree_inputs(6, 1, n, hq, hkv)
+    out = torch.zeros((1, hq, n, d), device=DEV)
+    compute.attention_tree(torch.from_numpy(qt).to(DEV), case.k_pool, case.v_pool, torch.from_numpy(kt).to(DEV),
+                           torch.from_numpy(vt).to(DEV), torch.from_numpy(parents).to(DEV), out, hq, hkv, n, prefix, d,
+                           1.0 / np.sqrt(d), batch_size=1, block_tables=torch.from_numpy(case.tables).to(DEV),
+                           max_blocks_per_seq=case.max_blocks, num_blocks=case.num_blocks)
+    compute.sync()
+    rows = (torch.from_numpy(case.tables[0].astype(np.int64)).to(DEV)[:, None] * synth.PAGE
+            + torch.arange(synth.PAGE, device=DEV)[None]).reshape(-1)[:prefix]
+    kr = case.k_pool[rows].cpu().numpy().astype(np.float32)
+    vr = case.v_pool[rows].cpu().numpy().astype(np.float32)
+    ref = TT._oracle_one(qt[0], kr, vr, kt[0], vt[0], parents[0])
+    assert_attention_close(out.cpu().numpy()[0], ref, "tree over a 40000-token prefix")
