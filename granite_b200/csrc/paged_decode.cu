@@ -27,11 +27,10 @@
 
 namespace gb200 {
 
-constexpr int kHeadDim = 128;
+constexpr int kHeadDim = 128;  // the benchmarked head size; the decode kernel is also built for 64
 constexpr int kPageTokens = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kHeadPageBytes = kPageTokens * kHeadDim * 2;  // 4096: one head's K (or V) page
 constexpr int kMaxSlots = 16;
 
 struct DecodeParams {
@@ -54,7 +53,8 @@ struct DecodeParams {
     int* status;
     int* page_prefix;     // [batch + 1]
     int* cta_first_seq;   // [n_ctas]
-    float* part_o;        // [2 * n_ctas][num_heads][128]
+    int d;                // head_dim: 128 or 64
+    float* part_o;        // [2 * n_ctas][num_heads][d]
     float2* part_ml;      // [2 * n_ctas][num_heads]
 };
 
@@ -116,8 +116,8 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(DecodeParams p) {
     // rows of empty sequences are defined to be zero (rare: one thread per such row)
     for (int b = tid; b < p.batch; b += 1024) {
         if (p.page_prefix[b + 1] == p.page_prefix[b]) {
-            float* o = p.out + (size_t)b * p.num_heads * kHeadDim;
-            for (int i = 0; i < p.num_heads * kHeadDim; i++) o[i] = 0.f;
+            float* o = p.out + (size_t)b * p.num_heads * p.d;
+            for (int i = 0; i < p.num_heads * p.d; i++) o[i] = 0.f;
         }
     }
     const long long T = (long long)total * p.n_head_tiles;
@@ -187,10 +187,13 @@ struct SegmentWalker {
     }
 };
 
-template <int NT>
+template <int NT, int D>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
+    constexpr int kDSteps = D / 16;                     // 16-wide steps along head_dim
+    constexpr int kChunks = D / 64;                     // 128-byte swizzle blocks per row
+    constexpr int kHeadPageBytes = kPageTokens * D * 2;  // one head's K (or V) page
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle wants 1024-byte aligned slots
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -228,7 +231,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             tma_prefetch_desc(&kmap);
             tma_prefetch_desc(&vmap);
         }
-        const int nbox = p.tile_heads * 2;  // (head, 64-half chunk) boxes per page per tensor
+        const int nbox = p.tile_heads * kChunks;  // (head, 64-half chunk) boxes per page per tensor
         const bool is_v = lane >= 16;
         const int box = lane & 15;
         const CUtensorMap* map = is_v ? &vmap : &kmap;
@@ -268,7 +271,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                         return;
                     }
                     if (box < nbox) {
-                        const int h = box >> 1, chunk = box & 1;
+                        const int h = box / kChunks, chunk = box % kChunks;
                         const int my_slot = is_v ? slot_v : slot_k;
                         uint8_t* dst = smem + (size_t)my_slot * slot_bytes + h * kHeadPageBytes + chunk * 2048;
                         int x, y;
@@ -276,7 +279,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                             x = chunk * 64;
                             y = (seg.seq * p.num_kv_heads + head0 + h) * p.max_seq + entry * kPageTokens;
                         } else {
-                            x = (head0 + h) * kHeadDim + chunk * 64;
+                            x = (head0 + h) * D + chunk * 64;
                             y = entry * kPageTokens;
                         }
                         tma_load_2d(dst, map, &full[my_slot], x, y);
@@ -308,14 +311,14 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
         const int len = p.seq_lens ? p.seq_lens[seg.seq] : p.uniform_len;
 
         // Q^T as the B operand: lane (g,t) holds head nt*8+g, dims ks*16 + {2t,2t+1, 2t+8,2t+9}
-        uint32_t qhi[NT][8][2], qlo[NT][8][2];
+        uint32_t qhi[NT][kDSteps][2], qlo[NT][kDSteps][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const int n = nt * 8 + g;
             const bool valid = n < n_q;
-            const float* qp = p.q + ((size_t)seg.seq * p.num_heads + hq0 + (valid ? n : 0)) * kHeadDim;
+            const float* qp = p.q + ((size_t)seg.seq * p.num_heads + hq0 + (valid ? n : 0)) * D;
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
+            for (int ks = 0; ks < kDSteps; ks++) {
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     float2 v = make_float2(0.f, 0.f);
@@ -331,13 +334,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             }
         }
 
-        float m_run[NT][2], l_run[NT][2], o[NT][8][4];
+        float m_run[NT][2], l_run[NT][2], o[NT][kDSteps][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             m_run[nt][0] = m_run[nt][1] = -INFINITY;
             l_run[nt][0] = l_run[nt][1] = 0.f;
 #pragma unroll
-            for (int mt = 0; mt < 8; mt++)
+            for (int mt = 0; mt < kDSteps; mt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) o[nt][mt][i] = 0.f;
         }
@@ -360,7 +363,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 for (int i = 0; i < 4; i++) sa[nt][i] = sb[nt][i] = 0.f;
             const uint32_t kbase = smem_base + slot_k * slot_bytes + k_row * 128;
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
+            for (int ks = 0; ks < kDSteps; ks++) {
                 uint32_t a[4];
                 const int unit = (ks & 3) * 2 + k_unit;
                 ldmatrix_x4(a, kbase + (ks >> 2) * 2048 + ((unit ^ (k_row & 7)) << 4));
@@ -407,7 +410,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 plo[nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l01));
                 plo[nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l23));
 #pragma unroll
-                for (int mt = 0; mt < 8; mt++) {
+                for (int mt = 0; mt < kDSteps; mt++) {
                     o[nt][mt][0] *= alpha[nt][0];
                     o[nt][mt][1] *= alpha[nt][1];
                     o[nt][mt][2] *= alpha[nt][0];
@@ -425,8 +428,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 // rows past the sequence end may hold anything (even NaN): zero them so that
                 // 0 * garbage cannot poison the accumulators
                 uint8_t* vptr = smem + (size_t)slot_v * slot_bytes + kvh_local * kHeadPageBytes;
-                for (int i = lane; i < (kPageTokens - ntok) * 16; i += 32) {
-                    int r = ntok + (i >> 4), u = i & 15;  // 16 units of 16 B per 256-byte row
+                constexpr int kRowUnits = D / 8;  // 16-byte units per row
+                for (int i = lane; i < (kPageTokens - ntok) * kRowUnits; i += 32) {
+                    int r = ntok + i / kRowUnits, u = i % kRowUnits;
                     int chunk = u >> 3, unit = u & 7;
                     *reinterpret_cast<uint4*>(vptr + chunk * 2048 + r * 128 + ((unit ^ (r & 7)) << 4)) =
                         make_uint4(0, 0, 0, 0);
@@ -435,7 +439,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             }
             const uint32_t vbase = vslot + v_row * 128;
 #pragma unroll
-            for (int mt = 0; mt < 8; mt++) {
+            for (int mt = 0; mt < kDSteps; mt++) {
                 uint32_t a[4];
                 const int unit = (mt & 3) * 2 + v_unit;
                 ldmatrix_x4_trans(a, vbase + (mt >> 2) * 2048 + ((unit ^ (v_row & 7)) << 4));
@@ -465,16 +469,16 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 const int hq = hq0 + n;
                 if (seg.slot < 0) {
                     const float inv = 1.0f / l_run[nt][jx];
-                    float* dst = p.out + ((size_t)seg.seq * p.num_heads + hq) * kHeadDim;
+                    float* dst = p.out + ((size_t)seg.seq * p.num_heads + hq) * D;
 #pragma unroll
-                    for (int mt = 0; mt < 8; mt++) {
+                    for (int mt = 0; mt < kDSteps; mt++) {
                         dst[mt * 16 + g] = o[nt][mt][jx] * inv;
                         dst[mt * 16 + g + 8] = o[nt][mt][2 + jx] * inv;
                     }
                 } else {
-                    float* dst = p.part_o + ((size_t)seg.slot * p.num_heads + hq) * kHeadDim;
+                    float* dst = p.part_o + ((size_t)seg.slot * p.num_heads + hq) * D;
 #pragma unroll
-                    for (int mt = 0; mt < 8; mt++) {
+                    for (int mt = 0; mt < kDSteps; mt++) {
                         dst[mt * 16 + g] = o[nt][mt][jx];
                         dst[mt * 16 + g + 8] = o[nt][mt][2 + jx];
                     }
@@ -559,7 +563,8 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParam
         const int slot = s_slot[i];
         if (slot < 0) continue;
         const float w = s_w[i];
-        const float4 o = *(reinterpret_cast<const float4*>(p.part_o + ((size_t)slot * p.num_heads + hq) * kHeadDim) + lane);
+        if (lane * 4 >= p.d) continue;  // head_dim 64: half of the lanes carry data
+        const float4 o = *(reinterpret_cast<const float4*>(p.part_o + ((size_t)slot * p.num_heads + hq) * p.d) + lane);
         acc.x += w * o.x;
         acc.y += w * o.y;
         acc.z += w * o.z;
@@ -567,11 +572,11 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParam
     }
     s_acc[warp][lane] = acc;
     __syncthreads();
-    if (tid < kHeadDim) {
+    if (tid < p.d) {
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < kMergeThreads / 32; w++) sum += reinterpret_cast<const float*>(&s_acc[w][0])[tid];
-        p.out[((size_t)b * p.num_heads + hq) * kHeadDim + tid] = sum / L;
+        p.out[((size_t)b * p.num_heads + hq) * p.d + tid] = sum / L;
     }
 }
 
@@ -587,8 +592,9 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_heads must be a multiple of num_kv_heads");
     // shapes outside this kernel's tiling (head_dim 128, 16-token pages, 1, 2, 4 or 8k KV heads, at
     // most 16 query heads per consumer warp) run on the plain kernel
-    if (a.head_dim != kHeadDim || (!contiguous && a.block_size != kPageTokens))
+    if ((a.head_dim != 128 && a.head_dim != 64) || (!contiguous && a.block_size != kPageTokens))
         return launch_generic_decode(c, a, contiguous, max_seq);
+    const int D = (int)a.head_dim;
     const int hkv = (int)a.num_kv_heads;
     int tile_heads;
     if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
@@ -627,8 +633,9 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.max_seq = (int)max_seq;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = c->d_status;
+    p.d = D;
 
-    const int slot_bytes = tile_heads * kHeadPageBytes;
+    const int slot_bytes = tile_heads * kPageTokens * D * 2;
     const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
     int slots = (int)((c->smem_optin - 1024 - tail) / slot_bytes);
     if (slots > kMaxSlots) slots = kMaxSlots;
@@ -641,7 +648,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     const size_t off_prefix = off; off = align_up(off + (size_t)(p.batch + 1) * 4, 256);
     const size_t off_first = off;  off = align_up(off + (size_t)p.n_ctas * 4, 256);
     const size_t off_ml = off;     off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * sizeof(float2), 256);
-    const size_t off_o = off;      off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * kHeadDim * 4, 256);
+    const size_t off_o = off;      off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * D * 4, 256);
     int rc = c->ensure_scratch(off);
     if (rc) return rc;
     uint8_t* ws = static_cast<uint8_t*>(c->scratch);
@@ -653,17 +660,18 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     const CUtensorMap *kmap, *vmap;
     if (contiguous) {
         const uint64_t rows = (uint64_t)a.batch_size * hkv * max_seq;
-        kmap = c->tensor_map_2d(a.k_cache, kHeadDim, rows, kHeadDim * 2, 64, kPageTokens, 128);
-        vmap = c->tensor_map_2d(a.v_cache, kHeadDim, rows, kHeadDim * 2, 64, kPageTokens, 128);
+        kmap = c->tensor_map_2d(a.k_cache, D, rows, D * 2, 64, kPageTokens, 128);
+        vmap = c->tensor_map_2d(a.v_cache, D, rows, D * 2, 64, kPageTokens, 128);
     } else {
         const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens;
-        const uint64_t width = (uint64_t)hkv * kHeadDim;
+        const uint64_t width = (uint64_t)hkv * D;
         kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageTokens, 128);
         vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageTokens, 128);
     }
     if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
-    auto kern = nt == 1 ? paged_decode_kernel<1> : paged_decode_kernel<2>;
+    auto kern = D == 128 ? (nt == 1 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>)
+                         : (nt == 1 ? paged_decode_kernel<1, 64> : paged_decode_kernel<2, 64>);
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     {
         LaunchScope t(c, "decode_plan");
@@ -739,8 +747,8 @@ static int static_decode_setup(int device, StaticDeviceSetup** out) {
         if (major != 10) return fail(GRANITE_CUDA_BACKEND_NOT_SUPPORTED, "static decode: built for sm_100a only");
         GB_CUDA_TRY(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, device));
         GB_CUDA_TRY(cudaDeviceGetAttribute(&s.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
-        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
+        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<1, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
+        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
         s.scratch = static_cast<unsigned char*>(ptr);
         s.ready = true;
     }
@@ -838,7 +846,7 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     p.contiguous = 0;
     p.max_seq = 0;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    const int slot_bytes = tile_heads * kHeadPageBytes;
+    const int slot_bytes = tile_heads * kPageTokens * kHeadDim * 2;
     const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
     int slots = (int)((setup->smem_optin - 1024 - tail) / slot_bytes);
     if (slots > kMaxSlots) slots = kMaxSlots;
@@ -851,6 +859,7 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     p.cta_first_seq = reinterpret_cast<int*>(ws + kStaticOffFirst);
     p.part_ml = reinterpret_cast<float2*>(ws + kStaticOffMl);
     p.part_o = reinterpret_cast<float*>(ws + kStaticOffO);
+    p.d = kHeadDim;
     if (device_status) {
         p.status = device_status;  // the caller owns and clears it
     } else {
@@ -867,9 +876,9 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
 
     decode_plan_kernel<<<1, 1024, 0, st>>>(p);
     if (heads_per_warp <= 8)
-        paged_decode_kernel<1><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
+        paged_decode_kernel<1, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
     else
-        paged_decode_kernel<2><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
+        paged_decode_kernel<2, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
     decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, st>>>(p);
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;

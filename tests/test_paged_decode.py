@@ -141,3 +141,33 @@ def test_contiguous_decode_matches_cpu(compute, seq_kv, max_seq):
     vf = pyoracle.cache_to_fp32(v.view(np.uint16), seq_kv)
     ref = pyoracle.attention(q[None, None], kf, vf, start_pos=seq_kv - 1)[0, 0]
     assert_attention_close(out.cpu().numpy(), ref, f"contiguous seq_kv={seq_kv}")
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (32, 4), (14, 2), (8, 8), (16, 1), (64, 8)])
+def test_paged_decode_head_dim_64(compute, hq, hkv):
+    """The same split-KV kernel built for head_dim 64 (one 128-byte swizzle block per row, 16 KB pages
+    of eight heads, a 14-deep ring)."""
+    case = synth.paged_case(seed=90 + hq + hkv, batch=7, len_lo=0, len_hi=0, num_heads=hq, num_kv_heads=hkv, head_dim=64,
+                            seq_lens=np.array([1, 15, 16, 17, 700, 0, 3001], np.int32), spare_blocks=2)
+    got, k_np, v_np = _run_paged(compute, case, poison_unused=True)
+    assert_attention_close(got, _oracle(case, k_np, v_np), f"D=64 Hq={hq} Hkv={hkv}")
+    assert not got[5].any()
+
+
+def test_contiguous_decode_head_dim_64(compute):
+    import torch
+    from oracle import pyoracle
+    hq, hkv, d, seq_kv, max_seq = 32, 8, 64, 777, 1024
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    k = rng.standard_normal((hkv, max_seq, d), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((hkv, max_seq, d), dtype=np.float32).astype(np.float16)
+    k.view(np.uint16)[:, seq_kv:] = 0x7E00
+    v.view(np.uint16)[:, seq_kv:] = 0x7E00
+    out = torch.zeros((hq, d), device="cuda:0")
+    compute.multihead_attention(torch.from_numpy(q).to("cuda:0"), torch.from_numpy(k).to("cuda:0"),
+                                torch.from_numpy(v).to("cuda:0"), out, hq, hkv, 1, seq_kv, d, 1.0 / np.sqrt(d), max_seq)
+    compute.sync()
+    ref = pyoracle.attention(q[None, None], pyoracle.cache_to_fp32(k.view(np.uint16), seq_kv),
+                             pyoracle.cache_to_fp32(v.view(np.uint16), seq_kv), start_pos=seq_kv - 1, scale=1.0 / np.sqrt(d))[0, 0]
+    assert_attention_close(out.cpu().numpy(), ref, "contiguous decode D=64")
