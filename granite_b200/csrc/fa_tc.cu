@@ -77,6 +77,7 @@ struct TcParams {
     const int32_t* tables;      // [batch, max_blocks] (paged) or nullptr
     const int32_t* cache_lens;  // [batch] or nullptr
     int batch, num_nodes, cache_len, cache_stride, max_blocks, num_blocks;
+    int d_chunks;               // head_dim / 64: 2 (head_dim 128) or 1 (head_dim 64, half of every tile slot is used)
     int slot_shift;             // tree: a tile is (128 >> slot_shift) query heads x (1 << slot_shift) node slots
     unsigned long long* trace;  // timeline hook, only used in GB_FA_TRACE builds
 };
@@ -165,6 +166,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.num_nodes;
+    const int hd = p.d_chunks * 64;  // head_dim
 #ifdef GB_FA_TRACE
     if (threadIdx.x == 0) {
         unsigned long long gt;
@@ -275,8 +277,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     // the query tiles are replaced once the last score MMA of the previous item is done
                     alive = mbar_wait(&sh->q_empty, (items_done & 1) ^ 1, abort_flag);
                     if (alive) {
-                        mbar_arrive_expect_tx(&sh->q_full, kQSlots * kTileBytes);
-                        for (int c = 0; c < 2; c++) {
+                        mbar_arrive_expect_tx(&sh->q_full, kQSlots * p.d_chunks * kChunkBytes);
+                        for (int c = 0; c < p.d_chunks; c++) {
                             if (kTree) {
                                 // Q [batch*Hq, N, 128]: a box is 64 halfs x node slots x heads per tile (16 KB)
                                 const int z0 = it.b * p.num_heads + it.head0;
@@ -287,10 +289,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             } else {
                                 for (int t = 0; t < kTiles; t++)
                                     tma_load_2d(q_smem + t * kTileBytes + c * kChunkBytes, &qmap, &sh->q_full,
-                                                (it.head0 + t) * kT + c * 64, it.b * p.seq_q + it.q0);
+                                                (it.head0 + t) * hd + c * 64, it.b * p.seq_q + it.q0);
                                 if (kSplitQ)
                                     tma_load_2d(q_smem + kTileBytes + c * kChunkBytes, &qlomap, &sh->q_full,
-                                                it.head0 * kT + c * 64, it.b * p.seq_q + it.q0);
+                                                it.head0 * hd + c * 64, it.b * p.seq_q + it.q0);
                             }
                         }
                     }
@@ -318,7 +320,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     const bool tree_step = kTree && j == it.n_prefix;
                     const int entry = entry_next;
                     entry_next = load_entry(j + 1);
-                    const uint32_t bytes = tree_step ? kTileBytes / 2 : kTileBytes;
+                    const uint32_t bytes = (uint32_t)(p.d_chunks * kChunkBytes) >> (tree_step ? 1 : 0);  // the tree tile has 64 rows
                     uint8_t* kd = k_smem + st * kTileBytes;
                     uint8_t* vd = v_smem + st * kTileBytes;
                     const int c = lane & 1;
@@ -336,17 +338,17 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         uint8_t* dst = is_v ? vd : kd;
                         if (tree_step) {
                             // tree K/V [batch*Hkv, N, 128]: 64-row boxes; rows >= N are zero-filled by TMA
-                            if (lane < 2)
+                            if (lane < p.d_chunks)
                                 tma_load_3d(dst + c * kChunkBytes, is_v ? &vtmap : &ktmap, full, c * 64, 0,
                                             it.b * p.num_kv_heads + it.kvh);
                         } else if (kPaged) {
                             // lane = (page, chunk): 8 pages x 2 chunks
                             const int pg = (lane >> 1) & 7;
                             const int e = __shfl_sync(0xffffffffu, entry, pg);
-                            if (lane < 16)
+                            if (lane < 16 && c < p.d_chunks)
                                 tma_load_2d(dst + c * kChunkBytes + pg * 2048, is_v ? &vmap : &kmap, full,
-                                            it.kvh * kT + c * 64, e * kPageRows);
-                        } else if (lane < 2) {
+                                            it.kvh * hd + c * 64, e * kPageRows);
+                        } else if (lane < p.d_chunks) {
                             // contiguous cache [.., max rows, 128]: one 128-row box per chunk
                             const int y = kTree ? (it.b * p.num_kv_heads + it.kvh) * p.cache_stride + j * kT
                                                 : (it.b * p.num_kv_heads + it.kvh) * p.max_seq + j * kT;
@@ -397,14 +399,18 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             // row, the second 64-wide block 16 KB further)
 #pragma unroll
                             for (int ks = 0; ks < 8; ks++) {
-                                const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-                                umma_ss_words(d, q_lo + off, k_lo + off, kDescHiSw128, idesc, ks > 0 ? 1u : 0u);
+                                if (ks < 4 * p.d_chunks) {
+                                    const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                                    umma_ss_words(d, q_lo + off, k_lo + off, kDescHiSw128, idesc, ks > 0 ? 1u : 0u);
+                                }
                             }
                             if (kSplitQ) {
 #pragma unroll
                                 for (int ks = 0; ks < 8; ks++) {
-                                    const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-                                    umma_ss_words(d, q_lo0 + (kTileBytes >> 4) + off, k_lo + off, kDescHiSw128, idesc, 1u);
+                                    if (ks < 4 * p.d_chunks) {
+                                        const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
+                                        umma_ss_words(d, q_lo0 + (kTileBytes >> 4) + off, k_lo + off, kDescHiSw128, idesc, 1u);
+                                    }
                                 }
                             }
                             tc_commit(&sh->s_full[b]);
@@ -426,7 +432,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             // warp 2 multiplies the hi half of P, warp 3 the lo half; O was zeroed by the softmax
             // warps, so every MMA accumulates and the two issuers need no order between them
             if (lane == 0) {
-                constexpr uint32_t idesc_pv = umma_idesc_f16(kT, kT, false, true);
+                const uint32_t idesc_pv = umma_idesc_f16(kT, hd, false, true);  // N = head_dim output columns
                 const uint32_t part = warp - 2;  // 0: hi, 1: lo
                 const uint32_t v_lo0 = desc_lo(smem_u32(v_smem), kChunkBytes);
                 bool ok = true;
@@ -498,7 +504,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         // its accumulator while the next item starts in the other one, and one 64-column half is
         // written after each of the next item's first softmax steps, behind the MMAs of those steps.
         constexpr bool kDefer = kTiles == 1;
-        constexpr int kHalves = 2;
         struct Readout {
             int halves_left;     // 0: nothing pending
             uint32_t phase;      // o_final parity of the item
@@ -509,7 +514,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         } pend;
         pend.halves_left = 0;
         auto readout_half = [&](Readout& e) {
-            const int h = kHalves - e.halves_left;
+            const int h = p.d_chunks - e.halves_left;
             if (h == 0) {
                 if (ok) ok = mbar_wait(&sh->o_final, e.phase, abort_flag);
                 tc_fence_after_sync();
@@ -584,7 +589,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         l_run_t[t][q] = 0.f;
                     }
 #pragma unroll
-                    for (int h = 0; h < 2; h++) tmem_st_16x256b_x8(frag_base + 2 * kT + (t + o_sel) * kT + h * 64, z);  // own rows only
+                    for (int h = 0; h < 2; h++)
+                        if (h < p.d_chunks) tmem_st_16x256b_x8(frag_base + 2 * kT + (t + o_sel) * kT + h * 64, z);  // own rows only
                 }
                 tmem_wait_st();
             }
@@ -668,7 +674,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             l_run[1] *= alpha1;
                             uint32_t rr[32];
 #pragma unroll 1
-                            for (int h = 0; h < 2; h++) {
+                            for (int h = 0; h < p.d_chunks; h++) {
                                 tmem_ld_16x256b_x8(o_frag + h * 64, rr);
                                 tmem_wait_ld();
 #pragma unroll
@@ -722,8 +728,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         ok = mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag);
                         const int first_bad = (kTree ? it.cache_len : p.seq_kv) - k0;
                         uint8_t* vt = v_smem + st * kTileBytes;
-                        for (int i = row; i < (kT - first_bad) * 16; i += 128) {
-                            const int vr = first_bad + (i >> 4), u = i & 15;
+                        const int row_units = 8 * p.d_chunks;  // 16-byte units per V row
+                        for (int i = row; i < (kT - first_bad) * row_units; i += 128) {
+                            const int vr = first_bad + i / row_units, u = i % row_units;
                             *reinterpret_cast<uint4*>(vt + (u >> 3) * kChunkBytes + vr * 128 + (((u & 7) ^ (vr & 7)) << 4)) =
                                 make_uint4(0, 0, 0, 0);
                         }
@@ -748,7 +755,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
 #pragma unroll
             for (int t = 0; t < kTiles; t++) {
                 Readout e;
-                e.halves_left = kHalves;
+                e.halves_left = p.d_chunks;
                 e.phase = items_done & 1;
                 e.o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
 #pragma unroll
@@ -762,10 +769,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         const int node = row_of[q] & ((1 << p.slot_shift) - 1);
                         const int head = it.head0 + (kT >> p.slot_shift) * t + (row_of[q] >> p.slot_shift);
                         e.store[q] = node < N && head < (it.kvh + 1) * p.group;
-                        e.base[q] = (((size_t)it.b * p.num_heads + head) * N + node) * kT;
+                        e.base[q] = (((size_t)it.b * p.num_heads + head) * N + node) * hd;
                     } else {
                         e.store[q] = row_of[q] < it.rows_here;
-                        e.base[q] = (((size_t)it.b * p.seq_q + it.q0 + row_of[q]) * p.num_heads + it.head0 + t) * kT;
+                        e.base[q] = (((size_t)it.b * p.seq_q + it.q0 + row_of[q]) * p.num_heads + it.head0 + t) * hd;
                     }
                 }
                 if (kDefer) {
@@ -877,7 +884,8 @@ static int split_queries(granite_cuda_compute* c, const void* q, size_t n, const
 
 int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     if (!a.q || !a.k || !a.v || !a.output) return fail(GRANITE_CUDA_NULL_POINTER, "prefill: null buffer");
-    if (a.head_dim != kT) return launch_generic_prefill(c, a);  // the plain kernel takes the other head dims
+    if (a.head_dim != 128 && a.head_dim != 64) return launch_generic_prefill(c, a);  // the plain kernel takes the other head dims
+    const uint32_t D = a.head_dim;
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: num_heads must be a multiple of num_kv_heads");
     if (a.q_dtype > 1 || a.out_dtype > 1) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "prefill: dtype must be 0 (fp32) or 1 (fp16)");
@@ -891,10 +899,11 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     const bool split_q = a.q_dtype == 0;
     const void *q16 = a.q, *q16_lo = a.q;
     if (split_q) {
-        int rc = split_queries(c, a.q, (size_t)batch * a.seq_q * a.num_heads * kT, &q16, &q16_lo);
+        int rc = split_queries(c, a.q, (size_t)batch * a.seq_q * a.num_heads * D, &q16, &q16_lo);
         if (rc) return rc;
     }
     TcParams p{};
+    p.d_chunks = (int)D / 64;
     p.batch = (int)batch;
     p.num_heads = (int)a.num_heads;
     p.num_kv_heads = (int)a.num_kv_heads;
@@ -912,11 +921,11 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
     p.start_pos = (int)a.start_pos;
 
     const uint64_t q_rows = (uint64_t)batch * a.seq_q;
-    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, q_rows, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
-    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, q_rows, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
+    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * D, q_rows, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
+    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * D, q_rows, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
     const uint64_t kv_rows = (uint64_t)batch * a.num_kv_heads * max_seq;
-    const CUtensorMap* kmap = c->tensor_map_2d(a.k, kT, kv_rows, kT * 2, 64, kT, 128);
-    const CUtensorMap* vmap = c->tensor_map_2d(a.v, kT, kv_rows, kT * 2, 64, kT, 128);
+    const CUtensorMap* kmap = c->tensor_map_2d(a.k, D, kv_rows, D * 2, 64, kT, 128);
+    const CUtensorMap* vmap = c->tensor_map_2d(a.v, D, kv_rows, D * 2, 64, kT, 128);
     if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
     TcKernel kern = split_q ? fa_tc_kernel<false, false, true, 1> : fa_tc_kernel<false, false, false, 1>;
@@ -929,7 +938,8 @@ int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a) {
 int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillArgs& a) {
     if (!a.q || !a.k_cache || !a.v_cache || !a.block_table || !a.output)
         return fail(GRANITE_CUDA_NULL_POINTER, "paged_prefill_attention: null buffer");
-    if (a.head_dim != kT || a.block_size != (uint32_t)kPageRows) return launch_generic_paged_prefill(c, a);
+    if ((a.head_dim != 128 && a.head_dim != 64) || a.block_size != (uint32_t)kPageRows) return launch_generic_paged_prefill(c, a);
+    const uint32_t D = a.head_dim;
     if (a.num_blocks == 0 || a.max_blocks_per_seq == 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged_prefill_attention: empty pool or table");
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
@@ -944,10 +954,11 @@ int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillA
     const bool split_q = a.q_dtype == 0;
     const void *q16 = a.q, *q16_lo = a.q;
     if (split_q) {
-        int rc = split_queries(c, a.q, (size_t)a.seq_q * a.num_heads * kT, &q16, &q16_lo);
+        int rc = split_queries(c, a.q, (size_t)a.seq_q * a.num_heads * D, &q16, &q16_lo);
         if (rc) return rc;
     }
     TcParams p{};
+    p.d_chunks = (int)D / 64;
     p.num_heads = (int)a.num_heads;
     p.num_kv_heads = (int)a.num_kv_heads;
     p.group = (int)(a.num_heads / a.num_kv_heads);
@@ -966,9 +977,9 @@ int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillA
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
 
-    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
-    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * kT, a.seq_q, (uint64_t)a.num_heads * kT * 2, 64, kT, 128);
-    const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * kT;
+    const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * D, a.seq_q, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
+    const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * D, a.seq_q, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
+    const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * D;
     const CUtensorMap* kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
     const CUtensorMap* vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
     if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
@@ -994,8 +1005,9 @@ int launch_tree_mask(granite_cuda_compute* c, const int32_t* parents, uint64_t* 
 int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a) {
     if (!a.q || !a.k_tree || !a.v_tree || !a.parent_indices || !a.output)
         return fail(GRANITE_CUDA_NULL_POINTER, "attention_tree: null buffer");
-    if (a.head_dim != kT || (a.block_tables != nullptr && a.block_size != (uint32_t)kPageRows))
+    if ((a.head_dim != 128 && a.head_dim != 64) || (a.block_tables != nullptr && a.block_size != (uint32_t)kPageRows))
         return launch_generic_tree(c, a);  // the plain kernel takes the other head dims and page sizes
+    const uint32_t D = a.head_dim;
     if (a.num_nodes == 0 || a.num_nodes > (uint32_t)kNodeSlots)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "attention_tree: num_nodes must be in [1, 64]");
     if (a.num_kv_heads == 0 || a.num_heads % a.num_kv_heads != 0)
@@ -1014,10 +1026,11 @@ int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionAr
     const bool split_q = a.q_dtype == 0;
     const void *q16 = a.q, *q16_lo = a.q;
     if (split_q) {
-        int rc = split_queries(c, a.q, (size_t)a.batch_size * a.num_heads * a.num_nodes * kT, &q16, &q16_lo);
+        int rc = split_queries(c, a.q, (size_t)a.batch_size * a.num_heads * a.num_nodes * D, &q16, &q16_lo);
         if (rc) return rc;
     }
     TcParams p{};
+    p.d_chunks = (int)D / 64;
     p.num_heads = (int)a.num_heads;
     p.num_kv_heads = (int)a.num_kv_heads;
     p.group = (int)(a.num_heads / a.num_kv_heads);
@@ -1044,22 +1057,22 @@ int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionAr
 
     // Q / tree K / tree V as [heads, nodes, 128]: box = 64 halfs x node slots x heads per tile (Q), 64 nodes x 1 head (K/V)
     const uint64_t qz = (uint64_t)a.batch_size * a.num_heads;
-    const uint64_t node_pitch = (uint64_t)a.num_nodes * kT * 2;
-    const CUtensorMap* qmap = c->tensor_map_3d(q16, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, slots, heads_per_tile, 128);
-    const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, kT, a.num_nodes, qz, kT * 2, node_pitch, 64, slots, heads_per_tile, 128);
+    const uint64_t node_pitch = (uint64_t)a.num_nodes * D * 2;
+    const CUtensorMap* qmap = c->tensor_map_3d(q16, D, a.num_nodes, qz, D * 2, node_pitch, 64, slots, heads_per_tile, 128);
+    const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, D, a.num_nodes, qz, D * 2, node_pitch, 64, slots, heads_per_tile, 128);
     const uint64_t tz = (uint64_t)a.batch_size * a.num_kv_heads;
-    const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);
-    const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, kT, a.num_nodes, tz, kT * 2, node_pitch, 64, kNodeSlots, 1, 128);
+    const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, kNodeSlots, 1, 128);
+    const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, kNodeSlots, 1, 128);
     const CUtensorMap *kmap = ktmap, *vmap = vtmap;  // placeholders when there is no prefix
     if (has_cache) {
         if (paged) {
-            const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * kT;
+            const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * D;
             kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
             vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
         } else {
             const uint64_t rows = (uint64_t)a.batch_size * a.num_kv_heads * cache_stride;
-            kmap = c->tensor_map_2d(a.k_cache, kT, rows, kT * 2, 64, kT, 128);
-            vmap = c->tensor_map_2d(a.v_cache, kT, rows, kT * 2, 64, kT, 128);
+            kmap = c->tensor_map_2d(a.k_cache, D, rows, D * 2, 64, kT, 128);
+            vmap = c->tensor_map_2d(a.v_cache, D, rows, D * 2, 64, kT, 128);
         }
     }
     if (!qmap || !qlomap || !ktmap || !vtmap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;

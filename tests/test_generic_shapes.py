@@ -93,3 +93,75 @@ def test_tree_other_shapes(compute, d, bs, n, hq, hkv):
         ref = pyoracle.attention_tree(q4, pyoracle.f16_bits_to_f32(kr), pyoracle.f16_bits_to_f32(vr), ktb, vtb, parents[b],
                                       scale=1.0 / np.sqrt(d))[0].transpose(1, 0, 2)
         assert_attention_close(got[b], ref, f"tree D={d} page={bs} N={n} prefix={int(lens[b])}")
+
+
+@pytest.mark.parametrize("seq_q,start,hq,hkv,q16,out16", [(300, 0, 8, 2, True, True), (129, 0, 4, 4, False, False),
+                                                          (77, 500, 12, 3, True, False), (1024, 0, 8, 1, True, True),
+                                                          (2, 0, 2, 1, False, True)])
+def test_prefill_head_dim_64_on_the_tensor_kernel(compute, seq_q, start, hq, hkv, q16, out16):
+    """head_dim 64 runs on the tcgen05 kernel too (half of every tile slot, four score steps, 64 output
+    columns); stale cache rows are NaN."""
+    from oracle import pyoracle
+    d = 64
+    seq_kv = start + seq_q
+    q, k, v = TP._case(seq_q * 3 + hq, seq_q, seq_kv, seq_kv + 50, hq, hkv, d=d)
+    got = TP._run(compute, q, k, v, seq_kv, start, q16, out16)
+    qq = q.astype(np.float16).astype(np.float32) if q16 else q
+    ref = pyoracle.attention(qq[None], pyoracle.cache_to_fp32(k.view(np.uint16), seq_kv),
+                             pyoracle.cache_to_fp32(v.view(np.uint16), seq_kv), start_pos=start, scale=1.0 / np.sqrt(d))[0]
+    assert_attention_close(got, ref, f"prefill D=64 seq_q={seq_q} start={start}")
+
+
+@pytest.mark.parametrize("n,hq,hkv,q16", [(64, 32, 8, True), (16, 8, 2, False), (33, 6, 6, True), (5, 16, 2, True)])
+def test_tree_and_chunked_prefill_head_dim_64(compute, n, hq, hkv, q16):
+    import torch
+    from oracle import pyoracle
+    from granite_b200 import synth
+    d, bs = 64, 16
+    rng = np.random.default_rng(n * 7 + hq)
+    lens = np.array([0, 130, 1000], np.int32)
+    batch = len(lens)
+    tables, num_blocks, k, v = _paged(rng, lens, hkv, d, bs)
+    k_bits, v_bits = k.view(np.uint16).copy(), v.view(np.uint16).copy()
+    live = np.zeros(num_blocks * bs, bool)
+    for b, length in enumerate(lens):
+        for pos in range(int(length)):
+            live[tables[b, pos // bs] * bs + pos % bs] = True
+    k_bits[~live] = 0x7E00
+    v_bits[~live] = 0x7E00
+    kd, vd = torch.from_numpy(k_bits.view(np.float16)).to(DEV), torch.from_numpy(v_bits.view(np.float16)).to(DEV)
+    q = rng.standard_normal((batch, hq, n, d), dtype=np.float32)
+    if q16:
+        q = q.astype(np.float16).astype(np.float32)
+    kt = rng.standard_normal((batch, hkv, n, d), dtype=np.float32).astype(np.float16)
+    vt = rng.standard_normal((batch, hkv, n, d), dtype=np.float32).astype(np.float16)
+    parents = np.stack([synth.tree_parents(int(rng.integers(1 << 30)), n) for _ in range(batch)])
+    out = torch.full((batch, hq, n, d), float("nan"), device=DEV)
+    compute.attention_tree(torch.from_numpy(q.astype(np.float16) if q16 else q).to(DEV), kd, vd, torch.from_numpy(kt).to(DEV),
+                           torch.from_numpy(vt).to(DEV), torch.from_numpy(parents).to(DEV), out, hq, hkv, n, 0, d,
+                           1.0 / np.sqrt(d), batch_size=batch, block_tables=torch.from_numpy(tables).to(DEV),
+                           cache_lens=torch.from_numpy(lens).to(DEV), block_size=bs, max_blocks_per_seq=tables.shape[1],
+                           num_blocks=num_blocks, q_dtype=int(q16))
+    compute.sync()
+    got = out.cpu().numpy()
+    for b in range(batch):
+        kr, _ = pyoracle.paged_gather(k_bits, tables[b], int(lens[b]), bs)
+        vr, _ = pyoracle.paged_gather(v_bits, tables[b], int(lens[b]), bs)
+        q4 = np.ascontiguousarray(q[b].transpose(1, 0, 2))[None]
+        ktb = np.ascontiguousarray(kt[b].astype(np.float32).transpose(1, 0, 2))[None]
+        vtb = np.ascontiguousarray(vt[b].astype(np.float32).transpose(1, 0, 2))[None]
+        ref = pyoracle.attention_tree(q4, pyoracle.f16_bits_to_f32(kr), pyoracle.f16_bits_to_f32(vr), ktb, vtb, parents[b],
+                                      scale=1.0 / np.sqrt(d))[0].transpose(1, 0, 2)
+        assert_attention_close(got[b], ref, f"tree D=64 N={n} prefix={int(lens[b])}")
+    # a chunk of the longest sequence through the block table
+    start, seq_q = 700, 300
+    cq = rng.standard_normal((seq_q, hq, d), dtype=np.float32).astype(np.float16)
+    cout = torch.full((seq_q, hq, d), float("nan"), device=DEV)
+    compute.paged_prefill_attention(torch.from_numpy(cq).to(DEV), kd, vd, torch.from_numpy(tables[2].copy()).to(DEV), cout, hq,
+                                    hkv, seq_q, start, d, bs, tables.shape[1], num_blocks, 1.0 / np.sqrt(d), q_dtype=1, out_dtype=0)
+    compute.sync()
+    kr, _ = pyoracle.paged_gather(k_bits, tables[2], start + seq_q, bs)
+    vr, _ = pyoracle.paged_gather(v_bits, tables[2], start + seq_q, bs)
+    ref = pyoracle.attention(cq.astype(np.float32)[None], pyoracle.f16_bits_to_f32(kr), pyoracle.f16_bits_to_f32(vr),
+                             start_pos=start, scale=1.0 / np.sqrt(d))[0]
+    assert_attention_close(cout.cpu().numpy(), ref, "chunked prefill D=64")
