@@ -1,6 +1,6 @@
-// Attention for the shapes the tuned kernels do not take: head_dim other than 128 (the reference's
-// GPU path also serves 64, src/backend/metal/metal_compute.mm:2550-2561), page
-// sizes other than 16, KV-head counts the decode tiling does not cover.  One plain kernel for
+// Attention for the shapes the tuned kernels do not take: head_dim other than 128 and 64 (the two
+// the reference's GPU path serves, src/backend/metal/metal_compute.mm:2550-2561), page sizes other
+// than 16, KV-head counts the decode tiling does not cover.  One plain kernel for
 // decode, causal prefill and tree verification over a contiguous or paged cache: fp32 arithmetic
 // throughout, one block per (sequence, query row, query head), keys in chunks of 128 with an
 // online softmax.  It keeps such models running on the GPU - there is no CPU fallback - at a

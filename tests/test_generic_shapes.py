@@ -1,6 +1,6 @@
-"""Shapes outside the tuned kernels' tiling - head_dim 64 (which the reference's GPU path also
-serves, src/backend/metal/metal_compute.mm:2550-2561), 32-token pages, odd KV-head counts - run on
-the plain fp32 kernel: same entry points, same layouts, same checker."""
+"""Shapes beside the benchmarked ones through the same entry points and the same checker: head_dim
+64 (which the reference's GPU path also serves, src/backend/metal/metal_compute.mm:2550-2561) on the
+tuned kernels; head_dim 96 / 256, 32-token pages and odd KV-head counts on the plain fp32 kernel."""
 import numpy as np
 import pytest
 
