@@ -64,15 +64,16 @@ const CUtensorMap* granite_cuda_compute::encode_map(const TensorMapKey& key) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
         return nullptr;
     }
-    if ((reinterpret_cast<uintptr_t>(key.base) & 15) != 0 || (key.stride1 & 15) != 0 || (key.stride2 & 15) != 0) {
+    if ((reinterpret_cast<uintptr_t>(key.base) & 15) != 0 || (key.stride1 & 15) != 0 || (key.stride2 & 15) != 0 ||
+        (key.stride3 & 15) != 0) {
         set_error("tensor map: base address and strides must be 16-byte aligned");
         return nullptr;
     }
     CUtensorMap map;
-    cuuint64_t dims[3] = {key.dim0, key.dim1, key.dim2};
-    cuuint64_t strides[2] = {key.stride1, key.stride2};
-    cuuint32_t box[3] = {key.box0, key.box1, key.box2};
-    cuuint32_t elem[3] = {1, 1, 1};
+    cuuint64_t dims[4] = {key.dim0, key.dim1, key.dim2, key.dim3};
+    cuuint64_t strides[3] = {key.stride1, key.stride2, key.stride3};
+    cuuint32_t box[4] = {key.box0, key.box1, key.box2, key.box3};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
     CUtensorMapSwizzle sw = key.swizzle == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
                             : key.swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                             : key.swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
@@ -101,6 +102,17 @@ const CUtensorMap* granite_cuda_compute::tensor_map_3d(const void* base, uint64_
                                                        uint32_t box2, int swizzle_bytes) {
     return encode_map(TensorMapKey{base, dim0, dim1, dim2, stride1_bytes, stride2_bytes, box0, box1, box2,
                                    swizzle_bytes, 3});
+}
+
+const CUtensorMap* granite_cuda_compute::tensor_map_pages(const void* base, uint32_t head_dim, uint64_t rows,
+                                                          uint64_t row_stride_bytes, uint64_t heads,
+                                                          uint64_t head_stride_bytes, uint32_t rows_per_box,
+                                                          uint32_t tile_heads) {
+    TensorMapKey key{base, 64, rows, head_dim / 64, row_stride_bytes, 128, 64, rows_per_box, head_dim / 64, 128, 4};
+    key.dim3 = heads;
+    key.stride3 = head_stride_bytes;
+    key.box3 = tile_heads;
+    return encode_map(key);
 }
 
 cudaEvent_t granite_cuda_compute::take_event() {

@@ -43,10 +43,12 @@ struct TensorMapKey {
     uint32_t box0, box1, box2;
     int swizzle;
     int rank;
+    uint64_t dim3 = 0, stride3 = 0;  // rank 4 only
+    uint32_t box3 = 0;
     bool operator<(const TensorMapKey& o) const {
-        return std::tie(base, dim0, dim1, dim2, stride1, stride2, box0, box1, box2, swizzle, rank) <
-               std::tie(o.base, o.dim0, o.dim1, o.dim2, o.stride1, o.stride2, o.box0, o.box1, o.box2,
-                        o.swizzle, o.rank);
+        return std::tie(base, dim0, dim1, dim2, dim3, stride1, stride2, stride3, box0, box1, box2, box3, swizzle, rank) <
+               std::tie(o.base, o.dim0, o.dim1, o.dim2, o.dim3, o.stride1, o.stride2, o.stride3, o.box0, o.box1,
+                        o.box2, o.box3, o.swizzle, o.rank);
     }
 };
 
@@ -85,6 +87,12 @@ struct granite_cuda_compute {
     const CUtensorMap* tensor_map_3d(const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
                                      uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
                                      uint32_t box1, uint32_t box2, int swizzle_bytes);
+    // One K (or V) page of a tile of KV heads as a single box: dims {64 halfs, rows, 64-wide chunks
+    // of a head, heads}, box {64, 16 rows, all chunks, tile_heads}; lands in shared memory as
+    // [head][chunk][row][64] under the 128-byte swizzle.
+    const CUtensorMap* tensor_map_pages(const void* base, uint32_t head_dim, uint64_t rows, uint64_t row_stride_bytes,
+                                        uint64_t heads, uint64_t head_stride_bytes, uint32_t rows_per_box,
+                                        uint32_t tile_heads);
     const CUtensorMap* encode_map(const gb200::TensorMapKey& key);
 };
 

@@ -31,7 +31,7 @@ constexpr int kHeadDim = 128;  // the benchmarked head size; the decode kernel i
 constexpr int kPageTokens = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxSlots = 16;
+constexpr int kMaxSlots = 32;
 
 struct DecodeParams {
     const float* q;
@@ -187,7 +187,13 @@ struct SegmentWalker {
     }
 };
 
-template <int NT, int D>
+#ifndef GB_DECODE_PAGES_PER_ITER_D128
+#define GB_DECODE_PAGES_PER_ITER_D128 1
+#endif
+#ifndef GB_DECODE_PAGES_PER_ITER_D64
+#define GB_DECODE_PAGES_PER_ITER_D64 2
+#endif
+template <int NT, int D, int PP = (D == 64 ? GB_DECODE_PAGES_PER_ITER_D64 : GB_DECODE_PAGES_PER_ITER_D128)>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
@@ -231,10 +237,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             tma_prefetch_desc(&kmap);
             tma_prefetch_desc(&vmap);
         }
-        const int nbox = p.tile_heads * kChunks;  // (head, 64-half chunk) boxes per page per tensor
-        const bool is_v = lane >= 16;
-        const int box = lane & 15;
-        const CUtensorMap* map = is_v ? &vmap : &kmap;
+        // One TMA instruction moves a whole K (or V) page of the head tile: the box spans
+        // {64 halfs, 16 rows, the head's 64-wide chunks, tile_heads heads} and lands as
+        // [head][chunk][row][64].  Lane 0 issues K, lane 1 issues V.
+        const CUtensorMap* map = lane == 1 ? &vmap : &kmap;
         while (walk.next(seg)) {
             const int head0 = seg.head_tile * p.tile_heads;
             for (int j0 = 0; j0 < seg.npages; j0 += 32) {
@@ -257,32 +263,19 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     int slot_k = slot; uint32_t ph_k = phase; advance();
                     int slot_v = slot; uint32_t ph_v = phase; advance();
                     int ok = 1;
-                    if (lane == 0) {
-                        ok = mbar_wait(&empty[slot_k], ph_k ^ 1, abort_flag) &&
-                             mbar_wait(&empty[slot_v], ph_v ^ 1, abort_flag);
+                    if (lane < 2) {
+                        const int my_slot = lane ? slot_v : slot_k;
+                        ok = mbar_wait(&empty[my_slot], (lane ? ph_v : ph_k) ^ 1, abort_flag);
                         if (ok) {
-                            mbar_arrive_expect_tx(&full[slot_k], slot_bytes);
-                            mbar_arrive_expect_tx(&full[slot_v], slot_bytes);
+                            mbar_arrive_expect_tx(&full[my_slot], slot_bytes);
+                            // contiguous cache: dim 3 runs over (sequence, head); pool: over heads
+                            const int w = p.contiguous ? seg.seq * p.num_kv_heads + head0 : head0;
+                            tma_load_4d(smem + (size_t)my_slot * slot_bytes, map, &full[my_slot], 0, entry * kPageTokens, 0, w);
                         }
                     }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) {
+                    if (!__all_sync(0xffffffffu, ok)) {
                         if (lane == 0) atomicOr(p.status, kStatusTimeout);
                         return;
-                    }
-                    if (box < nbox) {
-                        const int h = box / kChunks, chunk = box % kChunks;
-                        const int my_slot = is_v ? slot_v : slot_k;
-                        uint8_t* dst = smem + (size_t)my_slot * slot_bytes + h * kHeadPageBytes + chunk * 2048;
-                        int x, y;
-                        if (p.contiguous) {
-                            x = chunk * 64;
-                            y = (seg.seq * p.num_kv_heads + head0 + h) * p.max_seq + entry * kPageTokens;
-                        } else {
-                            x = (head0 + h) * D + chunk * 64;
-                            y = entry * kPageTokens;
-                        }
-                        tma_load_2d(dst, map, &full[my_slot], x, y);
                     }
                 }
             }
@@ -345,113 +338,169 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 for (int i = 0; i < 4; i++) o[nt][mt][i] = 0.f;
         }
 
-        for (int j = 0; j < seg.npages; j++) {
-            const int logical = seg.page_begin + j;
-            const int ntok = min(kPageTokens, len - logical * kPageTokens);
-            const int slot_k = slot; const uint32_t ph_k = phase; advance();
-            const int slot_v = slot; const uint32_t ph_v = phase; advance();
+        // PP pages per iteration.  With head_dim 64 a page is half the bytes for the same chain of
+        // waits, shuffles and exponentials, so two pages share one softmax round (32 tokens) and
+        // their MMA chains interleave.
+        for (int j = 0; j < seg.npages; j += PP) {
+            int ntok[PP], slot_k[PP], slot_v[PP];
+            uint32_t ph_k[PP], ph_v[PP];
+            bool has[PP];
+#pragma unroll
+            for (int pp = 0; pp < PP; pp++) {
+                has[pp] = j + pp < seg.npages;
+                ntok[pp] = 0;
+                slot_k[pp] = slot_v[pp] = 0;
+                ph_k[pp] = ph_v[pp] = 0;
+                if (has[pp]) {
+                    ntok[pp] = min(kPageTokens, len - (seg.page_begin + j + pp) * kPageTokens);
+                    slot_k[pp] = slot; ph_k[pp] = phase; advance();
+                    slot_v[pp] = slot; ph_v[pp] = phase; advance();
+                }
+            }
 
             // ---- S^T = K Q^T
-            if (!mbar_wait(&full[slot_k], ph_k, abort_flag)) {
-                if (lane == 0) atomicOr(p.status, kStatusTimeout);
-                return;
+            float sa[PP][NT][4], sb[PP][NT][4];
+            uint32_t kbase[PP];
+#pragma unroll
+            for (int pp = 0; pp < PP; pp++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) sa[pp][nt][i] = sb[pp][nt][i] = 0.f;
+                kbase[pp] = smem_base + slot_k[pp] * slot_bytes + k_row * 128;
+                if (has[pp] && !mbar_wait(&full[slot_k[pp]], ph_k[pp], abort_flag)) {
+                    if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                    return;
+                }
             }
-            float sa[NT][4], sb[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) sa[nt][i] = sb[nt][i] = 0.f;
-            const uint32_t kbase = smem_base + slot_k * slot_bytes + k_row * 128;
 #pragma unroll
             for (int ks = 0; ks < kDSteps; ks++) {
-                uint32_t a[4];
                 const int unit = (ks & 3) * 2 + k_unit;
-                ldmatrix_x4(a, kbase + (ks >> 2) * 2048 + ((unit ^ (k_row & 7)) << 4));
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    mma_16816(sa[nt], a, qhi[nt][ks][0], qhi[nt][ks][1]);
-                    mma_16816(sb[nt], a, qlo[nt][ks][0], qlo[nt][ks][1]);
+                for (int pp = 0; pp < PP; pp++) {
+                    if (pp > 0 && !has[pp]) continue;  // warp-uniform
+                    uint32_t a[4];
+                    ldmatrix_x4(a, kbase[pp] + (ks >> 2) * 2048 + ((unit ^ (k_row & 7)) << 4));
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        mma_16816(sa[pp][nt], a, qhi[nt][ks][0], qhi[nt][ks][1]);
+                        mma_16816(sb[pp][nt], a, qlo[nt][ks][0], qlo[nt][ks][1]);
+                    }
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot_k]);
+            if (lane == 0) {
+#pragma unroll
+                for (int pp = 0; pp < PP; pp++)
+                    if (has[pp]) mbar_arrive(&empty[slot_k[pp]]);
+            }
 
-            // ---- online softmax (lane holds tokens g, g+8 for heads 2t, 2t+1 of each n-tile)
-            uint32_t phi[NT][2], plo[NT][2];
-            float alpha[NT][2];
+            // ---- online softmax (lane holds tokens g, g+8 of each page for heads 2t, 2t+1 of each n-tile)
+            uint32_t phi[PP][NT][2], plo[PP][NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                float s0 = sa[nt][0] + sb[nt][0], s1 = sa[nt][1] + sb[nt][1];
-                float s2 = sa[nt][2] + sb[nt][2], s3 = sa[nt][3] + sb[nt][3];
-                if (g >= ntok) s0 = s1 = -INFINITY;
-                if (g + 8 >= ntok) s2 = s3 = -INFINITY;
-                float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+                float s[PP][4];
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int pp = 0; pp < PP; pp++) {
+                    s[pp][0] = sa[pp][nt][0] + sb[pp][nt][0];
+                    s[pp][1] = sa[pp][nt][1] + sb[pp][nt][1];
+                    s[pp][2] = sa[pp][nt][2] + sb[pp][nt][2];
+                    s[pp][3] = sa[pp][nt][3] + sb[pp][nt][3];
+                    if (g >= ntok[pp]) s[pp][0] = s[pp][1] = -INFINITY;
+                    if (g + 8 >= ntok[pp]) s[pp][2] = s[pp][3] = -INFINITY;
+                    mx0 = fmaxf(mx0, fmaxf(s[pp][0], s[pp][2]));
+                    mx1 = fmaxf(mx1, fmaxf(s[pp][1], s[pp][3]));
+                }
 #pragma unroll
                 for (int sh = 4; sh < 32; sh <<= 1) {
                     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
                 }
                 const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
-                alpha[nt][0] = fast_exp2(m_run[nt][0] - mn0);
-                alpha[nt][1] = fast_exp2(m_run[nt][1] - mn1);
+                const float alpha0 = fast_exp2(m_run[nt][0] - mn0);
+                const float alpha1 = fast_exp2(m_run[nt][1] - mn1);
                 m_run[nt][0] = mn0;
                 m_run[nt][1] = mn1;
-                const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1);
-                const float p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
-                l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + p0 + p2;
-                l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + p1 + p3;
-                __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-                float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
-                __half2 l01 = __floats2half2_rn(p0 - b01.x, p1 - b01.y);
-                __half2 l23 = __floats2half2_rn(p2 - b23.x, p3 - b23.y);
-                // C-fragment layout -> B-fragment layout: transpose the 8x8 (token, head) blocks
-                phi[nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h01));
-                phi[nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h23));
-                plo[nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l01));
-                plo[nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l23));
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int pp = 0; pp < PP; pp++) {
+                    const float p0 = fast_exp2(s[pp][0] - mn0), p1 = fast_exp2(s[pp][1] - mn1);
+                    const float p2 = fast_exp2(s[pp][2] - mn0), p3 = fast_exp2(s[pp][3] - mn1);
+                    if (pp == 0) {
+                        sum0 = p0 + p2;
+                        sum1 = p1 + p3;
+                    } else {
+                        sum0 += p0 + p2;
+                        sum1 += p1 + p3;
+                    }
+                    __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+                    float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+                    __half2 l01 = __floats2half2_rn(p0 - b01.x, p1 - b01.y);
+                    __half2 l23 = __floats2half2_rn(p2 - b23.x, p3 - b23.y);
+                    // C-fragment layout -> B-fragment layout: transpose the 8x8 (token, head) blocks
+                    phi[pp][nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h01));
+                    phi[pp][nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&h23));
+                    plo[pp][nt][0] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l01));
+                    plo[pp][nt][1] = movmatrix_trans(*reinterpret_cast<uint32_t*>(&l23));
+                }
+                l_run[nt][0] = l_run[nt][0] * alpha0 + sum0;
+                l_run[nt][1] = l_run[nt][1] * alpha1 + sum1;
 #pragma unroll
                 for (int mt = 0; mt < kDSteps; mt++) {
-                    o[nt][mt][0] *= alpha[nt][0];
-                    o[nt][mt][1] *= alpha[nt][1];
-                    o[nt][mt][2] *= alpha[nt][0];
-                    o[nt][mt][3] *= alpha[nt][1];
+                    o[nt][mt][0] *= alpha0;
+                    o[nt][mt][1] *= alpha1;
+                    o[nt][mt][2] *= alpha0;
+                    o[nt][mt][3] *= alpha1;
                 }
             }
 
             // ---- O^T += V^T P^T
-            if (!mbar_wait(&full[slot_v], ph_v, abort_flag)) {
-                if (lane == 0) atomicOr(p.status, kStatusTimeout);
-                return;
-            }
-            const uint32_t vslot = smem_base + slot_v * slot_bytes;
-            if (ntok < kPageTokens) {
-                // rows past the sequence end may hold anything (even NaN): zero them so that
-                // 0 * garbage cannot poison the accumulators
-                uint8_t* vptr = smem + (size_t)slot_v * slot_bytes + kvh_local * kHeadPageBytes;
-                constexpr int kRowUnits = D / 8;  // 16-byte units per row
-                for (int i = lane; i < (kPageTokens - ntok) * kRowUnits; i += 32) {
-                    int r = ntok + i / kRowUnits, u = i % kRowUnits;
-                    int chunk = u >> 3, unit = u & 7;
-                    *reinterpret_cast<uint4*>(vptr + chunk * 2048 + r * 128 + ((unit ^ (r & 7)) << 4)) =
-                        make_uint4(0, 0, 0, 0);
+            uint32_t vbase[PP];
+#pragma unroll
+            for (int pp = 0; pp < PP; pp++) {
+                vbase[pp] = smem_base + slot_v[pp] * slot_bytes + v_row * 128;
+                if (!has[pp]) continue;
+                if (!mbar_wait(&full[slot_v[pp]], ph_v[pp], abort_flag)) {
+                    if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                    return;
                 }
-                __syncwarp();
+                if (ntok[pp] < kPageTokens) {
+                    // rows past the sequence end may hold anything (even NaN): zero them so that
+                    // 0 * garbage cannot poison the accumulators
+                    uint8_t* vptr = smem + (size_t)slot_v[pp] * slot_bytes + kvh_local * kHeadPageBytes;
+                    constexpr int kRowUnits = D / 8;  // 16-byte units per row
+                    for (int i = lane; i < (kPageTokens - ntok[pp]) * kRowUnits; i += 32) {
+                        int r = ntok[pp] + i / kRowUnits, u = i % kRowUnits;
+                        int chunk = u >> 3, unit = u & 7;
+                        *reinterpret_cast<uint4*>(vptr + chunk * 2048 + r * 128 + ((unit ^ (r & 7)) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
             }
-            const uint32_t vbase = vslot + v_row * 128;
 #pragma unroll
             for (int mt = 0; mt < kDSteps; mt++) {
-                uint32_t a[4];
                 const int unit = (mt & 3) * 2 + v_unit;
-                ldmatrix_x4_trans(a, vbase + (mt >> 2) * 2048 + ((unit ^ (v_row & 7)) << 4));
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    mma_16816(o[nt][mt], a, phi[nt][0], phi[nt][1]);
-                    mma_16816(o[nt][mt], a, plo[nt][0], plo[nt][1]);
+                for (int pp = 0; pp < PP; pp++) {
+                    if (pp > 0 && !has[pp]) continue;  // warp-uniform; an absent page's slot holds other data
+                    uint32_t a[4];
+                    ldmatrix_x4_trans(a, vbase[pp] + (mt >> 2) * 2048 + ((unit ^ (v_row & 7)) << 4));
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        mma_16816(o[nt][mt], a, phi[pp][nt][0], phi[pp][nt][1]);
+                        mma_16816(o[nt][mt], a, plo[pp][nt][0], plo[pp][nt][1]);
+                    }
                 }
             }
             __syncwarp();
-            if (ntok < kPageTokens) fence_proxy_async_smem();
-            if (lane == 0) mbar_arrive(&empty[slot_v]);
+#pragma unroll
+            for (int pp = 0; pp < PP; pp++) {
+                if (!has[pp]) continue;
+                if (ntok[pp] < kPageTokens) fence_proxy_async_smem();
+                if (lane == 0) mbar_arrive(&empty[slot_v[pp]]);
+            }
         }
 
         // ---- segment result
@@ -659,14 +708,15 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
 
     const CUtensorMap *kmap, *vmap;
     if (contiguous) {
-        const uint64_t rows = (uint64_t)a.batch_size * hkv * max_seq;
-        kmap = c->tensor_map_2d(a.k_cache, D, rows, D * 2, 64, kPageTokens, 128);
-        vmap = c->tensor_map_2d(a.v_cache, D, rows, D * 2, 64, kPageTokens, 128);
+        // [batch, Hkv, max_seq, D]: rows of one (sequence, head); a box past max_seq reads zeros
+        const uint64_t planes = (uint64_t)a.batch_size * hkv;
+        kmap = c->tensor_map_pages(a.k_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, tile_heads);
+        vmap = c->tensor_map_pages(a.v_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, tile_heads);
     } else {
+        // [num_blocks * 16, Hkv, D]
         const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens;
-        const uint64_t width = (uint64_t)hkv * D;
-        kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageTokens, 128);
-        vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageTokens, 128);
+        kmap = c->tensor_map_pages(a.k_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, tile_heads);
+        vmap = c->tensor_map_pages(a.v_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, tile_heads);
     }
     if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
@@ -757,7 +807,7 @@ static int static_decode_setup(int device, StaticDeviceSetup** out) {
 }
 
 // A tensor map built on the stack (the compute object's cache would allocate host memory).
-static int encode_pool_map(CUtensorMap* map, const void* base, uint64_t width_elems, uint64_t rows) {
+static int encode_pool_map(CUtensorMap* map, const void* base, uint64_t heads, uint64_t rows, uint32_t tile_heads) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -772,11 +822,12 @@ static int encode_pool_map(CUtensorMap* map, const void* base, uint64_t width_el
     if (!enc) return fail(GRANITE_CUDA_BACKEND_NOT_INITIALIZED, "static decode: cuTensorMapEncodeTiled unavailable");
     if (reinterpret_cast<uintptr_t>(base) & 15)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: K/V pools must be 16-byte aligned");
-    cuuint64_t dims[2] = {width_elems, rows};
-    cuuint64_t strides[1] = {width_elems * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)kPageTokens};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+    // same shape as granite_cuda_compute::tensor_map_pages for the pool [rows, heads, 128]
+    cuuint64_t dims[4] = {64, rows, kHeadDim / 64, heads};
+    cuuint64_t strides[3] = {heads * kHeadDim * 2, 128, kHeadDim * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)kPageTokens, kHeadDim / 64, tile_heads};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -870,9 +921,9 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     // prefix sums, first-sequence table and partials are fully rewritten before they are read
 
     CUtensorMap kmap, vmap;
-    const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens, width = (uint64_t)hkv * kHeadDim;
-    if ((rc = encode_pool_map(&kmap, a.k_cache, width, rows)) != 0) return rc;
-    if ((rc = encode_pool_map(&vmap, a.v_cache, width, rows)) != 0) return rc;
+    const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens;
+    if ((rc = encode_pool_map(&kmap, a.k_cache, hkv, rows, tile_heads)) != 0) return rc;
+    if ((rc = encode_pool_map(&vmap, a.v_cache, hkv, rows, tile_heads)) != 0) return rc;
 
     decode_plan_kernel<<<1, 1024, 0, st>>>(p);
     if (heads_per_warp <= 8)
