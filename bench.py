@@ -466,6 +466,9 @@ def main():
     ap.add_argument("--only", default="", choices=["", "prefill", "tree", "tree16", "step_write", "paged_prefill", "single_decode"],
                     help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (profiling captures)")
+    ap.add_argument("--head-dim", type=int, default=0, choices=[0, 64, 128],
+                    help="64: the same sequence lengths with head_dim 64 (the second build of the decode kernel; "
+                         "profiling captures and side measurements, not the benchmark line)")
     ap.add_argument("--sequences", type=int, default=0,
                     help="shrink the batch (profiling captures only; the benchmark uses the full workload)")
     args = ap.parse_args()
@@ -500,6 +503,8 @@ def main():
     cfg = dict(synth.CONFIGS[args.workload])
     if args.sequences > 0:
         cfg["batch"] = args.sequences
+    if args.head_dim:
+        cfg["head_dim"] = args.head_dim
     strong = args.workload != WORKLOAD
     if strong:
         # one fixed problem, sequences dealt to the ranks longest-first (granite_b200/sharding.py)
@@ -720,7 +725,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-            "config": {"workload": args.workload, "sequences_per_gpu": B,
+            "config": {"workload": args.workload + (f" (head_dim {D} variant)" if D != synth.CONFIGS[args.workload]["head_dim"] else ""),
+                       "sequences_per_gpu": B,
                        "context": f"{cfg['dist']}[{cfg['len_lo']},{cfg['len_hi']}]",
                        "page": synth.PAGE, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
                        "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
