@@ -441,7 +441,7 @@ def measure_single_decode(compute, dev, reps: int = 200):
     nbytes = 2 * hkv * ctx * d * 2 + hq * d * 4 * 2
     return {"workload": "decode_contiguous_ctx512", "kernels": "decode_plan + contiguous_decode_splitkv + decode_merge",
             "call_ms": ms, "graph_replay_ms": ms_graph, "launches": reps, "algorithmic_bytes": nbytes,
-            "bound": "launch latency (three dependent kernels)"}
+            "bound": "launch latency (three dependent kernels; a batch this small keeps the separate merge pass)"}
 
 
 def measure_tree16(compute, dev, reps: int = 200):
@@ -739,7 +739,8 @@ def main():
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "note": "host Q, block tables and lengths copied in (one pinned staging block), output copied out, sync per step; "
                             "K/V pages are cache state resident in HBM"},
-            "gpu_launches": 3 * args.steps,
+            # per rank and step: decode_plan + paged_decode_splitkv (+ push_rows when the rows are gathered by peer stores)
+            "gpu_launches": (3 if peer_ptrs is not None else 2) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "secondary": secondary,
         }

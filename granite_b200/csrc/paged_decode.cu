@@ -12,7 +12,7 @@
 // sequence, then page).  The list is cut into one equal contiguous range per CTA (one CTA per
 // SM), so the load is balanced to a page whatever the length distribution.  A range that holds
 // a whole sequence writes its output directly; a sequence cut by a range boundary leaves
-// un-normalised partials (m, l, o) that decode_merge_kernel combines.
+// un-normalised partials (m, l, o); the warp that finishes the sequence's last pages combines them.
 //
 // Inside a CTA: one producer warp walks the block table and has TMA copy each page - 16 rows of
 // up to 8 KV heads, one contiguous 32 KB piece of the pool - into a ring of shared-memory slots
@@ -56,6 +56,8 @@ struct DecodeParams {
     int d;                // head_dim: 128 or 64
     float* part_o;        // [2 * n_ctas][num_heads][d]
     float2* part_ml;      // [2 * n_ctas][num_heads]
+    int* pages_done;      // [batch][n_head_tiles][consumer warps]: pages of cut sequences finished so far
+    int fused_merge;      // 1: the warp that finishes a cut sequence merges it; 0: decode_merge_kernel follows
 };
 
 __device__ __forceinline__ long long range_start(long long total, int n_ctas, int c) {
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(DecodeParams p) {
         p.page_prefix[0] = 0;
     }
     __syncthreads();
+    if (p.fused_merge)
+        for (int i = tid; i < p.batch * p.n_head_tiles * kConsumerWarps; i += 1024) p.pages_done[i] = 0;
     const int max_len = p.contiguous ? p.max_seq : p.max_blocks * kPageTokens;
     for (int base = 0; base < p.batch; base += 1024) {
         int b = base + tid;
@@ -187,6 +191,92 @@ struct SegmentWalker {
     }
 };
 
+// ------------------------------------------------------------------------------------ merge
+// A sequence cut by range boundaries leaves one partial (m, l, o) per CTA that touched it.  The
+// consumer warp that finishes the last of its pages (counted per warp index, since the same warp
+// index owns the same heads in every CTA) combines them:
+//     out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c
+// always in CTA order, so the result does not depend on which warp came last.  Nothing waits: a
+// warp that is not last simply moves on.  Partials are read through L2 (written by other SMs).
+constexpr int kMaxMergeParts = 256;  // >= the largest grid the decode kernel is launched with
+template <int D>
+__device__ __forceinline__ void merge_cut_sequence(const DecodeParams& p, int b, int ht, int hq0, int n_q, int lane) {
+    const int total = p.page_prefix[p.batch];
+    const int s0 = p.page_prefix[b], s1 = p.page_prefix[b + 1];
+    const long long T = (long long)total * p.n_head_tiles;
+    const long long A = (long long)ht * total + s0, B = (long long)ht * total + s1;  // the sequence's pages [A, B)
+    auto cta_of = [&](long long P) {
+        int c = (int)((P * p.n_ctas) / T);
+        if (c >= p.n_ctas) c = p.n_ctas - 1;
+        while (c + 1 < p.n_ctas && range_start(T, p.n_ctas, c + 1) <= P) c++;
+        while (c > 0 && range_start(T, p.n_ctas, c) > P) c--;
+        return c;
+    };
+    const int c_lo = cta_of(A), c_hi = cta_of(B - 1);
+    const int n = min(c_hi - c_lo + 1, kMaxMergeParts);
+    // The first contributing range may hold the sequence as its second partial (slot 1); every
+    // later one starts inside the sequence, so the sequence is its first segment (slot 0).
+    // Ranges in between can be empty when there are fewer pages than CTAs: those wrote nothing.
+    int slot_l[kMaxMergeParts / 32];
+#pragma unroll
+    for (int k = 0; k < kMaxMergeParts / 32; k++) {
+        const int i = k * 32 + lane;
+        slot_l[k] = -1;
+        if (i < n) {
+            const int c = c_lo + i;
+            const bool empty = i > 0 && range_start(T, p.n_ctas, c) == range_start(T, p.n_ctas, c + 1);
+            if (!empty) slot_l[k] = i == 0 ? 2 * c + (range_start(T, p.n_ctas, c) >= A ? 0 : 1) : 2 * c;
+        }
+    }
+    for (int h = 0; h < n_q; h++) {
+        const int hq = hq0 + h;
+        float w_l[kMaxMergeParts / 32], l_l[kMaxMergeParts / 32];
+        float M = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < kMaxMergeParts / 32; k++) {
+            w_l[k] = -INFINITY;
+            l_l[k] = 0.f;
+            if (k * 32 < n && slot_l[k] >= 0) {
+                const float2 ml = __ldcg(p.part_ml + (size_t)slot_l[k] * p.num_heads + hq);
+                w_l[k] = ml.x;
+                l_l[k] = ml.y;
+            }
+            M = fmaxf(M, w_l[k]);
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+        float L = 0.f;
+#pragma unroll
+        for (int k = 0; k < kMaxMergeParts / 32; k++) {
+            w_l[k] = slot_l[k] >= 0 ? fast_exp2(w_l[k] - M) : 0.f;
+            L += w_l[k] * l_l[k];
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) L += __shfl_xor_sync(0xffffffffu, L, sh);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < kMaxMergeParts / 32; k++) {
+            if (k * 32 >= n) break;
+            const int lim = min(32, n - k * 32);
+            for (int j = 0; j < lim; j++) {
+                const int slot = __shfl_sync(0xffffffffu, slot_l[k], j);
+                const float w = __shfl_sync(0xffffffffu, w_l[k], j);
+                if (slot < 0 || lane * 4 >= D) continue;
+                const float4 o = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((size_t)slot * p.num_heads + hq) * D) + lane);
+                acc.x += w * o.x;
+                acc.y += w * o.y;
+                acc.z += w * o.z;
+                acc.w += w * o.w;
+            }
+        }
+        if (lane * 4 < D) {
+            const float inv = 1.0f / L;
+            *(reinterpret_cast<float4*>(p.out + ((size_t)b * p.num_heads + hq) * D) + lane) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        }
+    }
+}
+
 #ifndef GB_DECODE_PAGES_PER_ITER_D128
 #define GB_DECODE_PAGES_PER_ITER_D128 1
 #endif
@@ -297,6 +387,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     const int v_row = (lane & 7) + ((lane >> 4) & 1) * 8;
     const int v_unit = (lane >> 3) & 1;
     const uint32_t smem_base = smem_u32(smem) + kvh_local * kHeadPageBytes;
+    // cut sequences whose last pages this warp finished: merged after the walk (at most the first
+    // and the last segment of a range are cut), so that the page ring never waits for a merge
+    int merge_seq[2] = {-1, -1}, merge_ht[2] = {0, 0};
 
     while (walk.next(seg)) {
         const int kvh = seg.head_tile * p.tile_heads + kvh_local;
@@ -536,17 +629,46 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 }
             }
         }
+        if (seg.slot >= 0 && p.fused_merge) {
+            // publish the partial, then count this warp's pages of the sequence; the warp whose
+            // count completes the sequence merges (release: fence before the add; acquire: after)
+            __threadfence();
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                int* done = p.pages_done + ((size_t)seg.seq * p.n_head_tiles + seg.head_tile) * kConsumerWarps + warp;
+                last = atomicAdd(done, seg.npages) + seg.npages == seg.seq_pages;
+                __threadfence();
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                if (seg.slot & 1) {
+                    merge_seq[1] = seg.seq;
+                    merge_ht[1] = seg.head_tile;
+                } else {
+                    merge_seq[0] = seg.seq;
+                    merge_ht[0] = seg.head_tile;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        if (merge_seq[i] < 0) continue;
+        const int kvh = merge_ht[i] * p.tile_heads + kvh_local;
+        merge_cut_sequence<D>(p, merge_seq[i], merge_ht[i], kvh * p.group + first_q, n_q, lane);
     }
 }
 
 // ------------------------------------------------------------------------------------ merge
+// Separate merge pass, used when the batch is small against the number of CTAs (a sequence is then
+// cut into many partials, which one warp would combine too slowly inside the decode kernel).
 // grid (batch, num_heads), 256 threads.  Combines the partials of a sequence that was cut by CTA
 // range boundaries:  out = sum_c 2^(m_c-M) o_c / sum_c 2^(m_c-M) l_c.  A single long sequence is cut
 // by every CTA (a batch of one leaves as many partials as there are SMs), so the partials are
 // spread over the block: one thread per partial for the maxima and weights, one warp per eighth
 // of the partials (a lane per four output dims) for the weighted sum.
 constexpr int kMergeThreads = 256;
-constexpr int kMaxMergeParts = 256;  // >= the largest grid the decode kernel is launched with
 __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParams p) {
     __shared__ float s_w[kMaxMergeParts];
     __shared__ int s_slot[kMaxMergeParts];
@@ -632,6 +754,13 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParam
 // ------------------------------------------------------------------------------------ host
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// In-kernel merging costs one warp about a microsecond per handful of partials; it pays when a
+// sequence is cut into few pieces, i.e. when there are at least a quarter as many (sequence,
+// head tile) pairs as CTAs.  Smaller batches leave tens of partials per sequence to the merge kernel.
+static int fused_merge_pays(int batch, int n_head_tiles, int n_ctas) {
+    return (long long)batch * n_head_tiles * 4 >= n_ctas ? 1 : 0;
+}
+
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
                         bool contiguous, uint32_t max_seq) {
     if (!a.q || !a.k_cache || !a.v_cache || !a.output || (!contiguous && !a.block_tables))
@@ -677,12 +806,13 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.n_head_tiles = hkv / tile_heads;
     p.heads_per_warp = heads_per_warp;
     p.active_warps = subs_active * tile_heads;
-    p.n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds one partial per thread
+    p.n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds up to 8 partials per lane
     p.contiguous = contiguous ? 1 : 0;
     p.max_seq = (int)max_seq;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = c->d_status;
     p.d = D;
+    p.fused_merge = fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
 
     const int slot_bytes = tile_heads * kPageTokens * D * 2;
     const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
@@ -698,6 +828,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     const size_t off_first = off;  off = align_up(off + (size_t)p.n_ctas * 4, 256);
     const size_t off_ml = off;     off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * sizeof(float2), 256);
     const size_t off_o = off;      off = align_up(off + (size_t)2 * p.n_ctas * p.num_heads * D * 4, 256);
+    const size_t off_done = off;   off = align_up(off + (size_t)p.batch * p.n_head_tiles * kConsumerWarps * 4, 256);
     int rc = c->ensure_scratch(off);
     if (rc) return rc;
     uint8_t* ws = static_cast<uint8_t*>(c->scratch);
@@ -705,6 +836,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.cta_first_seq = reinterpret_cast<int*>(ws + off_first);
     p.part_ml = reinterpret_cast<float2*>(ws + off_ml);
     p.part_o = reinterpret_cast<float*>(ws + off_o);
+    p.pages_done = reinterpret_cast<int*>(ws + off_done);
 
     const CUtensorMap *kmap, *vmap;
     if (contiguous) {
@@ -731,7 +863,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         LaunchScope t(c, contiguous ? "contiguous_decode_splitkv" : "paged_decode_splitkv");
         kern<<<p.n_ctas, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
     }
-    {
+    if (!p.fused_merge) {
         LaunchScope t(c, "decode_merge");
         decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, c->stream>>>(p);
     }
@@ -750,7 +882,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
 // acceptable.  For them the scratch that the split-KV decode needs (page prefix sums, the first
 // sequence of every CTA range, and the partial (m, l, o) of sequences cut by a range boundary)
 // lives in the fixed device array below instead of the compute object's growable arena.
-// Every GPU that loads the library carries these ~12.7 MB until the process exits.
+// Every GPU that loads the library carries these ~13.8 MB until the process exits.
 // =====================================================================================
 namespace gb200 {
 
@@ -762,7 +894,9 @@ constexpr size_t kStaticOffPrefix = 256;
 constexpr size_t kStaticOffFirst = kStaticOffPrefix + ((size_t)(kStaticMaxBatch + 1) * 4 + 255) / 256 * 256;
 constexpr size_t kStaticOffMl = kStaticOffFirst + ((size_t)kStaticMaxCtas * 4 + 255) / 256 * 256;
 constexpr size_t kStaticOffO = kStaticOffMl + (size_t)2 * kStaticMaxCtas * kStaticMaxHeads * sizeof(float2);
-constexpr size_t kStaticScratchBytes = kStaticOffO + (size_t)2 * kStaticMaxCtas * kStaticMaxHeads * kHeadDim * 4;
+constexpr size_t kStaticOffDone = kStaticOffO + (size_t)2 * kStaticMaxCtas * kStaticMaxHeads * kHeadDim * 4;
+// page counters: at most kStaticMaxHeads / 8 head tiles (eight KV heads per tile, or one tile)
+constexpr size_t kStaticScratchBytes = kStaticOffDone + (size_t)kStaticMaxBatch * (kStaticMaxHeads / 8) * kConsumerWarps * 4;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
 static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
@@ -910,6 +1044,8 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     p.cta_first_seq = reinterpret_cast<int*>(ws + kStaticOffFirst);
     p.part_ml = reinterpret_cast<float2*>(ws + kStaticOffMl);
     p.part_o = reinterpret_cast<float*>(ws + kStaticOffO);
+    p.pages_done = reinterpret_cast<int*>(ws + kStaticOffDone);
+    p.fused_merge = fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
     p.d = kHeadDim;
     if (device_status) {
         p.status = device_status;  // the caller owns and clears it
@@ -930,7 +1066,7 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
         paged_decode_kernel<1, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
     else
         paged_decode_kernel<2, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
-    decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, st>>>(p);
+    if (!p.fused_merge) decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, st>>>(p);
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }

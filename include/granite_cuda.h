@@ -137,7 +137,7 @@ int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c,
  * device-wide synchronisation hidden in cudaMalloc/cudaFree.  Same arguments, layouts, limits and
  * results as granite_cuda_batched_paged_attention_decode, but it needs no compute object and
  * calls no cudaMalloc, cudaFree or other allocating routine: its scratch (prefix sums and the
- * partials of sequences split across SMs) is a fixed ~12.7 MB array that every GPU which loads
+ * partials of sequences split across SMs) is a fixed ~13.8 MB array that every GPU which loads
  * this library holds until the process exits.
  *   - Limits: batch_size <= 4096, num_heads <= 64, at most 192 SMs; beyond them the call returns
  *     GRANITE_CUDA_BUFFER_TOO_SMALL and launches nothing.

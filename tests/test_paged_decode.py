@@ -75,6 +75,25 @@ def test_paged_decode_many_short_sequences(compute):
     assert_attention_close(got, _oracle(case, k_np, v_np), "600 short sequences")
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (32, 16, 128), (32, 4, 128), (14, 2, 64), (64, 8, 64)])
+def test_cut_sequences_merged_inside_the_decode_kernel(compute, hq, hkv, d):
+    """Batches large enough for the in-kernel merge (the warp that finishes a cut sequence's last pages
+    combines its partials): one sequence cut by almost every CTA among short and empty ones, and a
+    batch of mid-sized sequences cut two or three times each.  Same bits on a second run."""
+    rng = np.random.default_rng(hq * 100 + hkv)
+    skewed = rng.integers(0, 200, size=48).astype(np.int32)
+    skewed[17] = 20000
+    skewed[3] = 0
+    middling = rng.integers(1500, 4000, size=40).astype(np.int32)
+    for name, lens in (("one long among short", skewed), ("forty mid-sized", middling)):
+        case = synth.paged_case(seed=21, batch=len(lens), len_lo=0, len_hi=0, num_heads=hq, num_kv_heads=hkv,
+                                head_dim=d, seq_lens=lens)
+        got, k_np, v_np = _run_paged(compute, case)
+        assert_attention_close(got, _oracle(case, k_np, v_np), f"{name}, Hq={hq} Hkv={hkv} D={d}")
+        again, _, _ = _run_paged(compute, case)
+        assert np.array_equal(got, again), name
+
+
 def test_single_sequence_paged_decode(compute):
     import torch
     case = synth.paged_case(seed=13, batch=1, len_lo=0, len_hi=0, seq_lens=np.array([777], np.int32))
