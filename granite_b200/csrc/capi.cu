@@ -115,6 +115,15 @@ const CUtensorMap* granite_cuda_compute::tensor_map_pages(const void* base, uint
     return encode_map(key);
 }
 
+const CUtensorMap* granite_cuda_compute::tensor_map_page_groups(const void* base, uint64_t width, uint64_t rows,
+                                                                uint32_t head_dim) {
+    TensorMapKey key{base, width, 8, head_dim / 64, width * 2, 128, 64, 8, head_dim / 64, 128, 4};
+    key.dim3 = rows / 8;
+    key.stride3 = width * 2 * 8;
+    key.box3 = 2;
+    return encode_map(key);
+}
+
 cudaEvent_t granite_cuda_compute::take_event() {
     if (!event_pool.empty()) {
         cudaEvent_t e = event_pool.back();

@@ -93,6 +93,10 @@ struct granite_cuda_compute {
     const CUtensorMap* tensor_map_pages(const void* base, uint32_t head_dim, uint64_t rows, uint64_t row_stride_bytes,
                                         uint64_t heads, uint64_t head_stride_bytes, uint32_t rows_per_box,
                                         uint32_t tile_heads);
+    // The pool [rows, width halfs] (width = Hkv * head_dim) seen in groups of 8 rows: dims {width,
+    // 8 rows, 64-wide chunks of a head, rows / 8}, box {64, 8, all chunks, 2} = one 16-row page of one
+    // head, landing as [row group][chunk][8 rows][64]; x selects the head (x = head * head_dim).
+    const CUtensorMap* tensor_map_page_groups(const void* base, uint64_t width, uint64_t rows, uint32_t head_dim);
     const CUtensorMap* encode_map(const gb200::TensorMapKey& key);
 };
 

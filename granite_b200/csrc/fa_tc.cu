@@ -167,6 +167,12 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.num_nodes;
     const int hd = p.d_chunks * 64;  // head_dim
+    // K/V tile layout in shared memory.  Contiguous caches: [chunk][128 rows][64 halfs] (8-row groups 1 KB
+    // apart, the second 64 dims 16 KB further).  Paged pool: one TMA box per page lands as
+    // [row group][chunk][8 rows][64], so the groups are head_dim * 16 bytes apart and the second 64 dims
+    // of a group follow its first after 1 KB; the MMA descriptors take either pitch.
+    const uint32_t group_bytes = kPaged ? 1024u * p.d_chunks : 1024u;
+    const uint32_t chunk_off = kPaged ? 1024u : (uint32_t)kChunkBytes;
 #ifdef GB_FA_TRACE
     if (threadIdx.x == 0) {
         unsigned long long gt;
@@ -337,17 +343,23 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         if (!alive) break;
                         uint8_t* dst = is_v ? vd : kd;
                         if (tree_step) {
-                            // tree K/V [batch*Hkv, N, 128]: 64-row boxes; rows >= N are zero-filled by TMA
-                            if (lane < p.d_chunks)
+                            if (kPaged) {
+                                // tree K/V [batch*Hkv, N, 128] in the grouped layout: lane = (row group, chunk),
+                                // 8-row boxes; rows >= N are zero-filled by TMA
+                                const int g = lane >> 1;
+                                if (lane < 16 && c < p.d_chunks)
+                                    tma_load_3d(dst + g * group_bytes + c * 1024, is_v ? &vtmap : &ktmap, full, c * 64, g * 8,
+                                                it.b * p.num_kv_heads + it.kvh);
+                            } else if (lane < p.d_chunks) {
+                                // tree K/V [batch*Hkv, N, 128]: 64-row boxes; rows >= N are zero-filled by TMA
                                 tma_load_3d(dst + c * kChunkBytes, is_v ? &vtmap : &ktmap, full, c * 64, 0,
                                             it.b * p.num_kv_heads + it.kvh);
+                            }
                         } else if (kPaged) {
-                            // lane = (page, chunk): 8 pages x 2 chunks
-                            const int pg = (lane >> 1) & 7;
-                            const int e = __shfl_sync(0xffffffffu, entry, pg);
-                            if (lane < 16 && c < p.d_chunks)
-                                tma_load_2d(dst + c * kChunkBytes + pg * 2048, is_v ? &vmap : &kmap, full,
-                                            it.kvh * hd + c * 64, e * kPageRows);
+                            // lane = page: one box per 16-row page (both row groups, all chunks of the head)
+                            const int e = __shfl_sync(0xffffffffu, entry, lane & 7);
+                            if (lane < 8)
+                                tma_load_4d(dst + lane * 2 * group_bytes, is_v ? &vmap : &kmap, full, it.kvh * hd, 0, 0, e * 2);
                         } else if (lane < p.d_chunks) {
                             // contiguous cache [.., max rows, 128]: one 128-row box per chunk
                             const int y = kTree ? (it.b * p.num_kv_heads + it.kvh) * p.cache_stride + j * kT
@@ -370,6 +382,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                 constexpr uint32_t idesc_qk_tree = umma_idesc_f16(kT, kNodeSlots, false, false);
                 const uint32_t q_lo0 = desc_lo(smem_u32(q_smem), 16);
                 const uint32_t k_lo0 = desc_lo(smem_u32(k_smem), 16);
+                const uint32_t k_hi = desc_hi_sw128(group_bytes);
                 bool ok = true;
                 int st = 0, items_done = 0;
                 int vs = 0;  // virtual steps issued so far across items: S buffer = vs & 1
@@ -401,7 +414,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             for (int ks = 0; ks < 8; ks++) {
                                 if (ks < 4 * p.d_chunks) {
                                     const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-                                    umma_ss_words(d, q_lo + off, k_lo + off, kDescHiSw128, idesc, ks > 0 ? 1u : 0u);
+                                    const uint32_t off_k = ((ks >> 2) * chunk_off + (ks & 3) * 32) >> 4;
+                                    umma_ss_words2(d, q_lo + off, kDescHiSw128, k_lo + off_k, k_hi, idesc, ks > 0 ? 1u : 0u);
                                 }
                             }
                             if (kSplitQ) {
@@ -409,7 +423,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                                 for (int ks = 0; ks < 8; ks++) {
                                     if (ks < 4 * p.d_chunks) {
                                         const uint32_t off = ((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4;
-                                        umma_ss_words(d, q_lo0 + (kTileBytes >> 4) + off, k_lo + off, kDescHiSw128, idesc, 1u);
+                                        const uint32_t off_k = ((ks >> 2) * chunk_off + (ks & 3) * 32) >> 4;
+                                        umma_ss_words2(d, q_lo0 + (kTileBytes >> 4) + off, kDescHiSw128, k_lo + off_k, k_hi, idesc, 1u);
                                     }
                                 }
                             }
@@ -434,7 +449,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             if (lane == 0) {
                 const uint32_t idesc_pv = umma_idesc_f16(kT, hd, false, true);  // N = head_dim output columns
                 const uint32_t part = warp - 2;  // 0: hi, 1: lo
-                const uint32_t v_lo0 = desc_lo(smem_u32(v_smem), kChunkBytes);
+                const uint32_t v_lo0 = desc_lo(smem_u32(v_smem), chunk_off);  // leading offset: the second 64 dims
+                const uint32_t v_hi = desc_hi_sw128(group_bytes);
                 bool ok = true;
                 int st = 0, vs = 0, items_done = 0;
                 uint32_t ph = 0;
@@ -460,12 +476,12 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                             tc_fence_after_sync();
                             const uint32_t d = tmem + 2 * kT + (t + o_sel) * kT;
                             // P: hi in columns 0-63 of S_b, lo in 64-127, 8 columns per 16 keys;
-                            // V MN-major: 16 keys = 2 KB further per step, second 64 dims via LBO
+                            // V MN-major: 16 keys = two row groups further per step, second 64 dims via LBO
 #pragma unroll
                             for (int ks = 0; ks < 8; ks++) {
                                 if (ks < nks) {
                                     const uint32_t a = tmem + b * kT + part * 64 + ks * 8;
-                                    umma_ts_words(d, a, v_lo + ks * (2048 >> 4), kDescHiSw128, idesc_pv, 1u);
+                                    umma_ts_words(d, a, v_lo + ks * (2 * group_bytes >> 4), v_hi, idesc_pv, 1u);
                                 }
                             }
                             tc_commit(&sh->s_free[b]);
@@ -731,8 +747,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         const int row_units = 8 * p.d_chunks;  // 16-byte units per V row
                         for (int i = row; i < (kT - first_bad) * row_units; i += 128) {
                             const int vr = first_bad + i / row_units, u = i % row_units;
-                            *reinterpret_cast<uint4*>(vt + (u >> 3) * kChunkBytes + vr * 128 + (((u & 7) ^ (vr & 7)) << 4)) =
-                                make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4*>(vt + (vr >> 3) * group_bytes + (u >> 3) * chunk_off + (vr & 7) * 128 +
+                                                      (((u & 7) ^ (vr & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                         }
                         fence_proxy_async_smem();
                     }
@@ -980,8 +996,8 @@ int launch_paged_prefill(granite_cuda_compute* c, const GraniteCudaPagedPrefillA
     const CUtensorMap* qmap = c->tensor_map_2d(q16, (uint64_t)a.num_heads * D, a.seq_q, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
     const CUtensorMap* qlomap = c->tensor_map_2d(q16_lo, (uint64_t)a.num_heads * D, a.seq_q, (uint64_t)a.num_heads * D * 2, 64, kT, 128);
     const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * D;
-    const CUtensorMap* kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
-    const CUtensorMap* vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
+    const CUtensorMap* kmap = c->tensor_map_page_groups(a.k_cache, width, rows, D);
+    const CUtensorMap* vmap = c->tensor_map_page_groups(a.v_cache, width, rows, D);
     if (!qmap || !qlomap || !kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
     TcKernel kern = split_q ? fa_tc_kernel<false, true, true, 1> : fa_tc_kernel<false, true, false, 1>;
@@ -1061,14 +1077,16 @@ int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionAr
     const CUtensorMap* qmap = c->tensor_map_3d(q16, D, a.num_nodes, qz, D * 2, node_pitch, 64, slots, heads_per_tile, 128);
     const CUtensorMap* qlomap = c->tensor_map_3d(q16_lo, D, a.num_nodes, qz, D * 2, node_pitch, 64, slots, heads_per_tile, 128);
     const uint64_t tz = (uint64_t)a.batch_size * a.num_kv_heads;
-    const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, kNodeSlots, 1, 128);
-    const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, kNodeSlots, 1, 128);
+    // with a paged prefix the tiles are laid out in 8-row groups (see the kernel), so the tree tile comes in 8-row boxes
+    const uint32_t tree_box_rows = paged ? 8 : kNodeSlots;
+    const CUtensorMap* ktmap = c->tensor_map_3d(a.k_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, tree_box_rows, 1, 128);
+    const CUtensorMap* vtmap = c->tensor_map_3d(a.v_tree, D, a.num_nodes, tz, D * 2, node_pitch, 64, tree_box_rows, 1, 128);
     const CUtensorMap *kmap = ktmap, *vmap = vtmap;  // placeholders when there is no prefix
     if (has_cache) {
         if (paged) {
             const uint64_t rows = (uint64_t)a.num_blocks * kPageRows, width = (uint64_t)a.num_kv_heads * D;
-            kmap = c->tensor_map_2d(a.k_cache, width, rows, width * 2, 64, kPageRows, 128);
-            vmap = c->tensor_map_2d(a.v_cache, width, rows, width * 2, 64, kPageRows, 128);
+            kmap = c->tensor_map_page_groups(a.k_cache, width, rows, D);
+            vmap = c->tensor_map_page_groups(a.v_cache, width, rows, D);
         } else {
             const uint64_t rows = (uint64_t)a.batch_size * a.num_kv_heads * cache_stride;
             kmap = c->tensor_map_2d(a.k_cache, D, rows, D * 2, 64, kT, 128);
