@@ -2,13 +2,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-One step = one batched paged decode call (plan + split-KV kernel + merge) over one batch of
+One step = one batched paged decode call (plan kernel + split-KV kernel, which also merges cut sequences) over one batch of
 synthetic sequences whose K/V pages already live in HBM.  Workload at N = 1: 64 sequences, context
 lengths uniform in [1024, 32768], page 16, shuffled block table, Hq 32 / Hkv 8 / D 128, fp16 K/V,
 fp32 Q and output.  At N > 1 every rank owns its own batch of that shape (sequences are
 independent: sharded by sequence, no collective inside attention); every step the per-rank outputs
-are gathered on every rank by peer stores over NVLink (granite_cuda_push_rows into symmetric
-memory, beside the next step's kernel; NCCL all-gather as the fall-back).  Prints ONE JSON line (rank 0).
+are gathered on every rank by the decode kernel itself, which stores each final row into every rank's buffer
+(peer stores over NVLink into symmetric memory; NCCL all-gather as the fall-back).  Prints ONE JSON line (rank 0).
 
 --impl reference times Granite's CPU attention arithmetic (oracle/, a restatement of
 src/llm/transformer.mm:1779-1840 over pages fetched by the rule of metal_compute.h:853-861, with
@@ -538,19 +538,19 @@ def main():
     if strong and world > 1:
         rows = sharding.padded_rows(plan)  # ranks own different numbers of sequences
         outs = [torch.zeros((rows, Hq, D), device=dev) for _ in range(2)]
-    # Output gather across the ranks: every rank pushes its rows into every rank's gathered buffer with
-    # peer stores over NVLink (symmetric memory), on a side stream so that the push of step i runs
-    # beside the decode kernel of step i + 1.  NCCL's all-gather is the fall-back where symmetric
-    # memory cannot be set up.
+    # Output gather across the ranks: the decode kernel itself stores every final row into every rank's
+    # gathered buffer (peer-mapped symmetric memory, plain stores over NVLink) - no extra launch.  NCCL's
+    # all-gather is the fall-back where symmetric memory cannot be set up, and the verifier.
     gathered, peer_ptrs, gather_mode = None, None, "none"
-    side = torch.cuda.Stream(device=dev) if world > 1 else None
     if world > 1:
         try:
             import torch.distributed._symmetric_memory as symm
             gathered = [symm.empty((world * rows, Hq, D), dtype=torch.float32, device=dev) for _ in range(2)]
+            for t in gathered:
+                t.zero_()  # padding rows (ranks own different numbers of sequences) compare equal
             handles = [symm.rendezvous(t, dist.group.WORLD) for t in gathered]
             peer_ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
-            gather_mode = "peer stores over NVLink (symmetric memory), overlapped with the next step"
+            gather_mode = "rows stored to every rank by the decode kernel (peer stores over NVLink, symmetric memory)"
         except Exception as exc:  # noqa: BLE001 - any failure means: use the collective library
             print(f"[bench] symmetric memory unavailable ({exc!r}); gathering with NCCL", file=sys.stderr)
             gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
@@ -561,31 +561,23 @@ def main():
         if int(flags.item()) == 0 and peer_ptrs is not None:
             gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
             peer_ptrs, gather_mode = None, "NCCL all-gather per step"
-    push_done = [None, None]
-    row_bytes = rows * Hq * D * 4
 
-    def decode(q, tables, lens, out):
+    def decode(q, tables, lens, out, gather_ptrs=None):
         compute.batched_paged_attention_decode(q, case.k_pool, case.v_pool, tables, lens, out, B, Hq, Hkv,
                                                D, synth.PAGE, case.max_blocks, scale,
-                                               num_blocks=case.num_blocks)
+                                               num_blocks=case.num_blocks, gather_ptrs=gather_ptrs,
+                                               gather_row_offset=rank * rows)
 
     def step(i):
         out = outs[i & 1]
-        if push_done[i & 1] is not None:
-            stream.wait_event(push_done[i & 1])  # the push of step i - 2 has read this buffer
-        decode(q_d, tables_d, lens_d, out)
         if world > 1 and peer_ptrs is not None:
-            ready = torch.cuda.Event()
-            ready.record(stream)
-            side.wait_event(ready)
-            compute.push_rows(out, peer_ptrs[i & 1], rank * row_bytes, row_bytes, stream=side.cuda_stream)
-            done = torch.cuda.Event()
-            done.record(side)
-            push_done[i & 1] = done
-        elif world > 1:
-            # the gather is ordered after this step's kernels and before the next step's: a
-            # persistent one-CTA-per-SM decode kernel must not share SMs with an NCCL kernel
-            dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True).wait()
+            decode(q_d, tables_d, lens_d, out, peer_ptrs[i & 1])
+        else:
+            decode(q_d, tables_d, lens_d, out)
+            if world > 1:
+                # the gather is ordered after this step's kernels and before the next step's: a
+                # persistent one-CTA-per-SM decode kernel must not share SMs with an NCCL kernel
+                dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True).wait()
 
     def barrier():
         if world > 1:
@@ -605,9 +597,6 @@ def main():
     e0.record(stream)
     for i in range(args.steps):
         step(i)
-    for ev in push_done:
-        if ev is not None:
-            stream.wait_event(ev)  # the last pushes end inside the timed region
     e1.record(stream)
     barrier()
     clocks = sampler.stop()
@@ -739,8 +728,8 @@ def main():
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "note": "host Q, block tables and lengths copied in (one pinned staging block), output copied out, sync per step; "
                             "K/V pages are cache state resident in HBM"},
-            # per rank and step: decode_plan + paged_decode_splitkv (+ push_rows when the rows are gathered by peer stores)
-            "gpu_launches": (3 if peer_ptrs is not None else 2) * args.steps,
+            # per rank and step: decode_plan + paged_decode_splitkv (which also stores the rows to the other ranks)
+            "gpu_launches": 2 * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "secondary": secondary,
         }

@@ -118,8 +118,14 @@ struct LaunchScope {
         if (end) cudaEventRecord(end, c->stream);
     }
 };
-int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
-                        bool contiguous, uint32_t max_seq);
+// Optional gather of the decode output: every final row also goes to dst[r] (row row_offset + sequence).
+struct DecodeGather {
+    void* const* dst;
+    uint32_t n_dst;
+    uint64_t row_offset;
+};
+int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a, bool contiguous,
+                        uint32_t max_seq, const DecodeGather* gather = nullptr);
 int launch_prefill(granite_cuda_compute* c, const GraniteCudaAttentionArgs& a);
 int launch_tree_verify(granite_cuda_compute* c, const GraniteCudaTreeAttentionArgs& a);
 int launch_kv_cache_append(granite_cuda_compute* c, const GraniteCudaKvAppendArgs& a);

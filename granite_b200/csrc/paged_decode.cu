@@ -32,6 +32,7 @@ constexpr int kPageTokens = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxSlots = 32;
+constexpr int kMaxGatherDst = 16;
 
 struct DecodeParams {
     const float* q;
@@ -58,7 +59,26 @@ struct DecodeParams {
     float2* part_ml;      // [2 * n_ctas][num_heads]
     int* pages_done;      // [batch][n_head_tiles][consumer warps]: pages of cut sequences finished so far
     int fused_merge;      // 1: the warp that finishes a cut sequence merges it; 0: decode_merge_kernel follows
+    // optional gather: every final output row is also stored into these buffers (other GPUs' peer-mapped
+    // memory or this GPU's own), at row gather_row0 + sequence
+    float* gather[kMaxGatherDst];
+    int n_gather;
+    long long gather_row0;
 };
+
+// Final output element(s) of (sequence b, query head hq): the local row and every gather destination.
+// Plain stores: nothing waits for the peers; visibility to a consumer on another GPU is the caller's
+// ordering (end of the kernel plus whatever it uses between ranks).
+__device__ __forceinline__ void store_out(const DecodeParams& p, int b, int hq, int idx, float v) {
+    p.out[((size_t)b * p.num_heads + hq) * p.d + idx] = v;
+    for (int r = 0; r < p.n_gather; r++)
+        p.gather[r][((size_t)(p.gather_row0 + b) * p.num_heads + hq) * p.d + idx] = v;
+}
+__device__ __forceinline__ void store_out4(const DecodeParams& p, int b, int hq, int idx, float4 v) {
+    *reinterpret_cast<float4*>(p.out + ((size_t)b * p.num_heads + hq) * p.d + idx) = v;
+    for (int r = 0; r < p.n_gather; r++)
+        *reinterpret_cast<float4*>(p.gather[r] + ((size_t)(p.gather_row0 + b) * p.num_heads + hq) * p.d + idx) = v;
+}
 
 __device__ __forceinline__ long long range_start(long long total, int n_ctas, int c) {
     return (total * c) / n_ctas;
@@ -120,8 +140,8 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(DecodeParams p) {
     // rows of empty sequences are defined to be zero (rare: one thread per such row)
     for (int b = tid; b < p.batch; b += 1024) {
         if (p.page_prefix[b + 1] == p.page_prefix[b]) {
-            float* o = p.out + (size_t)b * p.num_heads * p.d;
-            for (int i = 0; i < p.num_heads * p.d; i++) o[i] = 0.f;
+            for (int h = 0; h < p.num_heads; h++)
+                for (int i = 0; i < p.d; i++) store_out(p, b, h, i, 0.f);
         }
     }
     const long long T = (long long)total * p.n_head_tiles;
@@ -271,8 +291,7 @@ __device__ __forceinline__ void merge_cut_sequence(const DecodeParams& p, int b,
         }
         if (lane * 4 < D) {
             const float inv = 1.0f / L;
-            *(reinterpret_cast<float4*>(p.out + ((size_t)b * p.num_heads + hq) * D) + lane) =
-                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            store_out4(p, b, hq, lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
         }
     }
 }
@@ -611,11 +630,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 const int hq = hq0 + n;
                 if (seg.slot < 0) {
                     const float inv = 1.0f / l_run[nt][jx];
-                    float* dst = p.out + ((size_t)seg.seq * p.num_heads + hq) * D;
 #pragma unroll
                     for (int mt = 0; mt < kDSteps; mt++) {
-                        dst[mt * 16 + g] = o[nt][mt][jx] * inv;
-                        dst[mt * 16 + g + 8] = o[nt][mt][2 + jx] * inv;
+                        store_out(p, seg.seq, hq, mt * 16 + g, o[nt][mt][jx] * inv);
+                        store_out(p, seg.seq, hq, mt * 16 + g + 8, o[nt][mt][2 + jx] * inv);
                     }
                 } else {
                     float* dst = p.part_o + ((size_t)seg.slot * p.num_heads + hq) * D;
@@ -747,7 +765,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(DecodeParam
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < kMergeThreads / 32; w++) sum += reinterpret_cast<const float*>(&s_acc[w][0])[tid];
-        p.out[((size_t)b * p.num_heads + hq) * p.d + tid] = sum / L;
+        store_out(p, b, hq, tid, sum / L);
     }
 }
 
@@ -762,26 +780,48 @@ static int fused_merge_pays(int batch, int n_head_tiles, int n_ctas) {
 }
 
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
-                        bool contiguous, uint32_t max_seq) {
+                        bool contiguous, uint32_t max_seq, const DecodeGather* gather) {
+    if (gather && gather->n_dst > 0) {
+        if (!gather->dst) return fail(GRANITE_CUDA_NULL_POINTER, "decode gather: null destination list");
+        if (gather->n_dst > (uint32_t)kMaxGatherDst)
+            return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode gather: at most 16 destinations");
+        for (uint32_t r = 0; r < gather->n_dst; r++) {
+            if (!gather->dst[r]) return fail(GRANITE_CUDA_NULL_POINTER, "decode gather: null destination");
+            if (reinterpret_cast<uintptr_t>(gather->dst[r]) & 15)
+                return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode gather: destinations must be 16-byte aligned");
+        }
+    } else {
+        gather = nullptr;
+    }
     if (!a.q || !a.k_cache || !a.v_cache || !a.output || (!contiguous && !a.block_tables))
         return fail(GRANITE_CUDA_NULL_POINTER, "paged decode: null buffer");
     if (a.batch_size == 0) return GRANITE_CUDA_SUCCESS;
     if (a.num_kv_heads == 0 || a.num_heads == 0 || a.num_heads % a.num_kv_heads != 0)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_heads must be a multiple of num_kv_heads");
+    // the plain kernel does not store to gather destinations itself: its rows are pushed afterwards
+    auto plain = [&]() {
+        int rc = launch_generic_decode(c, a, contiguous, max_seq);
+        if (rc == GRANITE_CUDA_SUCCESS && gather) {
+            const uint64_t row_bytes = (uint64_t)a.num_heads * a.head_dim * 4;
+            rc = launch_push_rows(c, nullptr, a.output, gather->dst, gather->n_dst, gather->row_offset * row_bytes,
+                                  a.batch_size * row_bytes);
+        }
+        return rc;
+    };
     // shapes outside this kernel's tiling (head_dim 128, 16-token pages, 1, 2, 4 or 8k KV heads, at
     // most 16 query heads per consumer warp) run on the plain kernel
     if ((a.head_dim != 128 && a.head_dim != 64) || (!contiguous && a.block_size != kPageTokens))
-        return launch_generic_decode(c, a, contiguous, max_seq);
+        return plain();
     const int D = (int)a.head_dim;
     const int hkv = (int)a.num_kv_heads;
     int tile_heads;
     if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
     else if (hkv % 8 == 0) tile_heads = 8;
-    else return launch_generic_decode(c, a, contiguous, max_seq);
+    else return plain();
     const int group = (int)(a.num_heads / a.num_kv_heads);
     const int warps_per_head = kConsumerWarps / tile_heads;
     const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
-    if (heads_per_warp > 16) return launch_generic_decode(c, a, contiguous, max_seq);
+    if (heads_per_warp > 16) return plain();
     const int nt = heads_per_warp <= 8 ? 1 : 2;
     const int subs_active = (group + heads_per_warp - 1) / heads_per_warp;
     if (contiguous) {
@@ -813,6 +853,11 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.status = c->d_status;
     p.d = D;
     p.fused_merge = fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
+    if (gather) {
+        p.n_gather = (int)gather->n_dst;
+        p.gather_row0 = (long long)gather->row_offset;
+        for (uint32_t r = 0; r < gather->n_dst; r++) p.gather[r] = static_cast<float*>(gather->dst[r]);
+    }
 
     const int slot_bytes = tile_heads * kPageTokens * D * 2;
     const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;

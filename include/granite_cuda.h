@@ -107,9 +107,11 @@ int granite_cuda_memset(granite_cuda_compute_t* c, void* dev_dst, int byte, size
  * MetalCompute::paged_attention_decode (metal_compute.h:869-881, metal_compute.mm:2535-2621).
  * Addressing rule (metal_compute.h:853-861): token pos of a sequence lives at pool row
  * block_table[pos / block_size] * block_size + pos % block_size.
- * Supported: head_dim 128, block_size 16, num_heads % num_kv_heads == 0, num_kv_heads in
- * {1,2,4} or a multiple of 8; anything else returns InvalidArgument as the reference does for an
- * unsupported head_dim (metal_compute.mm:2556-2559).  A sequence of length 0 gets a zero row. */
+ * Tuned kernel: head_dim 128 or 64, block_size 16, num_kv_heads in {1,2,4} or a multiple of 8; other
+ * head dims (multiples of 8 up to 256), page sizes and KV-head counts run on a plain fp32 kernel;
+ * num_heads % num_kv_heads != 0 or a head_dim outside that range returns InvalidArgument as the
+ * reference does for an unsupported head_dim (metal_compute.mm:2556-2559).  A sequence of length 0
+ * gets a zero row. */
 typedef struct {
     const float* q;              /* [batch, num_heads, head_dim] fp32, device */
     const void* k_cache;         /* [num_blocks*block_size, num_kv_heads, head_dim] fp16, device */
@@ -130,6 +132,19 @@ typedef struct {
 
 int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c,
                                                 const GraniteCudaPagedDecodeArgs* args);
+
+/* The same decode with the gather that follows it on several GPUs fused in: when sequences are
+ * sharded across GPUs, every rank needs all output rows.  Each final row (sequence b, all heads) is
+ * stored by the attention kernel itself to args->output and to dst_ptrs[r] + (dst_row_offset + b) rows,
+ * r < n_dst (<= 16) - buffers [total sequences, num_heads, head_dim] fp32 that may live on other GPUs
+ * (peer-mapped, e.g. symmetric memory) or on this one.  Plain stores over NVLink from the kernel that
+ * produced the row: no extra launch, no multicast, no waiting on another GPU.  Ordering towards a
+ * reader on another GPU is the caller's (stream completion plus its own signal between ranks).
+ * No reference counterpart (the reference runs on one GPU). */
+int granite_cuda_batched_paged_attention_decode_gather(granite_cuda_compute_t* c,
+                                                       const GraniteCudaPagedDecodeArgs* args,
+                                                       void* const* dst_ptrs, uint32_t n_dst,
+                                                       uint64_t dst_row_offset);
 
 /* Allocation-free batched paged decode.  This entry point has no counterpart in the reference.
  * It exists for hosts that cannot let a plug-in allocate device memory: a serving process whose

@@ -94,6 +94,38 @@ def test_cut_sequences_merged_inside_the_decode_kernel(compute, hq, hkv, d):
         assert np.array_equal(got, again), name
 
 
+@pytest.mark.parametrize("name,lens,d", [("in-kernel merge", [0] + [3000, 40, 1] * 15 + [20000, 0], 128),
+                                         ("merge pass", [700, 0, 33, 5000, 16], 128),
+                                         ("head_dim 64", list(range(1, 1200, 29)), 64),
+                                         ("plain kernel", [100, 0, 900], 96)])
+def test_decode_with_fused_gather(compute, name, lens, d):
+    """The decode that also stores every final row into gather buffers (here two buffers on the same
+    GPU standing in for peers): rows row_offset .. row_offset + batch hold exactly the output, every
+    other row is untouched.  Covers rows written by the decode kernel itself, by the warp that merges a
+    cut sequence, by the separate merge pass, the zero rows of empty sequences and the plain kernel."""
+    import torch
+    dev = "cuda:0"
+    case = synth.paged_case(seed=31, batch=len(lens), len_lo=0, len_hi=0, head_dim=d, seq_lens=np.array(lens, np.int32))
+    q = torch.from_numpy(case.q).to(dev)
+    k = torch.from_numpy(case.k_pool).to(dev)
+    v = torch.from_numpy(case.v_pool).to(dev)
+    tables = torch.from_numpy(case.tables).to(dev)
+    seq_lens = torch.from_numpy(case.seq_lens).to(dev)
+    out = torch.full((case.batch, case.num_heads, d), float("nan"), device=dev)
+    total, offset = case.batch + 11, 7
+    gathered = [torch.full((total, case.num_heads, d), float("nan"), device=dev) for _ in range(2)]
+    compute.batched_paged_attention_decode(q, k, v, tables, seq_lens, out, case.batch, case.num_heads, case.num_kv_heads,
+                                           d, synth.PAGE, case.max_blocks, 1.0 / np.sqrt(d), num_blocks=case.num_blocks,
+                                           gather_ptrs=[g.data_ptr() for g in gathered], gather_row_offset=offset)
+    compute.sync()
+    got = out.cpu().numpy()
+    ref = _oracle(case, case.k_pool.view(np.uint16), case.v_pool.view(np.uint16))
+    assert_attention_close(got, ref, name)
+    for g in gathered:
+        assert torch.equal(g[offset:offset + case.batch], out), name
+        assert torch.isnan(g[:offset]).all() and torch.isnan(g[offset + case.batch:]).all(), name
+
+
 def test_single_sequence_paged_decode(compute):
     import torch
     case = synth.paged_case(seed=13, batch=1, len_lo=0, len_hi=0, seq_lens=np.array([777], np.int32))
