@@ -120,6 +120,12 @@ Result<void> CudaCompute::batched_paged_attention_decode(const float* Q, const v
     return cuda_result(granite_cuda_batched_paged_attention_decode(h_, &a));
 }
 
+Result<void> CudaCompute::batched_paged_attention_decode_gather(const GraniteCudaPagedDecodeArgs& args,
+                                                                void* const* gather_dst, uint32_t n_dst,
+                                                                uint64_t gather_row_offset) {
+    return cuda_result(granite_cuda_batched_paged_attention_decode_gather(h_, &args, gather_dst, n_dst, gather_row_offset));
+}
+
 Result<void> CudaCompute::rope_multihead(float* q, float* k, uint32_t num_heads_q, uint32_t num_heads_k,
                                          uint32_t seq_len, uint32_t head_dim, uint32_t start_pos,
                                          const float* cos_table, const float* sin_table, uint32_t table_len) {

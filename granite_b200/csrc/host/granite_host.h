@@ -271,6 +271,11 @@ public:
                                                 float* output, uint32_t batch_size, uint32_t num_heads,
                                                 uint32_t num_kv_heads, uint32_t head_dim, uint32_t block_size,
                                                 uint32_t max_blocks_per_seq, float scale, uint32_t num_blocks);
+    // Several GPUs, sequences sharded: the same decode, whose kernels also store every final row into the
+    // ranks' gathered buffers (gather_dst[r], n_dst <= 16, row gather_row_offset + sequence).  No counterpart
+    // upstream (one GPU).
+    Result<void> batched_paged_attention_decode_gather(const GraniteCudaPagedDecodeArgs& args, void* const* gather_dst,
+                                                       uint32_t n_dst, uint64_t gather_row_offset);
     // The step before attention and the ones after verification (the "next" tier of the path):
     // RoPE with host-built tables, RoPE fused with the paged cache write, the tree commit copy and
     // chunked prefill over the paged cache.  Argument meaning as in granite_cuda.h.
