@@ -631,9 +631,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 if (seg.slot < 0) {
                     const float inv = 1.0f / l_run[nt][jx];
 #pragma unroll
+                    float* dst = p.out + ((size_t)seg.seq * p.num_heads + hq) * D;
+#pragma unroll
                     for (int mt = 0; mt < kDSteps; mt++) {
-                        store_out(p, seg.seq, hq, mt * 16 + g, o[nt][mt][jx] * inv);
-                        store_out(p, seg.seq, hq, mt * 16 + g + 8, o[nt][mt][2 + jx] * inv);
+                        dst[mt * 16 + g] = o[nt][mt][jx] * inv;
+                        dst[mt * 16 + g + 8] = o[nt][mt][2 + jx] * inv;
                     }
                 } else {
                     float* dst = p.part_o + ((size_t)seg.slot * p.num_heads + hq) * D;
@@ -645,6 +647,19 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     if (g == 0)
                         p.part_ml[(size_t)seg.slot * p.num_heads + hq] = make_float2(m_run[nt][jx], l_run[nt][jx]);
                 }
+            }
+        }
+        if (seg.slot < 0 && p.n_gather > 0) {
+            // gather destinations get whole rows as 16-byte stores (a lane's own fragment holds every
+            // eighth pair of a row, which would cross NVLink as 32-byte pieces): the warp reads back
+            // the rows it has just written
+            __syncwarp();
+            for (int h = 0; h < n_q; h++) {
+                if (lane * 4 >= D) continue;
+                const size_t row = ((size_t)seg.seq * p.num_heads + hq0 + h) * D + lane * 4;
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(p.out + row));
+                for (int r = 0; r < p.n_gather; r++)
+                    *reinterpret_cast<float4*>(p.gather[r] + (size_t)p.gather_row0 * p.num_heads * D + row) = v;
             }
         }
         if (seg.slot >= 0 && p.fused_merge) {
