@@ -57,8 +57,12 @@ int granite_cuda_compute::ensure_scratch(size_t bytes) {
 }
 
 const CUtensorMap* granite_cuda_compute::encode_map(const TensorMapKey& key) {
+    const uint64_t tick = ++tensor_map_tick;
     auto it = tensor_maps.find(key);
-    if (it != tensor_maps.end()) return &it->second;
+    if (it != tensor_maps.end()) {
+        it->second.last_use = tick;
+        return &it->second.map;
+    }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -85,9 +89,15 @@ const CUtensorMap* granite_cuda_compute::encode_map(const TensorMapKey& key) {
         set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
         return nullptr;
     }
-    if (tensor_maps.size() > 256) tensor_maps.clear();  // callers re-create what they need
-    auto ins = tensor_maps.emplace(key, map);
-    return &ins.first->second;
+    // Bounded cache.  A launcher holds the pointers of up to six maps while it fetches the next
+    // one, so eviction never touches the kKeepRecent most recently used entries; erasing other
+    // nodes of a std::map leaves pointers to the remaining ones valid.
+    if (tensor_maps.size() >= kMaxTensorMaps) {
+        for (auto e = tensor_maps.begin(); e != tensor_maps.end();)
+            e = (e->second.last_use + kKeepRecent < tick) ? tensor_maps.erase(e) : std::next(e);
+    }
+    auto ins = tensor_maps.emplace(key, CachedTensorMap{map, tick});
+    return &ins.first->second.map;
 }
 
 const CUtensorMap* granite_cuda_compute::tensor_map_2d(const void* base, uint64_t dim0, uint64_t dim1,

@@ -67,7 +67,14 @@ struct granite_cuda_compute {
     // scratch arena (grown on demand, never shrunk)
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
-    std::map<gb200::TensorMapKey, CUtensorMap> tensor_maps;
+    // Cached TMA descriptors, keyed by (buffer, shape).  Bounded: once kMaxTensorMaps entries exist,
+    // everything but the kKeepRecent most recently used ones is dropped (encode_map), so a pointer
+    // returned by encode_map stays valid for at least the next kKeepRecent - 1 calls to it.
+    struct CachedTensorMap { CUtensorMap map; uint64_t last_use; };
+    static constexpr size_t kMaxTensorMaps = 256;
+    static constexpr uint64_t kKeepRecent = 32;
+    std::map<gb200::TensorMapKey, CachedTensorMap> tensor_maps;
+    uint64_t tensor_map_tick = 0;
 
     // per-kernel GPU timing (MetalCompute::enable_kernel_timing, metal_compute.h:54-60)
     struct TimedLaunch { const char* name; cudaEvent_t begin, end; };

@@ -892,7 +892,7 @@ int PagedDecodeBatch::add_request(int slot) {
     if (batch_size() >= max_batch_ || slot < 0 || slot >= pool_->num_slots()) return -1;
     if (std::find(slots_.begin(), slots_.end(), slot) != slots_.end()) return -1;
     slots_.push_back(slot);
-    synced_blocks_.push_back(0);  // the whole row goes up at the next step
+    sent_rows_.emplace_back();  // the whole row goes up at the next step
     return batch_size() - 1;
 }
 
@@ -902,9 +902,9 @@ void PagedDecodeBatch::remove_request(int slot) {
     const size_t row = static_cast<size_t>(it - slots_.begin());
     // keep the rows dense: the last row moves into the hole and is re-sent whole
     slots_[row] = slots_.back();
-    synced_blocks_[row] = 0;
+    sent_rows_[row].clear();
     slots_.pop_back();
-    synced_blocks_.pop_back();
+    sent_rows_.pop_back();
 }
 
 Result<std::vector<int>> PagedDecodeBatch::begin_step() {
@@ -935,13 +935,19 @@ Result<std::vector<int>> PagedDecodeBatch::begin_step() {
         positions[row] = cache.seq_len() - 1;
         const int have = cache.num_blocks();
         if (have > max_blocks_) return Error(ErrorCode::BufferTooSmall, "PagedDecodeBatch: block table wider than max_blocks_per_seq");
-        if (have > synced_blocks_[row]) {  // only the entries the device has not seen
+        // only the entries the device row does not hold already: everything from the first one that
+        // differs from what was sent (a shrunken table drops the tail of the mirror first)
+        auto& sent = sent_rows_[row];
+        const auto& table = cache.block_table();
+        if (static_cast<int>(sent.size()) > have) sent.resize(static_cast<size_t>(have));
+        int first = 0;
+        while (first < static_cast<int>(sent.size()) && sent[static_cast<size_t>(first)] == table[static_cast<size_t>(first)]) first++;
+        if (first < have) {
             int32_t* stage = rows + static_cast<size_t>(row) * max_blocks_;
-            const int first = synced_blocks_[row];
-            std::copy(cache.block_table().begin() + first, cache.block_table().end(), stage + first);
+            std::copy(table.begin() + first, table.begin() + have, stage + first);
             rc = granite_cuda_write_buffer(compute_->handle(), d_tables_ + static_cast<size_t>(row) * max_blocks_ + first,
                                            stage + first, static_cast<size_t>(have - first) * 4);
-            synced_blocks_[row] = have;
+            sent.assign(table.begin(), table.begin() + have);
         }
     }
     if (!rc) rc = granite_cuda_write_buffer(compute_->handle(), d_positions_, positions, static_cast<size_t>(n) * 4);

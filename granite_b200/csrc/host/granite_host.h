@@ -478,7 +478,10 @@ private:
     ModelConfig config_;
     int max_batch_ = 0, max_blocks_ = 0;
     std::vector<int> slots_;            // row -> slot
-    std::vector<int> synced_blocks_;    // row -> table entries already on the device
+    // row -> the table entries the device row holds.  A step re-sends from the first entry that
+    // differs from the sequence's current table, so a table that shrank (truncate after a tree
+    // commit, or a slot released and taken again) and regrew over other blocks is never left stale.
+    std::vector<std::vector<int32_t>> sent_rows_;
     int32_t *d_tables_ = nullptr, *d_lens_ = nullptr, *d_positions_ = nullptr;
     int32_t* h_staging_ = nullptr;      // pinned: [max_batch] positions, [max_batch] lengths, [max_batch, max_blocks] rows
 };

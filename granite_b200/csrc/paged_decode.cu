@@ -914,7 +914,9 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
 
     auto kern = D == 128 ? (nt == 1 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>)
                          : (nt == 1 ? paged_decode_kernel<1, 64> : paged_decode_kernel<2, 64>);
-    GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    // always the device's opt-in maximum: the limit belongs to the kernel, not to this call, and the
+    // allocation-free entry point launches the same kernels with its own (possibly larger) window
+    GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin));
     {
         LaunchScope t(c, "decode_plan");
         decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
@@ -972,7 +974,7 @@ static StaticDeviceSetup g_static_setup[kMaxDevices];
 static std::mutex g_static_setup_mutex;
 
 // Once per device, with that device current: resolves the device address of the scratch array
-// and raises the kernels' dynamic shared-memory limit.  Allocates nothing.
+// and reads the device's limits.  Allocates nothing.
 static int static_decode_setup(int device, StaticDeviceSetup** out) {
     if (device < 0 || device >= kMaxDevices)
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: device index out of range");
@@ -991,8 +993,6 @@ static int static_decode_setup(int device, StaticDeviceSetup** out) {
         if (major != 10) return fail(GRANITE_CUDA_BACKEND_NOT_SUPPORTED, "static decode: built for sm_100a only");
         GB_CUDA_TRY(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, device));
         GB_CUDA_TRY(cudaDeviceGetAttribute(&s.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<1, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
-        GB_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, s.smem_optin));
         s.scratch = static_cast<unsigned char*>(ptr);
         s.ready = true;
     }
@@ -1121,11 +1121,12 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     if ((rc = encode_pool_map(&kmap, a.k_cache, hkv, rows, tile_heads)) != 0) return rc;
     if ((rc = encode_pool_map(&vmap, a.v_cache, hkv, rows, tile_heads)) != 0) return rc;
 
+    // The dynamic shared-memory limit is set on every call (it allocates nothing): another entry
+    // point, or another library object sharing these kernels, may have set a different one since.
+    auto kern = heads_per_warp <= 8 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>;
+    GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, setup->smem_optin));
     decode_plan_kernel<<<1, 1024, 0, st>>>(p);
-    if (heads_per_warp <= 8)
-        paged_decode_kernel<1, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
-    else
-        paged_decode_kernel<2, 128><<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
+    kern<<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);
     if (!p.fused_merge) decode_merge_kernel<<<dim3(p.batch, p.num_heads), kMergeThreads, 0, st>>>(p);
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;

@@ -149,18 +149,22 @@ int granite_cuda_batched_paged_attention_decode_gather(granite_cuda_compute_t* c
 /* Allocation-free batched paged decode.  This entry point has no counterpart in the reference.
  * It exists for hosts that cannot let a plug-in allocate device memory: a serving process whose
  * own arena already owns the GPU's memory, or a latency-critical loop that cannot afford the
- * device-wide synchronisation hidden in cudaMalloc/cudaFree.  Same arguments, layouts, limits and
- * results as granite_cuda_batched_paged_attention_decode, but it needs no compute object and
+ * device-wide synchronisation hidden in cudaMalloc/cudaFree.  Same arguments, layouts and results
+ * as granite_cuda_batched_paged_attention_decode, but it needs no compute object and
  * calls no cudaMalloc, cudaFree or other allocating routine: its scratch (prefix sums and the
  * partials of sequences split across SMs) is a fixed ~13.8 MB array that every GPU which loads
  * this library holds until the process exits.
+ *   - Shapes: narrower than the regular entry point, which falls back to other kernels.  Here
+ *     head_dim must be 128, block_size 16, num_kv_heads 1, 2, 4 or a multiple of 8, and at most
+ *     16 query heads may share one consumer warp (num_heads / num_kv_heads <= 16 when there are
+ *     eight or more KV heads); anything else returns GRANITE_CUDA_INVALID_ARGUMENT.
  *   - Limits: batch_size <= 4096, num_heads <= 64, at most 192 SMs; beyond them the call returns
  *     GRANITE_CUDA_BUFFER_TOO_SMALL and launches nothing.
  *   - Runs on the CURRENT device, on `stream` (a cudaStream_t; NULL is the default stream),
  *     asynchronously.
  *   - The first call on each device also does a one-time set-up (it resolves the array's device
- *     address and raises the kernels' shared-memory limit), so make that first call before any
- *     stream capture begins.
+ *     address and reads the device's limits), so make that first call before any stream capture
+ *     begins.
  *   - All calls share the one array and it keeps the previous call's contents; the call clears
  *     the only part that must start at zero.  Two calls that overlap on the same GPU (different
  *     streams, or different threads) race on it: serialise them.

@@ -17,9 +17,21 @@ _LIB = _DIR / "liboracle.so"
 _REF = _DIR / "_ref" / "libgranite_ref.so"
 
 
+def reference_checkout() -> Path | None:
+    """The Granite checkout the reference half is built from: $GRANITE_REF_DIR, else a directory
+    named `reference` beside this repository; None when neither holds Granite's sources."""
+    cand = os.environ.get("GRANITE_REF_DIR")
+    path = Path(cand) if cand else _DIR.parent.parent / "reference"
+    return path if (path / "src" / "llm" / "transformer.mm").exists() else None
+
+
 def build(quiet: bool = True) -> None:
     """Compiles liboracle.so (and _ref/ when the reference checkout is present)."""
-    res = subprocess.run(["make", "-C", str(_DIR)], capture_output=True, text=True)
+    cmd = ["make", "-C", str(_DIR)]
+    ref = reference_checkout()
+    if ref is not None:
+        cmd.append(f"GRANITE_REF_DIR={ref}")
+    res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + res.stdout + res.stderr)
     if not quiet:
@@ -250,7 +262,60 @@ class Ref:
         r.ref_rope_table.argtypes = [C.c_int, C.c_int, C.c_float, _f32p, _f32p]
         r.ref_rope_apply.restype = C.c_int
         r.ref_rope_apply.argtypes = [_f32p, _f32p] + [C.c_int] * 6 + [C.c_float]
+        # the reference's own attention statements (ref_loops.cpp)
+        r.ref_attention_loop.restype = None
+        r.ref_attention_loop.argtypes = [_f32p, _f32p, _f32p, _f32p] + [C.c_int] * 7 + [C.c_float]
+        r.ref_attention_cache_widen.restype = None
+        r.ref_attention_cache_widen.argtypes = [_u16p, _u16p, _f32p, _f32p] + [C.c_int] * 4
+        r.ref_tree_mask.restype = None
+        r.ref_tree_mask.argtypes = [_i32p, C.c_int, _u8p]
+        r.ref_attention_tree_loop.restype = None
+        r.ref_attention_tree_loop.argtypes = [_f32p] * 5 + [_i32p, _f32p] + [C.c_int] * 6 + [C.c_float]
         self._r = r
+
+    def attention_loop(self, q, k_all, v_all, start_pos: int, scale: float):
+        """The statements of TransformerModel::attention (transformer.mm:1779-1840) on q [B,Sq,Hq,D],
+        k_all / v_all [T,Hkv,D] fp32 -> context [B,Sq,Hq,D]."""
+        q = np.ascontiguousarray(q, np.float32)
+        k_all = np.ascontiguousarray(k_all, np.float32)
+        v_all = np.ascontiguousarray(v_all, np.float32)
+        b, sq, hq, d = q.shape
+        t, hkv, _ = k_all.shape
+        out = np.empty_like(q)
+        self._r.ref_attention_loop(q, k_all, v_all, out, b, sq, t, hq, hkv, d, start_pos, scale)
+        return out
+
+    def attention_cache_widen(self, ck, cv, total_seq: int):
+        """transformer.mm:1753-1765: [Hkv, max_seq, D] fp16 bits -> two [total_seq, Hkv, D] fp32."""
+        ck = np.ascontiguousarray(ck, np.uint16)
+        cv = np.ascontiguousarray(cv, np.uint16)
+        hkv, max_seq, d = ck.shape
+        k = np.empty((total_seq, hkv, d), np.float32)
+        v = np.empty_like(k)
+        self._r.ref_attention_cache_widen(ck, cv, k, v, hkv, max_seq, total_seq, d)
+        return k, v
+
+    def tree_mask(self, parents) -> np.ndarray:
+        """transformer.mm:822-841 on a parent array -> [N, N] bytes."""
+        parents = np.ascontiguousarray(parents, np.int32)
+        m = np.zeros((parents.size, parents.size), np.uint8)
+        self._r.ref_tree_mask(parents, parents.size, m)
+        return m
+
+    def attention_tree_loop(self, q, k_cached, v_cached, k_tree, v_tree, parents, scale: float):
+        """The statements of TransformerModel::attention_tree (transformer.mm:2044-2126), mask from
+        :822-841.  q [B,N,Hq,D]; k_cached / v_cached [L,Hkv,D]; k_tree / v_tree [B,N,Hkv,D]; fp32."""
+        q = np.ascontiguousarray(q, np.float32)
+        b, n, hq, d = q.shape
+        k_tree = np.ascontiguousarray(k_tree, np.float32)
+        v_tree = np.ascontiguousarray(v_tree, np.float32)
+        hkv = k_tree.shape[2]
+        k_cached = np.ascontiguousarray(k_cached, np.float32).reshape(-1, hkv, d)
+        v_cached = np.ascontiguousarray(v_cached, np.float32).reshape(-1, hkv, d)
+        out = np.empty_like(q)
+        self._r.ref_attention_tree_loop(q, k_cached, v_cached, k_tree, v_tree, np.ascontiguousarray(parents, np.int32),
+                                        out, b, n, k_cached.shape[0], hq, hkv, d, scale)
+        return out
 
     def rope_table(self, max_seq: int, head_dim: int, theta: float = 10000.0):
         cos = np.empty((max_seq, head_dim // 2), np.float32)

@@ -10,6 +10,12 @@ Sources of truth, per file:
   ref_kvcache_append.npz  reference KVCache::append layout (src/llm/kv_cache.cpp:52-107)
   ref_spec_tree.npz       reference SpeculationTree parents / depths / BFS order
                           (src/llm/speculation_tree.cpp:13-84)
+  ref_attention_loops.npz the reference's OWN attention statements - the blocks of src/llm/transformer.mm
+                          at :1779-1840 (attention), :1753-1765 (cache widening), :2044-2126 (tree
+                          attention) and :822-841 (tree mask), cut out of the checkout at build time
+                          and compiled into oracle/_ref (oracle/ref_loops.cpp) - run on seeded inputs
+                          with causal masks (start_pos 0 and > 0), GQA 4:1 and 8:1, a batch of two and
+                          a 64-node tree over a prefix.  Inputs and outputs are both stored.
   kat_sdpa_2x3x4.npz      the one attention known-answer test the reference holds
                           (tests/test_vulkan.cpp:353-482): inputs and expected values recomputed
                           here in numpy float32 in the test's own order, independently of oracle/
@@ -151,6 +157,69 @@ def ref_spec_tree(ref):
     np.savez_compressed(HERE / "ref_spec_tree.npz", **out)
 
 
+# (name, batch, seq_q, total_seq, start_pos, Hq, Hkv, D): what TransformerModel::attention is asked for
+ATTENTION_LOOP_CASES = [
+    ("prefill_gqa4", 1, 33, 33, 0, 8, 2, 32),          # causal from position 0, GQA 4:1
+    ("chunk_gqa8", 1, 5, 29, 24, 8, 1, 16),            # start_pos > 0, GQA 8:1: query i sees keys <= 24 + i
+    ("decode_d128", 1, 1, 77, 76, 8, 2, 128),          # one query token over a cache, head_dim 128
+    ("batch2_mha", 2, 3, 7, 4, 4, 4, 8),               # batch index in the query/context addressing
+    ("future_keys", 1, 2, 12, 3, 4, 2, 16),            # keys past start_pos + q stay masked although cached
+]
+# (name, batch, N nodes, prefix, Hq, Hkv, D, tree seed)
+TREE_LOOP_CASES = [
+    ("tree64_prefix100", 1, 64, 100, 8, 2, 32, 1004),  # the benchmark's tree shape over a prefix
+    ("tree16_no_prefix", 1, 16, 0, 4, 4, 16, 5),
+    ("tree33_gqa8_batch2", 2, 33, 9, 8, 1, 16, 8),
+]
+
+
+def ref_attention_loops(ref):
+    """Inputs are drawn like the cache holds them: K/V values that are exact in fp16 (stored as fp16
+    bits), fp32 queries; tree K/V are fp32 as the reference computes them (transformer.mm:1950-1975)."""
+    rng = np.random.default_rng(2044)
+    out = {}
+    for name, b, sq, t, start, hq, hkv, d in ATTENTION_LOOP_CASES:
+        q = rng.standard_normal((b, sq, hq, d), dtype=np.float32)
+        k16 = rng.standard_normal((t, hkv, d), dtype=np.float32).astype(np.float16)
+        v16 = rng.standard_normal((t, hkv, d), dtype=np.float32).astype(np.float16)
+        scale = np.float32(1.0) / np.sqrt(np.float32(d))
+        ctx = ref.attention_loop(q, k16.astype(np.float32), v16.astype(np.float32), start, float(scale))
+        out[f"{name}_cfg"] = np.array([b, sq, t, start, hq, hkv, d], np.int32)
+        out[f"{name}_scale"] = np.array([scale], np.float32)
+        out[f"{name}_q"], out[f"{name}_k16"], out[f"{name}_v16"] = q, k16.view(np.uint16), v16.view(np.uint16)
+        out[f"{name}_out"] = ctx.view(np.uint32)
+    # the widening of a cache that is longer than the live length
+    hkv, max_seq, d, total = 3, 40, 16, 27
+    ck = rng.integers(0, 65536, size=(hkv, max_seq, d)).astype(np.uint16)
+    cv = rng.integers(0, 65536, size=(hkv, max_seq, d)).astype(np.uint16)
+    kw, vw = ref.attention_cache_widen(ck, cv, total)
+    out.update(widen_cfg=np.array([hkv, max_seq, d, total], np.int32), widen_ck=ck, widen_cv=cv,
+               widen_k=kw.view(np.uint32), widen_v=vw.view(np.uint32))
+    for name, b, n, prefix, hq, hkv, d, seed in TREE_LOOP_CASES:
+        parents = synth.tree_parents(seed, n)
+        q = rng.standard_normal((b, n, hq, d), dtype=np.float32)
+        kp16 = rng.standard_normal((prefix, hkv, d), dtype=np.float32).astype(np.float16)
+        vp16 = rng.standard_normal((prefix, hkv, d), dtype=np.float32).astype(np.float16)
+        kt = rng.standard_normal((b, n, hkv, d), dtype=np.float32)
+        vt = rng.standard_normal((b, n, hkv, d), dtype=np.float32)
+        scale = np.float32(1.0) / np.sqrt(np.float32(d))
+        ctx = ref.attention_tree_loop(q, kp16.astype(np.float32), vp16.astype(np.float32), kt, vt, parents, float(scale))
+        out[f"{name}_cfg"] = np.array([b, n, prefix, hq, hkv, d], np.int32)
+        out[f"{name}_scale"] = np.array([scale], np.float32)
+        out[f"{name}_parents"] = parents
+        out[f"{name}_q"], out[f"{name}_kp16"], out[f"{name}_vp16"] = q, kp16.view(np.uint16), vp16.view(np.uint16)
+        out[f"{name}_kt"], out[f"{name}_vt"] = kt, vt
+        out[f"{name}_mask"] = np.packbits(ref.tree_mask(parents), axis=1)
+        out[f"{name}_out"] = ctx.view(np.uint32)
+    # masks alone: a chain, a star, several roots, one node
+    for i, parents in enumerate([np.arange(-1, 19), np.array([-1] + [0] * 11), np.array([-1, -1, 0, 1, 2, 3, -1, 6]),
+                                 np.array([-1])]):
+        parents = parents.astype(np.int32)
+        out[f"mask{i}_parents"] = parents
+        out[f"mask{i}"] = np.packbits(ref.tree_mask(parents), axis=1)
+    np.savez_compressed(HERE / "ref_attention_loops.npz", **out)
+
+
 def kat_sdpa():
     """tests/test_vulkan.cpp:366-474, recomputed in the test's own order with float32 steps."""
     f = np.float32
@@ -223,6 +292,7 @@ if __name__ == "__main__":
     ref_kvcache(ref)
     ref_spec_tree(ref)
     ref_rope(ref)
+    ref_attention_loops(ref)
     kat_sdpa()
     oracle_small_cases()
     for p in sorted(HERE.glob("*.npz")):

@@ -1,7 +1,7 @@
 """Pins the CPU checker (oracle/) before anything trusts it: against the reference's own
-compiled objects (golden files written by tests/golden/make_golden.py, and live against
-oracle/_ref when that library is present), and against the one attention known-answer test the
-reference holds (tests/test_vulkan.cpp:353-482)."""
+compiled objects and its own attention statements (golden files written by
+tests/golden/make_golden.py, and live against oracle/_ref when that library is present), and
+against the one attention known-answer test the reference holds (tests/test_vulkan.cpp:353-482)."""
 from pathlib import Path
 
 import numpy as np
@@ -42,6 +42,101 @@ def test_known_answer_2x3x4():
     q = g["q"][None, :, None, :]
     got2 = pyoracle.attention(q, k, v, start_pos=10, scale=float(g["scale"][0]), threads=1)[0, :, 0, :]
     assert np.abs(got2 - g["expected"]).max() <= 1e-4
+
+
+def _loop_cases(g, suffix="_cfg"):
+    names = [k[: -len(suffix)] for k in g.files if k.endswith(suffix)]
+    return [n for n in names if not n.startswith(("widen", "mask"))]
+
+
+def test_attention_loop_is_bit_identical_to_the_reference_statements():
+    """The restated loops against outputs of the reference's own statements (transformer.mm:1779-1840,
+    compiled from the checkout by oracle/ref_loops.cpp): causal masks with start_pos 0 and > 0, GQA 4:1
+    and 8:1, a batch of two, head_dim 128.  Bit for bit, with one thread and with several."""
+    g = np.load(GOLD / "ref_attention_loops.npz")
+    cases = [n for n in _loop_cases(g) if f"{n}_k16" in g.files]
+    assert len(cases) >= 5
+    for name in cases:
+        b, sq, t, start, hq, hkv, d = (int(x) for x in g[f"{name}_cfg"])
+        k = pyoracle.f16_bits_to_f32(g[f"{name}_k16"])
+        v = pyoracle.f16_bits_to_f32(g[f"{name}_v16"])
+        for threads in (1, 3):
+            got = pyoracle.attention(g[f"{name}_q"], k, v, start_pos=start, scale=float(g[f"{name}_scale"][0]), threads=threads)
+            assert np.array_equal(got.view(np.uint32), g[f"{name}_out"]), name
+        # scale 0 means 1/sqrt(head_dim) computed the reference's way (transformer.mm:1705)
+        got = pyoracle.attention(g[f"{name}_q"], k, v, start_pos=start, threads=2)
+        assert np.array_equal(got.view(np.uint32), g[f"{name}_out"]), name
+
+
+def test_cache_widening_is_bit_identical_to_the_reference_statements():
+    g = np.load(GOLD / "ref_attention_loops.npz")
+    hkv, max_seq, d, total = (int(x) for x in g["widen_cfg"])
+    assert np.array_equal(pyoracle.cache_to_fp32(g["widen_ck"], total).view(np.uint32), g["widen_k"])
+    assert np.array_equal(pyoracle.cache_to_fp32(g["widen_cv"], total).view(np.uint32), g["widen_v"])
+
+
+def test_tree_attention_and_mask_are_bit_identical_to_the_reference_statements():
+    """transformer.mm:2044-2126 with the mask of :822-841: a 64-node tree over a 100-token prefix (GQA 4:1),
+    a tree without a prefix, a batch of two with GQA 8:1."""
+    g = np.load(GOLD / "ref_attention_loops.npz")
+    cases = [n for n in _loop_cases(g) if f"{n}_parents" in g.files]
+    assert len(cases) >= 3
+    for name in cases:
+        b, n, prefix, hq, hkv, d = (int(x) for x in g[f"{name}_cfg"])
+        parents = g[f"{name}_parents"]
+        mask = pyoracle.tree_mask(parents)
+        assert np.array_equal(np.packbits(mask, axis=1), g[f"{name}_mask"]), name
+        kp = pyoracle.f16_bits_to_f32(g[f"{name}_kp16"])
+        vp = pyoracle.f16_bits_to_f32(g[f"{name}_vp16"])
+        for threads in (1, 3):
+            got = pyoracle.attention_tree(g[f"{name}_q"], kp, vp, g[f"{name}_kt"], g[f"{name}_vt"], parents,
+                                          scale=float(g[f"{name}_scale"][0]), threads=threads)
+            assert np.array_equal(got.view(np.uint32), g[f"{name}_out"]), name
+    for i in range(4):
+        assert np.array_equal(np.packbits(pyoracle.tree_mask(g[f"mask{i}_parents"]), axis=1), g[f"mask{i}"])
+
+
+@pytest.mark.skipif(not pyoracle.ref_available(), reason="oracle/_ref not built (needs the reference checkout)")
+def test_live_reference_statements_agree_on_fresh_seeded_cases():
+    """Where the compiled reference statements are present: fresh random shapes, bit for bit."""
+    ref = pyoracle.Ref()
+    rng = np.random.default_rng(1779)
+    for _ in range(12):
+        hkv = int(rng.choice([1, 2, 3, 4]))
+        hq = hkv * int(rng.choice([1, 2, 4, 8]))
+        d = int(rng.choice([8, 32, 64, 128]))
+        sq = int(rng.integers(1, 20))
+        past = int(rng.integers(0, 60))
+        extra = int(rng.integers(0, 3))  # keys cached beyond the last query's position
+        t = past + sq + extra
+        q = rng.standard_normal((1, sq, hq, d), dtype=np.float32)
+        k = rng.standard_normal((t, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+        v = rng.standard_normal((t, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+        want = ref.attention_loop(q, k, v, past, scale)
+        assert np.array_equal(pyoracle.attention(q, k, v, start_pos=past, scale=scale).view(np.uint32), want.view(np.uint32))
+        n = int(rng.integers(1, 65))
+        parents = synth.tree_parents(int(rng.integers(0, 1 << 30)), n)
+        tq = rng.standard_normal((1, n, hq, d), dtype=np.float32)
+        kt = rng.standard_normal((1, n, hkv, d), dtype=np.float32)
+        vt = rng.standard_normal((1, n, hkv, d), dtype=np.float32)
+        want = ref.attention_tree_loop(tq, k, v, kt, vt, parents, scale)
+        got = pyoracle.attention_tree(tq, k, v, kt, vt, parents, scale=scale)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(pyoracle.tree_mask(parents), ref.tree_mask(parents))
+    # the paged decode of the checker is the same loop over rows gathered through the table
+    case = synth.paged_case(seed=5, batch=3, len_lo=1, len_hi=200, num_heads=8, num_kv_heads=2, head_dim=64)
+    tables = np.where(case.tables < 0, 0, case.tables)
+    got, bad = pyoracle.paged_decode_batch(case.q, case.k_pool.view(np.uint16), case.v_pool.view(np.uint16), tables,
+                                           case.seq_lens, synth.PAGE)
+    assert bad == 0
+    for b in range(case.batch):
+        n = int(case.seq_lens[b])
+        kr, _ = pyoracle.paged_gather(case.k_pool.view(np.uint16), tables[b], n, synth.PAGE)
+        vr, _ = pyoracle.paged_gather(case.v_pool.view(np.uint16), tables[b], n, synth.PAGE)
+        want = ref.attention_loop(case.q[b][None, None], pyoracle.f16_bits_to_f32(kr), pyoracle.f16_bits_to_f32(vr), n - 1,
+                                  float(np.float32(1.0) / np.sqrt(np.float32(64))))
+        assert np.array_equal(got[b].view(np.uint32), want[0, 0].view(np.uint32))
 
 
 def test_oracle_small_cases_are_stable():
