@@ -742,8 +742,8 @@ def main():
 
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one paged_decode_splitkv
-# launch, from the ncu capture of the 16-sequence case summarised in
-# profiles/paged_decode_splitkv_b64.md; DRAM traffic grows in proportion to the tokens read.
+# launch, from an ncu capture of a 16-sequence case of the same kernel (ncu --set full
+# --clock-control none, one launch); DRAM traffic grows in proportion to the tokens read.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
 
 if __name__ == "__main__":

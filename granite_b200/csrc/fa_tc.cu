@@ -35,22 +35,12 @@
 //               rescale of O).  With one tile per item O alternates between the two accumulators and
 //               a finished item is read out behind the next item's first MMAs.
 // TMEM (512 columns): S[0] | S[1] | O[0] | O[1], 128 fp32 columns each.
-#include <cstdio>
 #include <cstring>
 
 #include "compute_internal.h"
 #include "ptx.cuh"
 
 namespace gb200 {
-
-// Development aid: built with -DGB_FA_TRACE one CTA records clock64() at the hand-over points of
-// its roles (slot = role * 256 + virtual step * 4 + event) and the launcher prints the timeline.
-#ifdef GB_FA_TRACE
-#define FA_TRACE(role, step, ev) \
-    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (step) < 64) p.trace[(role) * 256 + (step) * 4 + (ev)] = clock64(); } while (0)
-#else
-#define FA_TRACE(role, step, ev) do {} while (0)
-#endif
 
 constexpr int kTcThreads = 384;
 constexpr int kT = 128;                      // query rows per tile, keys per K/V tile, head_dim
@@ -79,7 +69,6 @@ struct TcParams {
     int batch, num_nodes, cache_len, cache_stride, max_blocks, num_blocks;
     int d_chunks;               // head_dim / 64: 2 (head_dim 128) or 1 (head_dim 64, half of every tile slot is used)
     int slot_shift;             // tree: a tile is (128 >> slot_shift) query heads x (1 << slot_shift) node slots
-    unsigned long long* trace;  // timeline hook, only used in GB_FA_TRACE builds
 };
 
 struct TcSmem {
@@ -173,21 +162,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     // of a group follow its first after 1 KB; the MMA descriptors take either pitch.
     const uint32_t group_bytes = kPaged ? 1024u * p.d_chunks : 1024u;
     const uint32_t chunk_off = kPaged ? 1024u : (uint32_t)kChunkBytes;
-#ifdef GB_FA_TRACE
-    if (threadIdx.x == 0) {
-        unsigned long long gt;
-        unsigned smid;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        if (blockIdx.x == 0) {
-            p.trace[3 * 256 + 0] = gt;
-            p.trace[3 * 256 + 1] = clock64();
-        }
-        p.trace[1024 + blockIdx.x * 4 + 0] = gt;
-        p.trace[1024 + blockIdx.x * 4 + 2] = smid;
-        p.trace[1024 + blockIdx.x * 4 + 3] = clock64();
-    }
-#endif
 
     // ---- work items.  Prefill: ordered heaviest query block first and dealt to the CTAs in a snake
     // (round r left to right when even, right to left when odd), which keeps the summed causal work
@@ -393,18 +367,15 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     ok = mbar_wait(&sh->q_full, items_done & 1, abort_flag);
                     items_done++;
                     for (int j = 0; j < it.n_steps && ok; j++) {
-                        FA_TRACE(0, vs, 3);
                         ok = mbar_wait(&sh->k_full[st], ph, abort_flag);
                         const uint32_t idesc = (kTree && j == it.n_prefix) ? idesc_qk_tree : idesc_qk;  // 64 keys in the tree tile
                         const uint32_t k_lo = k_lo0 + st * (kTileBytes >> 4);
 #pragma unroll
                         for (int t = 0; t < kTiles; t++, vs++) {
                             const int b = vs & 1;
-                            FA_TRACE(0, vs, 0);
                             // S_b still holds P of virtual step vs-2 until both output-MMA halves of it are done
                             if (ok && vs >= 2) ok = mbar_wait(&sh->s_free[b], ((vs >> 1) - 1) & 1, abort_flag);
                             if (!ok) break;
-                            FA_TRACE(0, vs, 1);
                             tc_fence_after_sync();
                             const uint32_t d = tmem + b * kT;
                             const uint32_t q_lo = q_lo0 + t * (kTileBytes >> 4);
@@ -429,7 +400,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                                 }
                             }
                             tc_commit(&sh->s_full[b]);
-                            FA_TRACE(0, vs, 2);
                         }
                         if (!ok) break;
                         tc_commit(&sh->k_empty[st]);
@@ -462,17 +432,14 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     const uint32_t o_sel = kTiles == 1 ? (items_done & 1) : 0;
                     items_done++;
                     for (int j = 0; j < it.n_steps && ok; j++) {
-                        if (part == 0) FA_TRACE(1, vs, 3);
                         ok = mbar_wait(&sh->v_full[st], ph, abort_flag);
                         const uint32_t v_lo = v_lo0 + st * (kTileBytes >> 4);
                         const int nks = (kTree && j == it.n_prefix) ? 4 : 8;  // 16 keys per step; the tree tile has 64
 #pragma unroll
                         for (int t = 0; t < kTiles; t++, vs++) {
                             const int b = vs & 1;
-                            if (part == 0) FA_TRACE(1, vs, 0);
                             if (ok) ok = mbar_wait(&sh->p_ready[b], (vs >> 1) & 1, abort_flag);
                             if (!ok) break;
-                            if (part == 0) FA_TRACE(1, vs, 1);
                             tc_fence_after_sync();
                             const uint32_t d = tmem + 2 * kT + (t + o_sel) * kT;
                             // P: hi in columns 0-63 of S_b, lo in 64-127, 8 columns per 16 keys;
@@ -485,7 +452,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                                 }
                             }
                             tc_commit(&sh->s_free[b]);
-                            if (part == 0) FA_TRACE(1, vs, 2);
                         }
                         if (!ok) break;
                         tc_commit(&sh->v_empty[st]);
@@ -625,9 +591,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     const int b = vs & 1;
                     const uint32_t s_frag = frag_base + b * kT;
                     const uint32_t o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
-                    if (warp == 4) FA_TRACE(2, vs, 0);
                     if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
-                    if (warp == 4) FA_TRACE(2, vs, 1);
                     if (!ok) continue;  // a role gave up: nothing below synchronises with another warp
                     tc_fence_after_sync();
                     // the two rows' scores: x[h][4i + 2q + e] = row q, column 64 h + 8 i + 2 tq + e
@@ -672,7 +636,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                         mx[q] = m * p.scale_log2;
                     }
-                    if (warp == 4) FA_TRACE(6, vs, 1);
                     if (j == 0) {
                         m_used[0] = mx[0];
                         m_used[1] = mx[1];
@@ -753,7 +716,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         fence_proxy_async_smem();
                     }
                     __syncwarp();
-                    if (warp == 4) FA_TRACE(6, vs, 2);
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(&sh->p_ready[b]);
@@ -762,9 +724,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         m_used_t[ti][q] = m_used[q];
                         l_run_t[ti][q] = l_run[q];
                     }
-                    if (warp == 4) FA_TRACE(2, vs, 2);
                     if (kDefer && pend.halves_left > 0) readout_half(pend);  // behind the MMAs of this step
-                    if (warp == 4) FA_TRACE(2, vs, 3);
                 }
             }
             while (kDefer && pend.halves_left > 0) readout_half(pend);  // an item shorter than the read-out
@@ -806,18 +766,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-#ifdef GB_FA_TRACE
-    if (threadIdx.x == 0) {
-        unsigned long long gt;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        if (blockIdx.x == 0) {
-            p.trace[3 * 256 + 2] = gt;
-            p.trace[3 * 256 + 3] = clock64();
-        }
-        p.trace[1024 + blockIdx.x * 4 + 1] = gt;
-        p.trace[1024 + blockIdx.x * 4 + 3] = clock64() - p.trace[1024 + blockIdx.x * 4 + 3];
-    }
-#endif
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, 512);
@@ -836,50 +784,10 @@ static int launch_tc(granite_cuda_compute* c, TcKernel kern, const char* name, i
     if (smem_bytes > (size_t)c->smem_optin) smem_bytes = (size_t)c->smem_optin;  // the window is 1 KB aligned in practice
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     const int grid = n_items < c->sm_count ? n_items : c->sm_count;  // persistent CTAs, one per SM
-#ifdef GB_FA_TRACE
-    static unsigned long long* trace_buf = nullptr;
-    if (!trace_buf) cudaMalloc(&trace_buf, 8 * 256 * sizeof(unsigned long long));
-    cudaMemsetAsync(trace_buf, 0, 8 * 256 * sizeof(unsigned long long), c->stream);
-    TcParams pt = p;
-    pt.trace = trace_buf;
-    {
-        LaunchScope t(c, name);
-        kern<<<grid, kTcThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, *ktmap, *vtmap, pt);
-    }
-    static unsigned long long host_trace[8 * 256];
-    cudaMemcpyAsync(host_trace, trace_buf, sizeof(host_trace), cudaMemcpyDeviceToHost, c->stream);
-    cudaStreamSynchronize(c->stream);
-    {
-        fprintf(stderr, "trace cta0: %lld ns, %lld cycles -> %.3f GHz\n", (long long)(host_trace[768 + 2] - host_trace[768 + 0]),
-                (long long)(host_trace[768 + 3] - host_trace[768 + 1]),
-                (double)(host_trace[768 + 3] - host_trace[768 + 1]) / (double)(host_trace[768 + 2] - host_trace[768 + 0]));
-        unsigned long long first = ~0ull, last = 0;
-        for (int b = 0; b < grid; b++) {
-            first = host_trace[1024 + b * 4] < first ? host_trace[1024 + b * 4] : first;
-            last = host_trace[1024 + b * 4 + 1] > last ? host_trace[1024 + b * 4 + 1] : last;
-        }
-        fprintf(stderr, "trace grid: first start -> last end %lld ns\n", (long long)(last - first));
-        for (int b = 0; b < grid; b++)
-            fprintf(stderr, "trace cta %3d sm %3d: start +%6lld ns, end +%6lld ns, life %6lld ns, %7lld clk\n", b,
-                    (int)host_trace[1024 + b * 4 + 2], (long long)(host_trace[1024 + b * 4] - first),
-                    (long long)(host_trace[1024 + b * 4 + 1] - first),
-                    (long long)(host_trace[1024 + b * 4 + 1] - host_trace[1024 + b * 4]), (long long)host_trace[1024 + b * 4 + 3]);
-        const unsigned long long t0 = host_trace[768 + 1];
-        const char* roles[4] = {"qk ", "pvh", "smx", "sm2"};
-        const int role_slot[4] = {0, 1, 2, 6};
-        for (int step = 0; step < 64; step++)
-            for (int r = 0; r < 4; r++) {
-                const unsigned long long* row = host_trace + role_slot[r] * 256 + step * 4;
-                fprintf(stderr, "trace %s vstep %2d: %8lld %8lld %8lld %8lld\n", roles[r], step, (long long)(row[0] - t0),
-                        (long long)(row[1] - t0), (long long)(row[2] - t0), (long long)(row[3] - t0));
-            }
-    }
-#else
     {
         LaunchScope t(c, name);
         kern<<<grid, kTcThreads, smem_bytes, c->stream>>>(*qmap, *qlomap, *kmap, *vmap, *ktmap, *vtmap, p);
     }
-#endif
     GB_CUDA_TRY(cudaGetLastError());
     return GRANITE_CUDA_SUCCESS;
 }

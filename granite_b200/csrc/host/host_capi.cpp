@@ -532,4 +532,59 @@ int granite_host_decode_batch_flow(int device, int batch, const int32_t* lens0, 
     return 0;
 }
 
+// The device block-table rows of PagedDecodeBatch after a sequence's table shrank and regrew
+// over different blocks: request 0 grows across a block boundary and is synced; it is truncated
+// back across the boundary (its tail block returns to the pool), request 1 grows and is handed
+// that block, request 0 regrows over another one.  After the next begin_step the device row of
+// each request must equal its PagedKVCache table.  Returns rows as [2, max_blocks] each.
+int granite_host_decode_batch_regrow(int device, int block_size, int max_blocks, int32_t* device_rows,
+                                     int32_t* host_rows, int32_t* lens_out) {
+    auto be = create_cuda_backend(device);
+    auto init = be->initialize();
+    if (!init.ok()) return host_fail(init.error());
+    CudaCompute compute;
+    auto ci = compute.initialize(device, be->get_native_queue());
+    if (!ci.ok()) return host_fail(ci.error());
+    ModelConfig cfg;
+    cfg.num_layers = 1;
+    cfg.num_heads = 8;
+    cfg.num_kv_heads = 2;
+    cfg.head_dim = 128;
+    PagedKVPool pool;
+    auto pr = pool.initialize(cfg, 2, 2 * max_blocks * block_size, block_size, be.get());
+    if (!pr.ok()) return host_fail(pr.error());
+    RoPECache rope;
+    rope.initialize(max_blocks * block_size, cfg.head_dim);
+    auto up = rope.upload(compute.handle());
+    if (!up.ok()) return host_fail(up.error());
+    if (pool.acquire_slot() != 0 || pool.acquire_slot() != 1) return 6101;
+    PagedDecodeBatch decode;
+    auto di = decode.initialize(&pool, &compute, &rope, cfg, 2, max_blocks);
+    if (!di.ok()) return host_fail(di.error());
+    if (decode.add_request(0) != 0 || decode.add_request(1) != 1) return 6102;
+    // request 0: two full blocks and one token of a third; request 1: half a block
+    if (!pool.get_cache(0).append_tokens(2 * block_size) || !pool.get_cache(1).append_tokens(block_size / 2)) return 6103;
+    auto s1 = decode.begin_step();  // both grow by one token; rows go up
+    if (!s1.ok()) return host_fail(s1.error());
+    const int third_before = pool.get_cache(0).block_table()[2];
+    pool.get_cache(0).truncate(2 * block_size - 3);                 // frees the third block
+    if (!pool.get_cache(1).append_tokens(block_size)) return 6104;  // request 1 takes it
+    if (pool.get_cache(1).block_table()[1] != third_before) return 6105;
+    if (!pool.get_cache(0).append_tokens(3)) return 6106;           // back to two full blocks
+    auto s2 = decode.begin_step();                                  // request 0 crosses the boundary again
+    if (!s2.ok()) return host_fail(s2.error());
+    if (pool.get_cache(0).block_table()[2] == third_before) return 6107;
+    granite_cuda_read_buffer(compute.handle(), device_rows, decode.device_tables(), static_cast<size_t>(2) * max_blocks * 4);
+    granite_cuda_read_buffer(compute.handle(), lens_out, decode.device_seq_lens(), 2 * 4);
+    auto sr = compute.sync_checked();
+    if (!sr.ok()) return host_fail(sr.error());
+    for (int b = 0; b < 2; b++) {
+        const auto& table = pool.get_cache(b).block_table();
+        for (int j = 0; j < max_blocks; j++)
+            host_rows[b * max_blocks + j] = j < static_cast<int>(table.size()) ? table[static_cast<size_t>(j)] : -1;
+        lens_out[2 + b] = pool.get_cache(b).seq_len();
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -29,6 +29,7 @@ def _lib():
     lib.granite_host_rope_apply.argtypes = [C.c_int, _f32p, _f32p] + [C.c_int] * 6 + [C.c_float]
     lib.granite_host_decode_batch_flow.argtypes = [C.c_int, C.c_int, _i32p] + [C.c_int] * 10 + [_f32p] * 7 + \
         [_i32p, _i32p, _u16p, _u16p]
+    lib.granite_host_decode_batch_regrow.argtypes = [C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p]
     return lib
 
 
@@ -287,3 +288,22 @@ def test_batched_decode_loop_replays_on_the_cpu_checker(lens0, n_steps, remove_s
             for pos in range(int(lens[-1, b])):
                 live[tables[-1, b, pos // bs] * bs + pos % bs] = True
     assert np.array_equal(k_pool[live], ck[live]) and np.array_equal(v_pool[live], cv[live])
+
+
+def test_device_block_table_follows_a_table_that_shrank_and_regrew():
+    """A sequence truncated across a block boundary (as after a tree commit) whose freed block went to
+    another request and which then regrew over a different block: the device row must not keep the
+    freed block's number."""
+    lib = _lib()
+    bs, max_blocks = 16, 6
+    dev_rows = np.full((2, max_blocks), -7, np.int32)
+    host_rows = np.full((2, max_blocks), -7, np.int32)
+    lens = np.zeros(4, np.int32)
+    rc = lib.granite_host_decode_batch_regrow(0, bs, max_blocks, dev_rows.reshape(-1), host_rows.reshape(-1), lens)
+    assert rc == 0, (rc, lib.granite_host_last_error())
+    assert np.array_equal(lens[:2], lens[2:])
+    for b in range(2):
+        n = int((host_rows[b] >= 0).sum())
+        assert n == (lens[2 + b] + bs - 1) // bs
+        assert np.array_equal(dev_rows[b, :n], host_rows[b, :n]), (b, dev_rows[b], host_rows[b])
+    assert len(set(host_rows[host_rows >= 0].tolist())) == int((host_rows >= 0).sum())  # no block owned twice
