@@ -10,9 +10,16 @@ independent: sharded by sequence, no collective inside attention); every step th
 are gathered on every rank by the decode kernel itself, which stores each final row into every rank's buffer
 (peer stores over NVLink into symmetric memory; NCCL all-gather as the fall-back).  Prints ONE JSON line (rank 0).
 
---impl reference times Granite's CPU attention arithmetic (oracle/, a restatement of
-src/llm/transformer.mm:1779-1840 over pages fetched by the rule of metal_compute.h:853-861, with
-the reference's thread policy) on a bounded sample of the same workload, on the host cores.
+Every run (every N, N = 1 included) also carries `secondary.long_context_b256`: ONE fixed problem - 256
+sequences, context lengths log-uniform in [4096, 131072], Hq 64 - split over the N ranks (strong scaling),
+by sequence and, when the KV heads divide among the ranks, by KV head; its `ms_per_step` at N = 1, 2, 4, 8
+gives the scaling efficiency T(1) / (N T(N)) on the identical problem.
+
+--impl reference times Granite's CPU attention arithmetic on a bounded sample of the same workload, on
+the host cores: pages fetched by the rule of metal_compute.h:853-861 into the contiguous cache layout,
+then the reference's own statements - the cache widening of src/llm/transformer.mm:1753-1765 and the
+loop of :1779-1840 with its thread policy - compiled from the checkout into oracle/_ref when that was
+built (kind "reference"), else their restatement in oracle/ (kind "port").
 """
 from __future__ import annotations
 
@@ -32,6 +39,7 @@ sys.path.insert(0, str(ROOT))
 WORKLOAD = "paged_decode_b64"
 METRIC = "paged decode attention GB/s"
 UNIT = "GB/s"
+kT_ROWS = 128  # rows and keys per tile of the tensor-core kernel
 
 
 def measured_peaks():
@@ -97,23 +105,62 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def cpu_baseline_sample(case_np, stride: int, repeats: int = 1):
-    """Times the CPU checker on every `stride`-th sequence; returns (GB/s, seconds, bytes)."""
+def cpu_arm():
+    """(kind, ref): the reference's own compiled statements (oracle/_ref) when present, else the port."""
+    from oracle import pyoracle
+    if pyoracle.ref_available():
+        try:
+            return "reference", pyoracle.Ref()
+        except Exception as exc:  # noqa: BLE001 - a stale or unloadable build: fall back to the port
+            print(f"[bench] oracle/_ref not usable ({exc!r}); timing the port", file=sys.stderr)
+    return "port", None
+
+
+def cpu_threads(ref) -> int:
+    from oracle import pyoracle
+    return ref.num_threads() if ref is not None else pyoracle.num_threads()
+
+
+def cpu_decode_sample(case_np, ref, repeats: int = 1):
+    """Times Granite's CPU decode path on every sequence of `case_np`: pages gathered into the
+    contiguous cache layout [Hkv, len, D] (metal_compute.h:853-861), the whole-cache fp16 -> fp32
+    widening (transformer.mm:1753-1765) and the attention loop (:1779-1840, seq_q = 1).  The page
+    gather stands in for the contiguous KVCache the reference's CPU path reads and is not timed.
+    Returns (bytes, seconds of widening + loop, seconds of the loop alone, sequences): best of `repeats`."""
     from oracle import pyoracle
     from granite_b200 import synth
-    sel = np.arange(0, case_np["seq_lens"].shape[0], stride)
-    lens = case_np["seq_lens"][sel]
+    lens = case_np["seq_lens"]
     hkv, d, hq = case_np["num_kv_heads"], case_np["head_dim"], case_np["num_heads"]
     pages = int(((lens + synth.PAGE - 1) // synth.PAGE).sum())
-    nbytes = int(lens.sum()) * hkv * d * 2 * 2 + pages * 4 + len(sel) * 4 + len(sel) * hq * d * 4 * 2
-    best = None
+    nbytes = int(lens.sum()) * hkv * d * 2 * 2 + pages * 4 + len(lens) * 4 + len(lens) * hq * d * 4 * 2
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    best_all, best_loop = None, None
     for _ in range(repeats):
-        t0 = time.perf_counter()
-        pyoracle.paged_decode_batch(case_np["q"], case_np["k_pool"], case_np["v_pool"], case_np["tables"],
-                                    case_np["seq_lens"], synth.PAGE, stride=stride)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return nbytes / best / 1e9, best, nbytes, len(sel)
+        t_all = t_loop = 0.0
+        for b, n in enumerate(int(x) for x in lens):
+            if n == 0:
+                continue
+            pos = np.arange(n)
+            rows = case_np["tables"][b, pos // synth.PAGE].astype(np.int64) * synth.PAGE + pos % synth.PAGE
+            ck = np.ascontiguousarray(case_np["k_pool"][rows].transpose(1, 0, 2))
+            cv = np.ascontiguousarray(case_np["v_pool"][rows].transpose(1, 0, 2))
+            t0 = time.perf_counter()
+            if ref is not None:
+                kf, vf = ref.attention_cache_widen(ck, cv, n)
+            else:
+                kf, vf = pyoracle.cache_to_fp32(ck, n), pyoracle.cache_to_fp32(cv, n)
+            t1 = time.perf_counter()
+            q = case_np["q"][b][None, None]
+            if ref is not None:
+                ref.attention_loop(q, kf, vf, n - 1, scale)
+            else:
+                pyoracle.attention(q, kf, vf, start_pos=n - 1, scale=scale)
+            t2 = time.perf_counter()
+            t_all += t2 - t0
+            t_loop += t2 - t1
+        best_all = t_all if best_all is None else min(best_all, t_all)
+        best_loop = t_loop if best_loop is None else min(best_loop, t_loop)
+    return nbytes, best_all, best_loop, len(lens)
 
 
 def host_case_for_cpu(seed: int, cfg: dict, sel):
@@ -141,15 +188,15 @@ def run_reference(args):
     workload - whole sequences taken from every 16th position - sized from a calibration run so
     that all steps together take about two minutes."""
     from granite_b200 import synth
-    from oracle import pyoracle
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    kind, ref = cpu_arm()
     cfg = dict(synth.CONFIGS[WORKLOAD])
     lens_all = workload_lengths(cfg)
     shortest = int(np.argmin(lens_all))
     calib = host_case_for_cpu(cfg["seed"], cfg, [shortest])
-    _, secs, _, _ = cpu_baseline_sample(calib, 1)
+    _, secs, _, _ = cpu_decode_sample(calib, ref)
     tok_per_s = float(lens_all[shortest]) / secs
     budget_tokens = tok_per_s * 120.0 / max(args.steps + args.warmup, 1)
     sel, tokens = [], 0
@@ -161,15 +208,16 @@ def run_reference(args):
         sel = [shortest]
     hc = host_case_for_cpu(cfg["seed"], cfg, sel)
     for _ in range(args.warmup):
-        cpu_baseline_sample(hc, 1)
+        cpu_decode_sample(hc, ref)
     t0 = time.perf_counter()
-    nbytes = 0
+    nbytes, loop_s = 0, 0.0
     for _ in range(args.steps):
-        _, _, b, nseq = cpu_baseline_sample(hc, 1)
+        b, _, t_loop, _ = cpu_decode_sample(hc, ref)
         nbytes += b
+        loop_s += t_loop
     dt = time.perf_counter() - t0
     value = nbytes / dt / 1e9
-    cores = pyoracle.num_threads()
+    cores = cpu_threads(ref)
     sample = (f"sequences {sel} of the workload's {cfg['batch']} ({int(hc['seq_lens'].sum())} tokens) per step")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
@@ -178,11 +226,71 @@ def run_reference(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample, "page": 16, "num_heads": cfg["num_heads"],
                    "num_kv_heads": cfg["num_kv_heads"], "head_dim": cfg["head_dim"]},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
+                         "value_loop_only": nbytes / loop_s / 1e9,
+                         "note": "value: the reference's serial whole-cache fp16->fp32 widening + the attention loop on all "
+                                 "host threads, as its CPU path runs each call; value_loop_only: the loop alone"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
     return 0
+
+
+def cpu_prefill_sample(ref, kind: str, seq: int, d: int, heads: int = 4):
+    """The reference loop (transformer.mm:1779-1840, causal from position 0) on `heads` query heads of one KV head
+    of the prefill configuration; returns a cpu_baseline object in TFLOP/s."""
+    from oracle import pyoracle
+    rng = np.random.default_rng(1002)
+    q = rng.standard_normal((1, seq, heads, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    k = rng.standard_normal((seq, 1, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    v = rng.standard_normal((seq, 1, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        if ref is not None:
+            ref.attention_loop(q, k, v, 0, scale)
+        else:
+            pyoracle.attention(q, k, v, start_pos=0, scale=scale)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    flops = 4 * d * heads * seq * (seq + 1) // 2
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(ref), "kind": kind,
+            "sample": f"{heads} query heads of one KV head, all {seq} tokens, best of 3, {best:.2f} s each; "
+                      "the loop computes the masked half too (it tests k_pos > abs_pos inside), credited flops are the unmasked half"}
+
+
+def cpu_tree_sample(ref, kind: str, n: int, prefix: int, d: int, parents, heads: int = 8, hkv: int = 2):
+    """The reference tree loop (transformer.mm:2044-2126) on one sequence of the tree configuration with
+    `heads` query heads over `hkv` KV heads."""
+    from oracle import pyoracle
+    rng = np.random.default_rng(1004)
+    q = rng.standard_normal((1, n, heads, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    kp = rng.standard_normal((prefix, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    vp = rng.standard_normal((prefix, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    kt = rng.standard_normal((1, n, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    vt = rng.standard_normal((1, n, hkv, d), dtype=np.float32).astype(np.float16).astype(np.float32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        if ref is not None:
+            ref.attention_tree_loop(q, kp, vp, kt, vt, parents, scale)
+        else:
+            pyoracle.attention_tree(q, kp, vp, kt, vt, parents, scale=scale)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    visible = 0
+    for i in range(n):
+        c, depth = parents[i], 1
+        while c >= 0:
+            depth += 1
+            c = parents[c]
+        visible += depth
+    flops = 4 * d * heads * (n * prefix + visible)
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(ref), "kind": kind,
+            "sample": f"one sequence ({prefix}-token prefix + {n}-node tree), {heads} query heads over {hkv} KV heads, "
+                      f"best of 3, {best:.2f} s each"}
 
 
 def tensor_peak():
@@ -223,7 +331,22 @@ def region_ms_per_launch(dev, step, reps: int, clocks: dict | None = None) -> fl
     return e0.elapsed_time(e1) / reps
 
 
-def measure_prefill(compute, dev, reps: int = 200):
+def e2e_ms_per_call(dev, call, reps: int = 30) -> float:
+    """Average duration of `call` (host buffers in, result out, sync inside) over `reps` calls, CUDA events."""
+    import torch
+    for _ in range(3):
+        call()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def measure_prefill(compute, dev, reps: int = 200, with_cpu: bool = True):
     """Causal prefill, seq 2048, Hq 32, Hkv 8, D 128, fp16 in/out (the prefill benchmark configuration); the
     kernel's own event-timed duration, rotating over 4 input sets."""
     import torch
@@ -258,15 +381,40 @@ def measure_prefill(compute, dev, reps: int = 200):
     flops = 4 * d * hq * seq * (seq + 1) // 2
     burst, sustained, kind = tensor_peak()
     tf = flops / ms / 1e9
-    return {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms,
-            "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
-            "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst,
-            "frac": tf / burst, "frac_of_sustained": tf / sustained, "peak_kind": kind,
-            "note": "unmasked half of the causal square counted only; P enters the PV product as fp16 hi+lo "
-                    "(two MMAs) to keep the CPU path's precision, which the flop count does not credit"}
+    # end to end through the C ABI: host Q/K/V (pinned, fp16) copied in, output copied out, sync per call
+    q_h, k_h, v_h = (t.cpu().pin_memory() for t in sets[0])
+    out_h = torch.empty((seq, hq, d), dtype=torch.float16).pin_memory()
+    q_d, k_d, v_d = (torch.empty_like(t) for t in sets[0])
+
+    def e2e_call():
+        compute.write_buffer(q_d, q_h, q_h.numel() * 2)
+        compute.write_buffer(k_d, k_h, k_h.numel() * 2)
+        compute.write_buffer(v_d, v_h, v_h.numel() * 2)
+        compute.multihead_attention(q_d, k_d, v_d, out, hq, hkv, seq, seq, d, 1.0 / float(np.sqrt(d)), seq,
+                                    q_dtype=1, out_dtype=1)
+        compute.read_buffer(out_h, out, out_h.numel() * 2)
+        compute.sync()
+
+    e2e_ms = e2e_ms_per_call(dev, e2e_call)
+    # the pipe executes more than is credited: P as hi + lo (1.5x) and the diagonal tile in full (+6 %)
+    executed = 1.5 * (1.0 + (kT_ROWS - 1) / (seq + 1))
+    res = {"workload": "prefill_causal_s2048", "kernel": "prefill_causal_fa", "kernel_ms": ms,
+           "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
+           "algorithmic_flops": flops, "tflops": tf, "bound": "tensor", "peak_tflops": burst,
+           "frac": tf / burst, "frac_of_sustained": tf / sustained, "peak_kind": kind,
+           "frac_executed": tf * executed / burst,
+           "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_call": e2e_ms,
+                   "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2, "d2h_bytes_per_step": out_h.numel() * 2},
+           "note": "unmasked half of the causal square counted only; P enters the PV product as fp16 hi+lo "
+                   "(two MMAs) to keep the CPU path's precision, which `frac` does not credit; `frac_executed` counts "
+                   "what the tensor pipe runs (hi + lo, and the whole diagonal tile)"}
+    if with_cpu:
+        ckind, ref = cpu_arm()
+        res["cpu_baseline"] = cpu_prefill_sample(ref, ckind, seq, d)
+    return res
 
 
-def measure_tree(compute, dev, reps: int = 200, nodes: int = 0):
+def measure_tree(compute, dev, reps: int = 200, nodes: int = 0, with_cpu: bool = True):
     """Tree verification: 16 sequences x (4096-token paged prefix + 64-node tree), Hq 32, Hkv 8
     (the tree-verification benchmark configuration); rotates over 3 pools (268 MB of prefix K/V each, larger than L2)."""
     import torch
@@ -319,11 +467,37 @@ def measure_tree(compute, dev, reps: int = 200, nodes: int = 0):
     hbm, hkind = measured_peaks()
     tf = flops / ms / 1e9
     gbs = nbytes / ms / 1e6
-    return {"workload": "tree_verify_b16" if n == cfg["nodes"] else f"tree_verify_b16_n{n}", "kernel": "tree_verify", "kernel_ms": ms,
-            "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
-            "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
-            "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
-            "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind}
+    # end to end through the C ABI: host queries, tree K/V and parents in, output out, sync per call; the
+    # committed prefix is cache state and stays in the paged pool
+    q_h, kt_h, vt_h, par_h = q.cpu().pin_memory(), kt.cpu().pin_memory(), vt.cpu().pin_memory(), parents.cpu().pin_memory()
+    out_h = torch.empty((batch, hq, n, d), dtype=torch.float32).pin_memory()
+    q_e, kt_e, vt_e, par_e = torch.empty_like(q), torch.empty_like(kt), torch.empty_like(vt), torch.empty_like(parents)
+
+    def e2e_call():
+        compute.write_buffer(q_e, q_h, q_h.numel() * 2)
+        compute.write_buffer(kt_e, kt_h, kt_h.numel() * 2)
+        compute.write_buffer(vt_e, vt_h, vt_h.numel() * 2)
+        compute.write_buffer(par_e, par_h, par_h.numel() * 4)
+        c = cases[0]
+        compute.attention_tree(q_e, c.k_pool, c.v_pool, kt_e, vt_e, par_e, out, hq, hkv, n, L, d,
+                               1.0 / float(np.sqrt(d)), batch_size=batch, block_tables=tables[0],
+                               max_blocks_per_seq=c.max_blocks, num_blocks=c.num_blocks, q_dtype=1)
+        compute.read_buffer(out_h, out, out_h.numel() * 4)
+        compute.sync()
+
+    e2e_ms = e2e_ms_per_call(dev, e2e_call)
+    res = {"workload": "tree_verify_b16" if n == cfg["nodes"] else f"tree_verify_b16_n{n}", "kernel": "tree_verify", "kernel_ms": ms,
+           "kernel_ms_timed_singly": ms_each, "launches": reps, "clocks": clocks,
+           "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": tf, "gbs": gbs,
+           "bound": "ridge (256 flop/B): both fractions reported", "frac_tensor": tf / burst,
+           "frac_hbm": gbs / hbm, "peak_tflops": burst, "peak_gbs": hbm, "peak_kind": kind,
+           "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_call": e2e_ms,
+                   "h2d_bytes_per_step": (q_h.numel() + kt_h.numel() + vt_h.numel()) * 2 + par_h.numel() * 4,
+                   "d2h_bytes_per_step": out_h.numel() * 4}}
+    if with_cpu and n == cfg["nodes"]:
+        ckind, ref = cpu_arm()
+        res["cpu_baseline"] = cpu_tree_sample(ref, ckind, n, L, d, parents_np[0])
+    return res
 
 
 def measure_decode_step_write(compute, dev, reps: int = 200):
@@ -446,7 +620,155 @@ def measure_single_decode(compute, dev, reps: int = 200):
 
 def measure_tree16(compute, dev, reps: int = 200):
     """The tree configuration with 16-node trees: four query heads share a 128-row tile."""
-    return measure_tree(compute, dev, reps, nodes=16)
+    return measure_tree(compute, dev, reps, nodes=16, with_cpu=False)
+
+
+class Gather:
+    """Buffers every rank's output rows are gathered into: symmetric memory whose peer addresses the
+    decode kernel stores to directly, or - where that cannot be set up on every rank - plain buffers
+    filled by an NCCL all-gather after each step."""
+
+    def __init__(self, dist, dev, world: int, shape):
+        import torch
+        self.dist, self.world = dist, world
+        self.bufs, self.peer_ptrs = None, None
+        self.mode = "none"
+        if world == 1:
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm
+            self.bufs = [symm.empty(shape, dtype=torch.float32, device=dev) for _ in range(2)]
+            for t in self.bufs:
+                t.zero_()  # padding rows (ranks own different numbers of sequences) compare equal
+            handles = [symm.rendezvous(t, dist.group.WORLD) for t in self.bufs]
+            self.peer_ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
+            self.mode = "rows stored to every rank by the decode kernel (peer stores over NVLink, symmetric memory)"
+        except Exception as exc:  # noqa: BLE001 - any failure means: use the collective library
+            print(f"[bench] symmetric memory unavailable ({exc!r}); gathering with NCCL", file=sys.stderr)
+            self.peer_ptrs = None
+        flags = torch.tensor([1 if self.peer_ptrs else 0], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same route
+        if int(flags.item()) == 0:
+            self.bufs = [torch.zeros(shape, device=dev) for _ in range(2)]
+            self.peer_ptrs, self.mode = None, "NCCL all-gather per step"
+
+
+def timed_regions(dev, dist, world: int, step, steps: int, min_regions: int = 5, min_total_s: float = 0.5,
+                  max_regions: int = 40, clock_index=None):
+    """Times regions of exactly `steps` calls of step(i), each bracketed by a barrier and a device
+    synchronize on both sides, CUDA events on the current stream, maximum over the ranks per region;
+    regions are repeated until there are `min_regions` of them and they cover `min_total_s`.
+    Returns (median ms per step, best ms per step, regions, clock record)."""
+    import torch
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(clock_index, 0.002) if clock_index is not None else None
+    per_step, total = [], 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if sampler:
+        sampler.start()
+    while len(per_step) < max_regions and (len(per_step) < min_regions or total < min_total_s):
+        barrier()
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            # every rank must take the same number of regions: the decision uses the maximum
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        per_step.append(ms / steps)
+        total += ms * 1e-3
+    clocks = sampler.stop() if sampler else None
+    return float(np.median(per_step)), float(min(per_step)), len(per_step), clocks
+
+
+def measure_long_context(compute, dev, dist, world: int, rank: int, steps: int = 8):
+    """The long-context configuration as ONE fixed problem split over the ranks (strong scaling): 256
+    sequences, lengths log-uniform in [4096, 131072], Hq 64, Hkv 8, D 128, 38.4 GB of K/V in all.
+    Split by sequence (longest first onto the least loaded rank) and, when the KV heads divide among the
+    ranks, by KV head (every rank holds all sequences and Hkv / ranks heads; perfectly balanced); both are
+    timed with the output gather fused into the decode kernel, and the one the plan predicts faster is
+    the figure.  T(1) / (N T(N)) over runs at N = 1, 2, 4, 8 is the scaling efficiency on the identical problem."""
+    import torch
+    from granite_b200 import sharding, synth
+    cfg = dict(synth.CONFIGS["paged_decode_long_b256"])
+    lens_all = workload_lengths(cfg)
+    B, Hq, Hkv, D = cfg["batch"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    scale = 1.0 / float(np.sqrt(D))
+    pages_all = int(((lens_all.astype(np.int64) + synth.PAGE - 1) // synth.PAGE).sum())
+    total_bytes = int(lens_all.astype(np.int64).sum()) * Hkv * D * 4 + pages_all * 4 + B * 4 + B * Hq * D * 8
+    res = {"workload": "paged_decode_long_b256", "scaling": "strong", "n_gpus": world, "sequences": B,
+           "tokens": int(lens_all.astype(np.int64).sum()), "algorithmic_bytes": total_bytes, "steps_per_region": steps,
+           "predicted_split": sharding.choose_split(lens_all, Hkv, world)}
+
+    def run(split: str):
+        if split == "sequence":
+            plan = sharding.lpt_assign(lens_all, world)
+            mine = plan[rank]
+            case = synth.paged_case(cfg["seed"] + 7919 * rank, len(mine), 0, 0, Hq, Hkv, D, seq_lens=lens_all[mine], device=dev)
+            rows = sharding.padded_rows(plan)
+            n_q, n_kv, q0, gshape = Hq, Hkv, 0, (world * rows, Hq, D)
+            row0, extra = rank * rows, {"lpt_imbalance": sharding.imbalance(lens_all, plan)}
+        else:
+            kv0, n_kv, q0, n_q = sharding.head_split(Hq, Hkv, world)[rank]
+            # every rank: all sequences, the same seeded tables, its own heads' K/V and queries
+            case = synth.paged_case(cfg["seed"], B, 0, 0, n_q, n_kv, D, seq_lens=lens_all, device=dev)
+            rows, gshape, row0, extra = B, (B, Hq, D), 0, {"kv_heads_per_gpu": n_kv}
+        nb = case.batch
+        tables = torch.from_numpy(case.tables).to(dev)
+        lens = torch.from_numpy(case.seq_lens).to(dev)
+        outs = [torch.zeros((rows, n_q, D), device=dev) for _ in range(2)]
+        g = Gather(dist, dev, world, gshape)
+
+        def step(i):
+            kw = {}
+            if g.peer_ptrs is not None:
+                kw = dict(gather_ptrs=g.peer_ptrs[i & 1], gather_row_offset=row0)
+                if split == "kv_head":
+                    kw.update(gather_num_heads=Hq, gather_head_offset=q0)
+            compute.batched_paged_attention_decode(case.q, case.k_pool, case.v_pool, tables, lens, outs[i & 1], nb, n_q,
+                                                   n_kv, D, synth.PAGE, case.max_blocks, scale, num_blocks=case.num_blocks, **kw)
+            if world > 1 and g.peer_ptrs is None:
+                dist.all_gather_into_tensor(g.bufs[i & 1].view(world, -1), outs[i & 1].view(1, -1), async_op=True).wait()
+
+        for i in range(3):
+            step(i)
+        med, best, regions, _ = timed_regions(dev, dist, world, step, steps, min_regions=5, min_total_s=0.25, max_regions=12)
+        ok = None
+        if world > 1 and g.peer_ptrs is not None:
+            last = (steps - 1) & 1
+            parts = torch.empty((world,) + tuple(outs[last].shape), device=dev)
+            dist.all_gather_into_tensor(parts.view(world, -1), outs[last].view(1, -1))
+            expect = parts.view(world * rows, Hq, D) if split == "sequence" else \
+                parts.permute(1, 0, 2, 3).reshape(B, Hq, D)
+            ok = bool(torch.equal(expect, g.bufs[last]))
+        out = {"ms_per_step": med, "ms_per_step_best": best, "regions": regions, "gbs": total_bytes / med / 1e6,
+               "gather": g.mode, **({"gather_verified": ok} if ok is not None else {}), **extra,
+               "kv_bytes_this_gpu": int(case.total_tokens) * n_kv * D * 4}
+        del case, tables, lens, outs, g
+        torch.cuda.empty_cache()
+        return out
+
+    res["by_sequence"] = run("sequence")
+    if world > 1 and sharding.head_split(Hq, Hkv, world) is not None:
+        res["by_kv_head"] = run("kv_head")
+    chosen = "by_kv_head" if res["predicted_split"] == "kv_head" and "by_kv_head" in res else "by_sequence"
+    res["split"] = chosen
+    res["ms_per_step"] = res[chosen]["ms_per_step"]
+    res["value"] = res[chosen]["gbs"]
+    res["unit"] = UNIT
+    hbm, _ = measured_peaks()
+    res["hbm_frac_of_measured_peak"] = res["value"] / world / hbm
+    return res
 
 
 SECONDARY = {"single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
@@ -522,6 +844,7 @@ def main():
         case = synth.paged_case(cfg["seed"] + 7919 * rank, cfg["batch"], 0, 0, cfg["num_heads"],
                                 cfg["num_kv_heads"], cfg["head_dim"], seq_lens=lens, device=dev)
     B, Hq, Hkv, D = case.batch, case.num_heads, case.num_kv_heads, case.head_dim
+    tokens_local = case.total_tokens
     scale = 1.0 / float(np.sqrt(D))
     stream = torch.cuda.current_stream()
     compute = g.CudaCompute(dev.index, stream.cuda_stream)
@@ -533,34 +856,15 @@ def main():
     tables_d = tables_h.to(dev)
     lens_d = lens_h.to(dev)
     q_d = case.q
-    outs = [torch.zeros((B, Hq, D), device=dev) for _ in range(2)]
     rows = B
     if strong and world > 1:
         rows = sharding.padded_rows(plan)  # ranks own different numbers of sequences
-        outs = [torch.zeros((rows, Hq, D), device=dev) for _ in range(2)]
+    outs = [torch.zeros((rows, Hq, D), device=dev) for _ in range(2)]
     # Output gather across the ranks: the decode kernel itself stores every final row into every rank's
     # gathered buffer (peer-mapped symmetric memory, plain stores over NVLink) - no extra launch.  NCCL's
     # all-gather is the fall-back where symmetric memory cannot be set up, and the verifier.
-    gathered, peer_ptrs, gather_mode = None, None, "none"
-    if world > 1:
-        try:
-            import torch.distributed._symmetric_memory as symm
-            gathered = [symm.empty((world * rows, Hq, D), dtype=torch.float32, device=dev) for _ in range(2)]
-            for t in gathered:
-                t.zero_()  # padding rows (ranks own different numbers of sequences) compare equal
-            handles = [symm.rendezvous(t, dist.group.WORLD) for t in gathered]
-            peer_ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
-            gather_mode = "rows stored to every rank by the decode kernel (peer stores over NVLink, symmetric memory)"
-        except Exception as exc:  # noqa: BLE001 - any failure means: use the collective library
-            print(f"[bench] symmetric memory unavailable ({exc!r}); gathering with NCCL", file=sys.stderr)
-            gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
-            peer_ptrs = None
-            gather_mode = "NCCL all-gather per step"
-        flags = torch.tensor([1 if peer_ptrs else 0], device=dev)
-        dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same route
-        if int(flags.item()) == 0 and peer_ptrs is not None:
-            gathered = [torch.empty((world * rows, Hq, D), device=dev) for _ in range(2)]
-            peer_ptrs, gather_mode = None, "NCCL all-gather per step"
+    gat = Gather(dist, dev, world, (world * rows, Hq, D))
+    gathered, peer_ptrs, gather_mode = gat.bufs, gat.peer_ptrs, gat.mode
 
     def decode(q, tables, lens, out, gather_ptrs=None):
         compute.batched_paged_attention_decode(q, case.k_pool, case.v_pool, tables, lens, out, B, Hq, Hkv,
@@ -568,66 +872,49 @@ def main():
                                                num_blocks=case.num_blocks, gather_ptrs=gather_ptrs,
                                                gather_row_offset=rank * rows)
 
-    def step(i):
+    def step_with(q, tables, lens, i):
         out = outs[i & 1]
         if world > 1 and peer_ptrs is not None:
-            decode(q_d, tables_d, lens_d, out, peer_ptrs[i & 1])
+            decode(q, tables, lens, out, peer_ptrs[i & 1])
         else:
-            decode(q_d, tables_d, lens_d, out)
+            decode(q, tables, lens, out)
             if world > 1:
                 # the gather is ordered after this step's kernels and before the next step's: a
                 # persistent one-CTA-per-SM decode kernel must not share SMs with an NCCL kernel
                 dist.all_gather_into_tensor(gathered[i & 1], out, async_op=True).wait()
+
+    def step(i):
+        step_with(q_d, tables_d, lens_d, i)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- resident-input throughput ("value")
+    # ---- resident-input throughput ("value"): regions of exactly --steps steps, each bracketed by a barrier
+    # and a synchronize, repeated until they cover half a second; the median region is the figure
     for i in range(args.warmup):
         step(i)
     barrier()
     compute.enable_kernel_timing(True)
     compute.reset_kernel_timing()
-    sampler = ClockSampler(dev.index)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    sampler.start()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    barrier()
-    clocks = sampler.stop()
+    ms_per_step, ms_best, regions, clocks = timed_regions(dev, dist, world, step, args.steps, clock_index=dev.index)
     compute.sync()
-    ms_total = e0.elapsed_time(e1)
+    kstats = compute.get_kernel_timing_stats()
+    compute.enable_kernel_timing(False)
     # the same steps without the output gather (max over ranks), to show what the gather costs
     ms_no_gather = None
     if world > 1:
-        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        ea.record(stream)
-        for i in range(args.steps):
-            decode(q_d, tables_d, lens_d, outs[i & 1])
-        eb.record(stream)
-        barrier()
-        t = torch.tensor([ea.elapsed_time(eb) / args.steps], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_no_gather = float(t.item())
+        ms_no_gather, _, _, _ = timed_regions(dev, dist, world, lambda i: decode(q_d, tables_d, lens_d, outs[i & 1]),
+                                              args.steps, min_regions=3, min_total_s=0.1)
     gather_ok = None
     if world > 1 and peer_ptrs is not None:
         # outside the timed region: what the peers stored here must be what NCCL would have gathered
-        last = (args.steps - 1) & 1
-        expect = torch.empty_like(gathered[last])
-        dist.all_gather_into_tensor(expect, outs[last])
-        gather_ok = bool(torch.equal(expect, gathered[last]))
-    kstats = compute.get_kernel_timing_stats()
-    compute.enable_kernel_timing(False)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        step(0)
+        barrier()
+        expect = torch.empty_like(gathered[0])
+        dist.all_gather_into_tensor(expect, outs[0])
+        gather_ok = bool(torch.equal(expect, gathered[0]))
     local_bytes = case.algorithmic_bytes()
     if world > 1:
         tb = torch.tensor([local_bytes], device=dev, dtype=torch.float64)
@@ -635,12 +922,9 @@ def main():
         total_bytes = float(tb.item())
     else:
         total_bytes = float(local_bytes)
-    ms_per_step = ms_total / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end through the C ABI with host buffers
-    e2e_steps = max(3, min(args.steps, 200))
-
+    # ---- end to end through the C ABI with host buffers (the gather to the other ranks included)
     # the step's inputs travel as one pinned staging block [Q | block tables | lengths] and one copy
     q_bytes, t_bytes, l_bytes = q_h.numel() * 4, tables_h.numel() * 4, lens_h.numel() * 4
     pad = lambda n: (n + 255) // 256 * 256  # noqa: E731
@@ -654,25 +938,16 @@ def main():
     tables_e = stage_d[o_t:o_t + t_bytes].view(torch.int32).view(B, -1)
     lens_e = stage_d[o_l:o_l + l_bytes].view(torch.int32)
 
-    def e2e_step():
+    def e2e_step(i):
         compute.write_buffer(stage_d, stage_h, stage_h.numel())
-        decode(q_e, tables_e, lens_e, outs[0])
-        compute.read_buffer(out_h, outs[0], out_h.numel() * 4)
+        step_with(q_e, tables_e, lens_e, i)
+        compute.read_buffer(out_h, outs[i & 1], out_h.numel() * 4)
         compute.sync()
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    for i in range(3):
+        e2e_step(i)
+    e2e_steps = max(3, min(args.steps, 200))
+    e2e_ms, e2e_best, e2e_regions, _ = timed_regions(dev, dist, world, e2e_step, e2e_steps)
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
     h2d = stage_h.numel()
     d2h = out_h.numel() * 4
@@ -685,7 +960,7 @@ def main():
     roofline = {
         "bound": "hbm", "kernel": "paged_decode_splitkv", "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
-        "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": local_bytes,
+        "kernel_ms": kernel_ms, "launches_timed": main_n, "algorithmic_bytes_per_launch": local_bytes,
         "traffic": int(local_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE),
         "other_kernels_ms": {k: v[0] / max(v[1], 1) for k, v in kstats.items() if k != "paged_decode_splitkv"},
     }
@@ -693,20 +968,31 @@ def main():
     # ---- CPU baseline (rank 0, N = 1 only): bounded sample
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not strong:
-        from oracle import pyoracle
-        sel = list(range(0, cfg["batch"], 2))  # about 10 s of CPU work on 16 cores
+        ckind, ref = cpu_arm()
+        sel = list(range(0, cfg["batch"], 4))  # about 10-20 s of CPU work
         hc = host_case_for_cpu(cfg["seed"], cfg, sel)
-        gbs, secs, nb, nseq = cpu_baseline_sample(hc, 1, repeats=2)
-        cpu = {"value": gbs, "unit": UNIT, "cores": pyoracle.num_threads(), "kind": "port",
-               "sample": f"every 2nd sequence ({nseq} of {cfg['batch']}, {int(hc['seq_lens'].sum())} tokens), "
-                         f"best of 2, {secs:.2f} s each"}
+        nb, secs, loop_secs, nseq = cpu_decode_sample(hc, ref, repeats=1)
+        cpu = {"value": nb / secs / 1e9, "unit": UNIT, "cores": cpu_threads(ref), "kind": ckind,
+               "value_loop_only": nb / loop_secs / 1e9,
+               "sample": f"every 4th sequence ({nseq} of {cfg['batch']}, {int(hc['seq_lens'].sum())} tokens), {secs:.2f} s",
+               "note": "value: the reference's serial whole-cache fp16->fp32 widening (transformer.mm:1753-1765) + the attention "
+                       "loop on all host threads, as its CPU path runs each call; value_loop_only: the loop alone on K/V "
+                       "already widened"}
 
     secondary = None
-    if world == 1 and not strong and args.sequences == 0 and not args.no_secondary:
-        secondary = {"prefill": measure_prefill(compute, dev), "tree_verify": measure_tree(compute, dev),
-                     "decode_step_cache_write": measure_decode_step_write(compute, dev),
-                     "paged_prefill": measure_paged_prefill(compute, dev),
-                     "single_sequence_decode": measure_single_decode(compute, dev)}
+    if not strong and args.sequences == 0 and not args.no_secondary:
+        secondary = {}
+        if world == 1:
+            with_cpu = not args.no_cpu_baseline
+            secondary = {"prefill": measure_prefill(compute, dev, with_cpu=with_cpu),
+                         "tree_verify": measure_tree(compute, dev, with_cpu=with_cpu),
+                         "decode_step_cache_write": measure_decode_step_write(compute, dev),
+                         "paged_prefill": measure_paged_prefill(compute, dev),
+                         "single_sequence_decode": measure_single_decode(compute, dev)}
+        # the headline workload's buffers are released first: the long-context problem holds 38.4 GB on one GPU
+        del case, outs, gat, gathered, stage_d, q_d, q_e, tables_e, lens_e
+        torch.cuda.empty_cache()
+        secondary["long_context_b256"] = measure_long_context(compute, dev, dist, world, rank)
 
     if rank == 0:
         line = {
@@ -714,20 +1000,24 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+            "timing": {"regions": regions, "steps_per_region": args.steps, "ms_per_step_median": ms_per_step,
+                       "ms_per_step_best": ms_best,
+                       "rule": "regions of exactly --steps steps, each between a barrier + synchronize, repeated until they "
+                               "cover 0.5 s; ms_per_step is the median region, maximum over ranks"},
             "config": {"workload": args.workload + (f" (head_dim {D} variant)" if D != synth.CONFIGS[args.workload]["head_dim"] else ""),
                        "sequences_per_gpu": B,
                        "context": f"{cfg['dist']}[{cfg['len_lo']},{cfg['len_hi']}]",
                        "page": synth.PAGE, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
-                       "tokens_per_gpu": case.total_tokens, "kv_bytes_per_gpu": case.total_tokens * Hkv * D * 4,
-                       "l2": f"inputs larger than L2 ({case.total_tokens * Hkv * D * 4 / 1e9:.1f} GB of K/V per GPU per step, no reuse)",
+                       "tokens_per_gpu": tokens_local, "kv_bytes_per_gpu": tokens_local * Hkv * D * 4,
+                       "l2": f"inputs larger than L2 ({tokens_local * Hkv * D * 4 / 1e9:.1f} GB of K/V per GPU per step, no reuse)",
                        "sharding": f"by sequence; output gather: {gather_mode}" if world > 1 else "single GPU",
                        **({"gather_verified": gather_ok} if gather_ok is not None else {}),
                        **({"ms_per_step_without_gather": ms_no_gather} if ms_no_gather is not None else {})},
             "hbm_frac_of_measured_peak": value / n_gpus / peak,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms, "ms_per_step_best": e2e_best, "steps": e2e_steps, "regions": e2e_regions,
                     "note": "host Q, block tables and lengths copied in (one pinned staging block), output copied out, sync per step; "
-                            "K/V pages are cache state resident in HBM"},
+                            "K/V pages are cache state resident in HBM" + ("; the rows also go to every other rank (fused gather)" if world > 1 else "")},
             # per rank and step: decode_plan + paged_decode_splitkv (which also stores the rows to the other ranks)
             "gpu_launches": 2 * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,

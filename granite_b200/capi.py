@@ -173,6 +173,8 @@ _sig("granite_cuda_memset", C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t
 _sig("granite_cuda_batched_paged_attention_decode", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs))
 _sig("granite_cuda_batched_paged_attention_decode_gather", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs),
      C.POINTER(C.c_void_p), C.c_uint32, C.c_uint64)
+_sig("granite_cuda_batched_paged_attention_decode_gather_heads", C.c_int, C.c_void_p, C.POINTER(PagedDecodeArgs),
+     C.POINTER(C.c_void_p), C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32)
 _sig("granite_cuda_multihead_attention", C.c_int, C.c_void_p, C.POINTER(AttentionArgs))
 _sig("granite_cuda_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(KvAppendArgs))
 _sig("granite_cuda_paged_kv_cache_append", C.c_int, C.c_void_p, C.POINTER(PagedKvAppendArgs))
@@ -294,7 +296,8 @@ class CudaCompute:
     def batched_paged_attention_decode(self, Q, K_cache, V_cache, block_tables, seq_lens, output,
                                        batch_size, num_heads, num_kv_heads, head_dim, block_size,
                                        max_blocks_per_seq, scale, *, num_blocks, seq_len=0,
-                                       gather_ptrs=None, gather_row_offset=0) -> None:
+                                       gather_ptrs=None, gather_row_offset=0, gather_num_heads=0,
+                                       gather_head_offset=0) -> None:
         a = PagedDecodeArgs(_ptr(Q), _ptr(K_cache), _ptr(V_cache), _ptr(block_tables), _ptr(seq_lens),
                             _ptr(output), batch_size, num_heads, num_kv_heads, head_dim, block_size,
                             max_blocks_per_seq, num_blocks, seq_len, scale)
@@ -302,6 +305,13 @@ class CudaCompute:
             # gather_ptrs: device addresses of [total sequences, num_heads, head_dim] fp32 buffers (this GPU's
             # or peer-mapped ones); every final row is also stored to row gather_row_offset + b of each
             arr = (C.c_void_p * len(gather_ptrs))(*[int(x) for x in gather_ptrs])
+            if gather_num_heads:
+                # KV heads sharded across GPUs: a destination row holds gather_num_heads query heads and this
+                # call's num_heads of them start at gather_head_offset
+                check(lib.granite_cuda_batched_paged_attention_decode_gather_heads(
+                    self._h, C.byref(a), arr, len(gather_ptrs), int(gather_row_offset), int(gather_num_heads),
+                    int(gather_head_offset)))
+                return
             check(lib.granite_cuda_batched_paged_attention_decode_gather(self._h, C.byref(a), arr, len(gather_ptrs),
                                                                          int(gather_row_offset)))
             return

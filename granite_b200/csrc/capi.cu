@@ -353,6 +353,15 @@ int granite_cuda_batched_paged_attention_decode_gather(granite_cuda_compute_t* c
     return launch_paged_decode(c, *args, false, 0, &g);
 }
 
+int granite_cuda_batched_paged_attention_decode_gather_heads(granite_cuda_compute_t* c, const GraniteCudaPagedDecodeArgs* args,
+                                                             void* const* dst_ptrs, uint32_t n_dst, uint64_t dst_row_offset,
+                                                             uint32_t dst_num_heads, uint32_t dst_head_offset) {
+    if (!c || !args) return fail(GRANITE_CUDA_NULL_POINTER, "paged decode: null argument");
+    GB_CUDA_TRY(cudaSetDevice(c->device));
+    const DecodeGather g{dst_ptrs, n_dst, dst_row_offset, dst_num_heads, dst_head_offset};
+    return launch_paged_decode(c, *args, false, 0, &g);
+}
+
 int granite_cuda_multihead_attention(granite_cuda_compute_t* c, const GraniteCudaAttentionArgs* a) {
     if (!c || !a) return fail(GRANITE_CUDA_NULL_POINTER, "multihead_attention: null argument");
     GB_CUDA_TRY(cudaSetDevice(c->device));

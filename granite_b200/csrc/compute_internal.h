@@ -130,6 +130,8 @@ struct DecodeGather {
     void* const* dst;
     uint32_t n_dst;
     uint64_t row_offset;
+    uint32_t dst_heads = 0;    // query heads per destination row; 0: this call's num_heads
+    uint32_t head_offset = 0;  // first destination head of this call's heads
 };
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a, bool contiguous,
                         uint32_t max_seq, const DecodeGather* gather = nullptr);

@@ -126,6 +126,14 @@ Result<void> CudaCompute::batched_paged_attention_decode_gather(const GraniteCud
     return cuda_result(granite_cuda_batched_paged_attention_decode_gather(h_, &args, gather_dst, n_dst, gather_row_offset));
 }
 
+Result<void> CudaCompute::batched_paged_attention_decode_gather_heads(const GraniteCudaPagedDecodeArgs& args,
+                                                                      void* const* gather_dst, uint32_t n_dst,
+                                                                      uint64_t gather_row_offset, uint32_t dst_num_heads,
+                                                                      uint32_t dst_head_offset) {
+    return cuda_result(granite_cuda_batched_paged_attention_decode_gather_heads(h_, &args, gather_dst, n_dst, gather_row_offset,
+                                                                                dst_num_heads, dst_head_offset));
+}
+
 Result<void> CudaCompute::rope_multihead(float* q, float* k, uint32_t num_heads_q, uint32_t num_heads_k,
                                          uint32_t seq_len, uint32_t head_dim, uint32_t start_pos,
                                          const float* cos_table, const float* sin_table, uint32_t table_len) {

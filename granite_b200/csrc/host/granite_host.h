@@ -276,6 +276,11 @@ public:
     // upstream (one GPU).
     Result<void> batched_paged_attention_decode_gather(const GraniteCudaPagedDecodeArgs& args, void* const* gather_dst,
                                                        uint32_t n_dst, uint64_t gather_row_offset);
+    // Several GPUs, KV heads sharded (every rank holds all sequences, num_kv_heads / ranks heads): args describes
+    // the local head slice; a destination row holds dst_num_heads query heads, this call's start at dst_head_offset.
+    Result<void> batched_paged_attention_decode_gather_heads(const GraniteCudaPagedDecodeArgs& args, void* const* gather_dst,
+                                                             uint32_t n_dst, uint64_t gather_row_offset,
+                                                             uint32_t dst_num_heads, uint32_t dst_head_offset);
     // The step before attention and the ones after verification (the "next" tier of the path):
     // RoPE with host-built tables, RoPE fused with the paged cache write, the tree commit copy and
     // chunked prefill over the paged cache.  Argument meaning as in granite_cuda.h.

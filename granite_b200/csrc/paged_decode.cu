@@ -60,11 +60,19 @@ struct DecodeParams {
     int* pages_done;      // [batch][n_head_tiles][consumer warps]: pages of cut sequences finished so far
     int fused_merge;      // 1: the warp that finishes a cut sequence merges it; 0: decode_merge_kernel follows
     // optional gather: every final output row is also stored into these buffers (other GPUs' peer-mapped
-    // memory or this GPU's own), at row gather_row0 + sequence
+    // memory or this GPU's own), at row gather_row0 + sequence.  A destination row holds gather_heads
+    // query heads (num_heads, or more when the heads are sharded across GPUs) and this call's heads
+    // start at gather_head0 of it.
     float* gather[kMaxGatherDst];
     int n_gather;
     long long gather_row0;
+    int gather_heads, gather_head0;
 };
+
+// Element offset of (sequence b, local query head hq) in a gather destination.
+__device__ __forceinline__ size_t gather_offset(const DecodeParams& p, int b, int hq) {
+    return ((size_t)(p.gather_row0 + b) * p.gather_heads + p.gather_head0 + hq) * p.d;
+}
 
 // Final output element(s) of (sequence b, query head hq): the local row and every gather destination.
 // Plain stores: nothing waits for the peers; visibility to a consumer on another GPU is the caller's
@@ -72,12 +80,12 @@ struct DecodeParams {
 __device__ __forceinline__ void store_out(const DecodeParams& p, int b, int hq, int idx, float v) {
     p.out[((size_t)b * p.num_heads + hq) * p.d + idx] = v;
     for (int r = 0; r < p.n_gather; r++)
-        p.gather[r][((size_t)(p.gather_row0 + b) * p.num_heads + hq) * p.d + idx] = v;
+        p.gather[r][gather_offset(p, b, hq) + idx] = v;
 }
 __device__ __forceinline__ void store_out4(const DecodeParams& p, int b, int hq, int idx, float4 v) {
     *reinterpret_cast<float4*>(p.out + ((size_t)b * p.num_heads + hq) * p.d + idx) = v;
     for (int r = 0; r < p.n_gather; r++)
-        *reinterpret_cast<float4*>(p.gather[r] + ((size_t)(p.gather_row0 + b) * p.num_heads + hq) * p.d + idx) = v;
+        *reinterpret_cast<float4*>(p.gather[r] + gather_offset(p, b, hq) + idx) = v;
 }
 
 __device__ __forceinline__ long long range_start(long long total, int n_ctas, int c) {
@@ -659,7 +667,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 const size_t row = ((size_t)seg.seq * p.num_heads + hq0 + h) * D + lane * 4;
                 const float4 v = __ldcg(reinterpret_cast<const float4*>(p.out + row));
                 for (int r = 0; r < p.n_gather; r++)
-                    *reinterpret_cast<float4*>(p.gather[r] + (size_t)p.gather_row0 * p.num_heads * D + row) = v;
+                    *reinterpret_cast<float4*>(p.gather[r] + gather_offset(p, seg.seq, hq0 + h) + lane * 4) = v;
             }
         }
         if (seg.slot >= 0 && p.fused_merge) {
@@ -800,6 +808,8 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         if (!gather->dst) return fail(GRANITE_CUDA_NULL_POINTER, "decode gather: null destination list");
         if (gather->n_dst > (uint32_t)kMaxGatherDst)
             return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode gather: at most 16 destinations");
+        if (gather->dst_heads != 0 && (uint64_t)gather->head_offset + a.num_heads > gather->dst_heads)
+            return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode gather: head_offset + num_heads exceeds the destination's heads");
         for (uint32_t r = 0; r < gather->n_dst; r++) {
             if (!gather->dst[r]) return fail(GRANITE_CUDA_NULL_POINTER, "decode gather: null destination");
             if (reinterpret_cast<uintptr_t>(gather->dst[r]) & 15)
@@ -815,6 +825,9 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: num_heads must be a multiple of num_kv_heads");
     // the plain kernel does not store to gather destinations itself: its rows are pushed afterwards
     auto plain = [&]() {
+        if (gather && gather->dst_heads != 0 && gather->dst_heads != a.num_heads)
+            return fail(GRANITE_CUDA_INVALID_ARGUMENT,
+                        "decode gather: a head-sharded destination needs head_dim 128 or 64, 16-token pages and 1, 2, 4 or 8k KV heads");
         int rc = launch_generic_decode(c, a, contiguous, max_seq);
         if (rc == GRANITE_CUDA_SUCCESS && gather) {
             const uint64_t row_bytes = (uint64_t)a.num_heads * a.head_dim * 4;
@@ -871,6 +884,8 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     if (gather) {
         p.n_gather = (int)gather->n_dst;
         p.gather_row0 = (long long)gather->row_offset;
+        p.gather_heads = gather->dst_heads ? (int)gather->dst_heads : p.num_heads;
+        p.gather_head0 = (int)gather->head_offset;
         for (uint32_t r = 0; r < gather->n_dst; r++) p.gather[r] = static_cast<float*>(gather->dst[r]);
     }
 

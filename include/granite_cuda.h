@@ -146,6 +146,22 @@ int granite_cuda_batched_paged_attention_decode_gather(granite_cuda_compute_t* c
                                                        void* const* dst_ptrs, uint32_t n_dst,
                                                        uint64_t dst_row_offset);
 
+/* The fused gather for KV-head sharding.  When every GPU holds ALL sequences but only a slice of the KV
+ * heads (pool shard [num_blocks * block_size, num_kv_heads / ranks, head_dim], block tables replicated -
+ * they index tokens, not heads), args describes the local slice (num_heads and num_kv_heads are the
+ * local counts) and a destination row holds dst_num_heads query heads, of which this call writes heads
+ * [dst_head_offset, dst_head_offset + args->num_heads): element (b, h, d) goes to
+ * dst + (((dst_row_offset + b) * dst_num_heads + dst_head_offset + h) * head_dim + d).
+ * dst_num_heads == 0 means args->num_heads (the by-sequence form above).  Needs the shapes of the
+ * tuned decode kernel (head_dim 128 or 64, 16-token pages, 1, 2, 4 or 8k local KV heads).
+ * No reference counterpart; the addressing rule inside the pool shard is the reference's
+ * (include/granite/metal_compute.h:853-861) with the local head count. */
+int granite_cuda_batched_paged_attention_decode_gather_heads(granite_cuda_compute_t* c,
+                                                             const GraniteCudaPagedDecodeArgs* args,
+                                                             void* const* dst_ptrs, uint32_t n_dst,
+                                                             uint64_t dst_row_offset, uint32_t dst_num_heads,
+                                                             uint32_t dst_head_offset);
+
 /* Allocation-free batched paged decode.  This entry point has no counterpart in the reference.
  * It exists for hosts that cannot let a plug-in allocate device memory: a serving process whose
  * own arena already owns the GPU's memory, or a latency-critical loop that cannot afford the

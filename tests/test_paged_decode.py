@@ -126,6 +126,64 @@ def test_decode_with_fused_gather(compute, name, lens, d):
         assert torch.isnan(g[:offset]).all() and torch.isnan(g[offset + case.batch:]).all(), name
 
 
+@pytest.mark.parametrize("ranks,hq,hkv", [(2, 32, 8), (4, 32, 8), (8, 64, 8), (2, 16, 16)])
+def test_decode_sharded_by_kv_head(compute, ranks, hq, hkv):
+    """Every GPU holds all sequences and num_kv_heads / ranks heads: pool shard [rows, Hkv / ranks, D], the same
+    block tables, its groups' query heads.  The ranks run here one after the other on one GPU, each storing its
+    head slice into the gathered [B, Hq, D] buffer through the fused gather; the assembled rows must match the
+    CPU checker on the unsharded problem and - bit for bit - the unsharded decode when each rank's tile still
+    holds whole KV heads."""
+    import torch
+    from granite_b200 import sharding
+    dev = "cuda:0"
+    rng = np.random.default_rng(ranks)
+    lens = rng.integers(0, 900, size=41).astype(np.int32)
+    lens[7] = 6000
+    lens[3] = 0
+    case = synth.paged_case(seed=51, batch=len(lens), len_lo=0, len_hi=0, num_heads=hq, num_kv_heads=hkv, seq_lens=lens)
+    d = case.head_dim
+    tables = torch.from_numpy(case.tables).to(dev)
+    seq_lens = torch.from_numpy(case.seq_lens).to(dev)
+    gathered = torch.full((case.batch + 5, hq, d), float("nan"), device=dev)
+    split = sharding.head_split(hq, hkv, ranks)
+    assert split is not None and len(split) == ranks
+    for r, (kv0, n_kv, q0, n_q) in enumerate(split):
+        k = torch.from_numpy(sharding.shard_pool_by_head(case.k_pool, r, ranks)).to(dev)
+        v = torch.from_numpy(sharding.shard_pool_by_head(case.v_pool, r, ranks)).to(dev)
+        q = torch.from_numpy(sharding.shard_queries_by_head(case.q, r, ranks)).to(dev)
+        assert k.shape[1] == n_kv and q.shape[1] == n_q and q0 == r * n_q
+        local = torch.full((case.batch, n_q, d), float("nan"), device=dev)
+        compute.batched_paged_attention_decode(q, k, v, tables, seq_lens, local, case.batch, n_q, n_kv, d, synth.PAGE,
+                                               case.max_blocks, 1.0 / np.sqrt(d), num_blocks=case.num_blocks,
+                                               gather_ptrs=[gathered.data_ptr()], gather_row_offset=2,
+                                               gather_num_heads=hq, gather_head_offset=q0)
+        compute.sync()
+        assert torch.equal(gathered[2:2 + case.batch, q0:q0 + n_q], local)
+    ref = _oracle(case, case.k_pool.view(np.uint16), case.v_pool.view(np.uint16))
+    got = gathered[2:2 + case.batch].cpu().numpy()
+    assert_attention_close(got, ref, f"{ranks} ranks by KV head")
+    assert torch.isnan(gathered[:2]).all() and torch.isnan(gathered[2 + case.batch:]).all()
+
+
+def test_head_sharded_gather_is_refused_outside_the_tuned_shapes(compute):
+    import torch
+    import granite_b200 as g
+    dev = "cuda:0"
+    case = synth.paged_case(seed=52, batch=2, len_lo=10, len_hi=50, num_heads=6, num_kv_heads=3)
+    out = torch.zeros((2, 6, 128), device=dev)
+    gathered = torch.zeros((2, 12, 128), device=dev)
+    args = [torch.from_numpy(x).to(dev) for x in (case.q, case.k_pool, case.v_pool, case.tables, case.seq_lens)]
+    with pytest.raises(g.GraniteCudaError) as ei:
+        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 128, synth.PAGE, case.max_blocks, 0.1,
+                                               num_blocks=case.num_blocks, gather_ptrs=[gathered.data_ptr()],
+                                               gather_num_heads=12, gather_head_offset=6)
+    assert ei.value.code == g.ErrorCode.InvalidArgument
+    with pytest.raises(g.GraniteCudaError):  # the slice would run past the destination row
+        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 128, synth.PAGE, case.max_blocks, 0.1,
+                                               num_blocks=case.num_blocks, gather_ptrs=[gathered.data_ptr()],
+                                               gather_num_heads=8, gather_head_offset=4)
+
+
 def test_single_sequence_paged_decode(compute):
     import torch
     case = synth.paged_case(seed=13, batch=1, len_lo=0, len_hi=0, seq_lens=np.array([777], np.int32))
