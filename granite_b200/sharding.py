@@ -86,9 +86,10 @@ def unshard_heads(gathered: np.ndarray) -> np.ndarray:
 
 
 # Throughput of the decode kernel with this many KV heads per page box, relative to eight (32 KB
-# boxes): fewer heads per rank mean smaller TMA boxes per page.  Measured on B200 with the
-# 256-sequence long-context batch (bench.py, secondary.long_context_b256).
-HEADS_PER_BOX_EFFICIENCY = {8: 1.0, 4: 1.0, 2: 1.0, 1: 1.0}
+# boxes).  A page of fewer heads is a smaller piece of HBM per step of every consumer warp's
+# wait - load - multiply - softmax chain, and the warps of one head all read the same page.  Measured on
+# B200 on the long-context lengths, 4.8 GB of K/V per call: 6.62, 6.13, 3.88 and 2.07 TB/s.
+HEADS_PER_BOX_EFFICIENCY = {8: 1.0, 4: 0.925, 2: 0.586, 1: 0.313}
 
 
 def predicted_cost(lengths, num_kv_heads: int, n_ranks: int, split: str) -> float:

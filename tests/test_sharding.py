@@ -41,7 +41,11 @@ def test_head_split_and_choice_of_split():
     assert sharding.choose_split(skewed, 8, 8) == "kv_head"
     assert sharding.choose_split(skewed, 8, 3) == "sequence"   # heads do not divide
     assert sharding.choose_split(skewed, 8, 1) == "sequence"
-    assert sharding.predicted_cost(skewed, 8, 8, "kv_head") == sum(skewed)
+    assert sharding.predicted_cost(skewed, 8, 8, "kv_head") == sum(skewed) / sharding.HEADS_PER_BOX_EFFICIENCY[1]
+    # balanced batches keep whole KV heads together: the decode kernel is slower on one-head pages
+    cfg = synth.CONFIGS["paged_decode_long_b256"]
+    lens = synth.draw_lengths(np.random.default_rng(cfg["seed"]), cfg["batch"], cfg["len_lo"], cfg["len_hi"], cfg["dist"])
+    assert sharding.choose_split(lens, 8, 8) == "sequence"
     assert sharding.predicted_cost(skewed, 8, 8, "sequence") == 100000 * 8 / sharding.HEADS_PER_BOX_EFFICIENCY[8]
 
 
