@@ -71,14 +71,6 @@ struct TcParams {
     int slot_shift;             // tree: a tile is (128 >> slot_shift) query heads x (1 << slot_shift) node slots
 };
 
-struct TcSmem {
-    uint64_t q_full, q_empty, k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages];
-    uint64_t s_full[2], s_free[2], p_ready[2], o_final;
-    uint32_t tmem_base;
-    int abort_flag;
-};
-static_assert(sizeof(TcSmem) <= 3072, "the barriers must fit beside seven 32 KB tiles");
-
 struct TcItem {
     int head0;      // first query head of the item
     int kvh;
@@ -90,6 +82,18 @@ struct TcItem {
     int cache_len;  // tree: prefix length
     bool valid;
 };
+
+constexpr int kMaxCachedItems = 32;  // work items of a CTA kept in shared memory (later rounds are derived on the fly)
+
+struct TcSmem {
+    uint64_t q_full, q_empty, k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages];
+    uint64_t s_full[2], s_free[2], p_ready[2], o_final;
+    uint32_t tmem_base;
+    int abort_flag;
+    TcItem items[kMaxCachedItems];  // item of round r, worked out once at start-up instead of by every role at every item boundary
+};
+static_assert(sizeof(TcSmem) <= 3072, "the barriers must fit beside seven 32 KB tiles");
+
 
 // fp32 -> fp16 hi + fp16 lo (x ~= hi + lo to about 22 bits), so fp32 queries lose nothing.
 __global__ void split_f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ hi,
@@ -169,7 +173,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
     const int n_items = kTree ? p.batch * p.num_kv_heads * p.units_per_kvh
                               : p.n_qblocks * p.batch * p.num_kv_heads * p.units_per_kvh;
     const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    auto item_of = [&](int r) {
+    auto derive_item = [&](int r) {
         TcItem it;
         const int pos = r * (int)gridDim.x + ((r & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
         it.valid = pos < n_items;
@@ -184,7 +188,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             int len = p.cache_lens ? p.cache_lens[it.b] : p.cache_len;
             const int cap = kPaged ? p.max_blocks * kPageRows : p.cache_stride;
             if (len < 0 || len > cap) {
-                if (threadIdx.x == 0) atomicOr(p.status, kStatusBadSeqLen);
+                atomicOr(p.status, kStatusBadSeqLen);
                 len = 0;
             }
             it.cache_len = len;
@@ -207,6 +211,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         return it;
     };
 
+    // threads 32.. work out the items of the first rounds (thread 0 is busy with the barriers)
+    if (threadIdx.x >= 32 && (int)threadIdx.x - 32 < min(n_rounds, kMaxCachedItems))
+        sh->items[threadIdx.x - 32] = derive_item((int)threadIdx.x - 32);
+    auto item_of = [&](int r) { return r < kMaxCachedItems ? sh->items[r] : derive_item(r); };
     if (threadIdx.x == 0) {
         mbar_init(&sh->q_full, 1);
         mbar_init(&sh->q_empty, 1);
@@ -499,6 +507,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             const int h = p.d_chunks - e.halves_left;
             if (h == 0) {
                 if (ok) ok = mbar_wait(&sh->o_final, e.phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tcgen05.ld below needs the whole warp
                 tc_fence_after_sync();
             }
             e.halves_left--;
@@ -592,6 +601,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     const uint32_t s_frag = frag_base + b * kT;
                     const uint32_t o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
                     if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);  // warp-uniform: everything below is warp-wide
                     if (!ok) continue;  // a role gave up: nothing below synchronises with another warp
                     tc_fence_after_sync();
                     // the two rows' scores: x[h][4i + 2q + e] = row q, column 64 h + 8 i + 2 tq + e
@@ -643,7 +653,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         const bool grow0 = mx[0] > m_used[0] + kLazyLog2, grow1 = mx[1] > m_used[1] + kLazyLog2;
                         if (__any_sync(0xffffffffu, grow0 || grow1)) {
                             // O_t must be quiescent: wait until both halves of its previous output MMA are done
-                            ok = mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag);
+                            ok = __all_sync(0xffffffffu, mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag));
                             tc_fence_after_sync();
                             const float alpha0 = grow0 ? fast_exp2(m_used[0] - mx[0]) : 1.0f;
                             const float alpha1 = grow1 ? fast_exp2(m_used[1] - mx[1]) : 1.0f;
@@ -704,7 +714,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         // keys past the live length carry P = 0, but their V rows may hold anything (even
                         // NaN): zero them in shared memory before the MMAs read the tile
                         const int st = kvs % kStages;
-                        ok = mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag);
+                        ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag));
                         const int first_bad = (kTree ? it.cache_len : p.seq_kv) - k0;
                         uint8_t* vt = v_smem + st * kTileBytes;
                         const int row_units = 8 * p.d_chunks;  // 16-byte units per V row
@@ -740,7 +750,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     float l = l_run_t[t][q];
                     l += __shfl_xor_sync(0xffffffffu, l, 1);
                     l += __shfl_xor_sync(0xffffffffu, l, 2);
-                    e.inv[q] = 1.0f / l;
+                    e.inv[q] = __frcp_rn(l);
                     if (kTree) {
                         const int node = row_of[q] & ((1 << p.slot_shift) - 1);
                         const int head = it.head0 + (kT >> p.slot_shift) * t + (row_of[q] >> p.slot_shift);

@@ -488,7 +488,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int i = 0; i < 4; i++) sa[pp][nt][i] = sb[pp][nt][i] = 0.f;
                 kbase[pp] = smem_base + slot_k[pp] * slot_bytes + k_row * 128;
-                if (has[pp] && !mbar_wait(&full[slot_k[pp]], ph_k[pp], abort_flag)) {
+                // the verdict is made warp-uniform: a lane that gave up must not leave the others to the
+                // warp-wide ldmatrix / shuffles that follow
+                if (has[pp] && !__all_sync(0xffffffffu, mbar_wait(&full[slot_k[pp]], ph_k[pp], abort_flag))) {
                     if (lane == 0) atomicOr(p.status, kStatusTimeout);
                     return;
                 }
@@ -581,7 +583,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             for (int pp = 0; pp < PP; pp++) {
                 vbase[pp] = smem_base + slot_v[pp] * slot_bytes + v_row * 128;
                 if (!has[pp]) continue;
-                if (!mbar_wait(&full[slot_v[pp]], ph_v[pp], abort_flag)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[slot_v[pp]], ph_v[pp], abort_flag))) {
                     if (lane == 0) atomicOr(p.status, kStatusTimeout);
                     return;
                 }
