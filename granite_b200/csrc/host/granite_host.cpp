@@ -14,6 +14,7 @@ Error cuda_error(int code) {
     return Error(static_cast<ErrorCode>(code), granite_cuda_last_error_message());
 }
 
+#ifndef GRANITE_WITH_REFERENCE_HEADERS  // upstream, backend.h provides this default inline
 Result<BufferHandle> IComputeBackend::create_buffer_from_host(const void* data, const BufferDesc& desc) {
     if (!data) return Error(ErrorCode::InvalidArgument, "Null host buffer");
     auto b = create_buffer(desc);
@@ -25,6 +26,7 @@ Result<BufferHandle> IComputeBackend::create_buffer_from_host(const void* data, 
     }
     return b;
 }
+#endif
 
 // =================================================================== CudaCompute
 CudaCompute::~CudaCompute() { shutdown(); }
@@ -207,7 +209,7 @@ Result<void> RoPECache::upload(granite_cuda_compute_t* compute) {
 
 Result<void> RoPECache::apply(Tensor& q, Tensor& k, int start_pos, IComputeBackend* backend) {
     if (!is_initialized()) return Error(ErrorCode::InvalidState, "RoPE cache not initialized");
-    if (!backend || backend->get_type() != BackendType::CUDA)
+    if (!backend || backend->get_type() != kCudaBackendType)
         return Error(ErrorCode::BackendNotSupported, "RoPECache::apply needs the CUDA backend (no CPU fallback)");
     const int seq_len = static_cast<int>(q.size(1));
     const int num_heads_q = static_cast<int>(q.size(2)), num_heads_k = static_cast<int>(k.size(2));
@@ -269,7 +271,7 @@ public:
         caps.supports_simd_groups = true;
         return caps;
     }
-    BackendType get_type() const override { return BackendType::CUDA; }
+    BackendType get_type() const override { return kCudaBackendType; }
 
     Result<BufferHandle> create_buffer(const BufferDesc& desc) override {
         if (!is_initialized()) return Error(ErrorCode::BackendNotInitialized, "CUDA backend not initialized");
@@ -423,6 +425,7 @@ private:
 
 std::unique_ptr<IComputeBackend> create_cuda_backend(int device) { return std::make_unique<CudaBackend>(device); }
 
+#ifndef GRANITE_WITH_REFERENCE_HEADERS  // upstream: src/core/tensor.cpp and src/core/operator_registry.cpp
 // =================================================================== Tensor
 size_t Tensor::numel() const {
     if (shape_.empty()) return 0;
@@ -475,6 +478,7 @@ std::unique_ptr<IOperator> OperatorRegistry::create(OpType op, BackendType backe
 bool OperatorRegistry::has_implementation(OpType op, BackendType backend) const {
     return factories_.count(op_key(op, backend)) != 0;
 }
+#endif
 
 namespace {
 
@@ -493,13 +497,14 @@ public:
     }
     Result<std::vector<std::vector<int64_t>>> infer_shapes(const OpContext& ctx) const override {
         if (ctx.num_inputs() < 1) return Error(ErrorCode::InvalidArgument, "Attention requires 3 inputs (Q, K, V)");
-        return std::vector<std::vector<int64_t>>{ctx.inputs[0].shape()};
+        const auto q_shape = ctx.inputs[0].shape();  // a vector here, a span over it upstream (tensor.h:45)
+        return std::vector<std::vector<int64_t>>{std::vector<int64_t>(q_shape.begin(), q_shape.end())};
     }
     Result<void> execute(OpContext& ctx) override {
         auto ok = validate(ctx);
         if (!ok.ok()) return ok;
         if (ctx.num_outputs() < 1) return Error(ErrorCode::InvalidArgument, "Attention requires an output tensor");
-        if (!ctx.backend || ctx.backend->get_type() != BackendType::CUDA)
+        if (!ctx.backend || ctx.backend->get_type() != kCudaBackendType)
             return Error(ErrorCode::OperatorNotImplemented, "CudaAttentionOp needs the CUDA backend (no CPU fallback)");
         const Tensor &Q = ctx.inputs[0], &K = ctx.inputs[1], &V = ctx.inputs[2];
         Tensor& out = ctx.outputs[0];
@@ -537,7 +542,7 @@ public:
 }  // namespace
 
 void register_cuda_operators() {
-    OperatorRegistry::instance().register_op(OpType::ScaledDotProductAttention, BackendType::CUDA,
+    OperatorRegistry::instance().register_op(OpType::ScaledDotProductAttention, kCudaBackendType,
                                              [] { return std::make_unique<CudaAttentionOp>(); });
 }
 

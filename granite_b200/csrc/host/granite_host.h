@@ -24,6 +24,22 @@
 
 #include "../../../include/granite_cuda.h"
 
+// Built inside Granite's tree (or against its headers: -DGRANITE_WITH_REFERENCE_HEADERS with
+// include/ of the checkout on the include path) the vocabulary below IS Granite's: every class
+// of this file then derives from the real interfaces with `override`, Tensor / Error /
+// OperatorRegistry are Granite's own objects, and only the enumerator for this backend is missing
+// upstream (a maintainer adds `CUDA` to BackendType, include/granite/types.h:93-98; until then the
+// next free value is used).  Built alone, the restatement below stands in for those headers.
+#ifdef GRANITE_WITH_REFERENCE_HEADERS
+#include "granite/backend.h"
+#include "granite/error.h"
+#include "granite/operators.h"
+#include "granite/tensor.h"
+#include "granite/types.h"
+namespace granite {
+inline constexpr BackendType kCudaBackendType = static_cast<BackendType>(static_cast<uint8_t>(BackendType::Talos) + 1);
+}
+#else
 namespace granite {
 
 // ------------------------------------------------------------------ errors (error.h:16-226)
@@ -69,13 +85,6 @@ public:
 private:
     std::shared_ptr<Error> e_;
 };
-
-// Error of the last failing C-ABI call, as a Granite error value.
-Error cuda_error(int code);
-inline Result<void> cuda_result(int code) {
-    if (code == 0) return {};
-    return cuda_error(code);
-}
 
 // ------------------------------------------------------------------ types (types.h:20-169)
 enum class DataType : uint8_t { FP32, FP16, INT32, INT64, UINT8 };
@@ -153,9 +162,6 @@ public:
     virtual void destroy_fence(FenceHandle fence) = 0;
 };
 
-// Factory, wired like the out-of-tree Talos backend (src/core/backend_factory.cpp:29-31,62-68).
-std::unique_ptr<IComputeBackend> create_cuda_backend(int device = 0);
-
 // ------------------------------------------------------------------ tensor (tensor.h:19-178)
 // Non-owning view: the buffer lives until destroy_buffer or backend shutdown.
 class Tensor {
@@ -224,6 +230,22 @@ public:
 private:
     std::unordered_map<uint64_t, OperatorFactory> factories_;
 };
+inline constexpr BackendType kCudaBackendType = BackendType::CUDA;
+}  // namespace granite
+#endif
+
+namespace granite {
+
+// Error of the last failing C-ABI call, as a Granite error value.
+Error cuda_error(int code);
+inline Result<void> cuda_result(int code) {
+    if (code == 0) return {};
+    return cuda_error(code);
+}
+
+// Factory, wired like the out-of-tree Talos backend (src/core/backend_factory.cpp:29-31,62-68).
+std::unique_ptr<IComputeBackend> create_cuda_backend(int device = 0);
+
 void register_cuda_operators();
 
 // ------------------------------------------------------------------ compute class

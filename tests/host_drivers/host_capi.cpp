@@ -2,8 +2,11 @@
 // language can exercise them the way Granite's own Catch2 tests exercise its backends:
 // the operator registry flow of tests/test_vulkan.cpp:353-482, page-manager scripts, the
 // speculation tree, the contiguous KVCache and an end-to-end paged decode through
-// PagedKVPool + CudaCompute.  These are test drivers, not part of the drop-in boundary.
+// PagedKVPool + CudaCompute.  TEST CODE: built into its own library beside the tests
+// (tests/host_drivers/build.py), never into the product library.
+#include <cmath>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "granite_host.h"
@@ -94,7 +97,7 @@ int granite_host_backend_selftest(int device) {
     auto be = create_cuda_backend(device);
     auto init = be->initialize();
     if (!init.ok()) return host_fail(init.error());
-    if (be->get_type() != BackendType::CUDA || !be->is_initialized()) return 1001;
+    if (be->get_type() != kCudaBackendType || !be->is_initialized()) return 1001;
     std::vector<uint8_t> pattern(4096), back(4096, 0);
     for (size_t i = 0; i < pattern.size(); i++) pattern[i] = static_cast<uint8_t>(i * 7 + 3);
     for (MemoryType mt : {MemoryType::Device, MemoryType::Managed, MemoryType::Shared}) {
@@ -154,7 +157,7 @@ int granite_host_operator_attention(int device, int dtype, const void* q, const 
         std::memcpy(m.value(), srcs[i], ts[i].size_bytes());
         be->unmap_buffer(ts[i].buffer());
     }
-    auto op = OperatorRegistry::instance().create(OpType::ScaledDotProductAttention, BackendType::CUDA);
+    auto op = OperatorRegistry::instance().create(OpType::ScaledDotProductAttention, kCudaBackendType);
     if (!op) return 2004;
     OpContext ctx;
     ctx.backend = be.get();
@@ -375,8 +378,9 @@ int granite_host_rope_apply(int device, float* q, float* k, int seq_len, int num
     Tensor none_q, none_k;
     if (rope.apply(none_q, none_k, 0, be.get()).ok()) return 5001;  // not initialized yet: InvalidState
     rope.initialize(max_seq, head_dim, theta);
-    auto qt = Tensor::allocate({1, seq_len, num_heads_q, head_dim}, DataType::FP32, be.get());
-    auto kt = Tensor::allocate({1, seq_len, num_heads_k, head_dim}, DataType::FP32, be.get());
+    const std::vector<int64_t> q_shape = {1, seq_len, num_heads_q, head_dim}, k_shape = {1, seq_len, num_heads_k, head_dim};
+    auto qt = Tensor::allocate(q_shape, DataType::FP32, be.get());
+    auto kt = Tensor::allocate(k_shape, DataType::FP32, be.get());
     if (!qt.ok() || !kt.ok()) return 5002;
     Tensor tq = std::move(qt).take(), tk = std::move(kt).take();
     if (!be->write_buffer(tq.buffer(), q, tq.size_bytes()).ok()) return 5003;

@@ -77,3 +77,14 @@ def test_ctypes_structures_match_the_header(tmp_path):
         assert int(out[cname]) == ctypes.sizeof(cls), cname
         for fname, _ in cls._fields_:
             assert int(out[f"{cname}.{fname}"]) == getattr(cls, fname).offset, f"{cname}.{fname}"
+
+
+def test_product_library_carries_no_test_drivers():
+    """The extern "C" drivers of the C++ host faces are test code: they live in their own library beside the
+    tests, and the product library exports none of them."""
+    import subprocess
+    import granite_b200 as g
+    from granite_b200 import capi
+    names = subprocess.run(["nm", "-D", "--defined-only", str(capi.library_path())], capture_output=True, text=True).stdout
+    assert "granite_cuda_compute_create" in names
+    assert "granite_host_" not in names

@@ -15,9 +15,14 @@ _u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 
 
-def _lib():
-    import granite_b200 as g
-    lib = g.lib
+@pytest.fixture(scope="module", params=["standin", "reference_headers"])
+def host_lib(request):
+    """The test drivers of the C++ host faces: over the product library's classes, and - where it was
+    built from the Granite checkout - the same class bodies compiled against Granite's real headers."""
+    from host_drivers import build as drivers
+    if request.param == "reference_headers" and not drivers.dropin_available():
+        pytest.skip("oracle/_ref/libgranite_dropin.so not built (needs the Granite checkout)")
+    lib = drivers.load(request.param)
     lib.granite_host_last_error.restype = C.c_char_p
     lib.granite_host_backend_selftest.argtypes = [C.c_int]
     lib.granite_host_operator_attention.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -33,15 +38,15 @@ def _lib():
     return lib
 
 
-def test_backend_buffer_semantics():
-    lib = _lib()
+def test_backend_buffer_semantics(host_lib):
+    lib = host_lib
     rc = lib.granite_host_backend_selftest(0)
     assert rc == 0, (rc, lib.granite_host_last_error())
 
 
-def test_operator_known_answer_2x3x4():
+def test_operator_known_answer_2x3x4(host_lib):
     """The reference's one attention test (tests/test_vulkan.cpp:353-482), same flow, CUDA backend."""
-    lib = _lib()
+    lib = host_lib
     g = np.load(GOLD / "kat_sdpa_2x3x4.npz")
     q, kt, v = (np.ascontiguousarray(g[k], np.float32) for k in ("q", "kt", "v"))
     out = np.zeros_like(q)
@@ -53,11 +58,11 @@ def test_operator_known_answer_2x3x4():
 
 @pytest.mark.parametrize("dtype,sq,skv,d,start_pos", [(0, 7, 33, 16, 0), (0, 50, 300, 128, 0), (1, 5, 9, 64, 0),
                                                       (1, 6, 40, 32, 11)])
-def test_operator_layouts(dtype, sq, skv, d, start_pos):
+def test_operator_layouts(host_lib, dtype, sq, skv, d, start_pos):
     """fp32: K pre-transposed, no mask (Vulkan contract); fp16: K row-major with the causal limit
     q + start_pos + 1 (Metal contract); default scale 1/sqrt(D)."""
     from oracle import pyoracle
-    lib = _lib()
+    lib = host_lib
     rng = np.random.default_rng(sq * 100 + skv)
     q = rng.standard_normal((sq, d), np.float32)
     k = rng.standard_normal((skv, d), np.float32)
@@ -81,9 +86,9 @@ def test_operator_layouts(dtype, sq, skv, d, start_pos):
     assert_attention_close(got, ref, f"operator dtype={dtype}")
 
 
-def test_kvcache_append_layout_matches_reference():
+def test_kvcache_append_layout_matches_reference(host_lib):
     """Device KVCache against the bytes the reference KVCache produced (src/llm/kv_cache.cpp:52-107)."""
-    lib = _lib()
+    lib = host_lib
     g = np.load(GOLD / "ref_kvcache_append.npz")
     hkv, d, max_seq = (int(x) for x in g["shape"])
     steps = np.ascontiguousarray(g["steps"], np.int32)
@@ -100,13 +105,13 @@ def test_kvcache_append_layout_matches_reference():
 
 
 @pytest.mark.parametrize("lens,hq,hkv,step", [([40, 7, 129, 16], 32, 8, 24), ([300], 8, 2, 300), ([5, 5, 5], 16, 4, 1)])
-def test_page_manager_in_hbm_end_to_end(lens, hq, hkv, step):
+def test_page_manager_in_hbm_end_to_end(host_lib, lens, hq, hkv, step):
     """PagedKVPool on the CUDA backend: ragged growth through BlockManager, fp32 K/V appended into
     the HBM pool by paged_kv_cache_append, tables mirrored to the device, one batched decode.
     Checks: every row read back through the block table is bit-identical to the reference's
     truncating fp32->fp16 of what was appended; the decode output matches the CPU attention."""
     from oracle import pyoracle
-    lib = _lib()
+    lib = host_lib
     d, bs = 128, 16
     lens_a = np.array(lens, np.int32)
     batch = len(lens)
@@ -203,9 +208,9 @@ def test_batched_paged_append_then_decode(compute):
     assert_attention_close(out.cpu().numpy(), ref, "append + decode")
 
 
-def test_rope_cache_apply_through_backend_tensors():
+def test_rope_cache_apply_through_backend_tensors(host_lib):
     """RoPECache::apply (src/llm/rope.cpp:24-92) on CUDA-backend tensors against the reference's outputs."""
-    lib = _lib()
+    lib = host_lib
     g = np.load(GOLD / "ref_rope.npz")
     for i in range(2):
         seq, hq, hk, d, start, max_seq = (int(x) for x in g[f"a{i}_cfg"])
@@ -223,11 +228,11 @@ def test_rope_cache_apply_through_backend_tensors():
 
 @pytest.mark.parametrize("lens0,n_steps,remove_slot,remove_at", [([5, 0, 31, 16, 100], 40, 2, 7), ([300] * 3, 20, -1, 0),
                                                                 ([1], 33, -1, 0)])
-def test_batched_decode_loop_replays_on_the_cpu_checker(lens0, n_steps, remove_slot, remove_at):
+def test_batched_decode_loop_replays_on_the_cpu_checker(host_lib, lens0, n_steps, remove_slot, remove_at):
     """PagedKVPool + RoPECache + PagedDecodeBatch over several decode steps, one request leaving on
     the way: every step's rotated queries and cache bytes bit-exact, every output within tolerance."""
     from oracle import pyoracle
-    lib = _lib()
+    lib = host_lib
     batch, hq, hkv, d, bs = len(lens0), 32, 8, 128, 16
     max_seq = 512
     max_blocks = max_seq // bs
@@ -290,11 +295,11 @@ def test_batched_decode_loop_replays_on_the_cpu_checker(lens0, n_steps, remove_s
     assert np.array_equal(k_pool[live], ck[live]) and np.array_equal(v_pool[live], cv[live])
 
 
-def test_device_block_table_follows_a_table_that_shrank_and_regrew():
+def test_device_block_table_follows_a_table_that_shrank_and_regrew(host_lib):
     """A sequence truncated across a block boundary (as after a tree commit) whose freed block went to
     another request and which then regrew over a different block: the device row must not keep the
     freed block's number."""
-    lib = _lib()
+    lib = host_lib
     bs, max_blocks = 16, 6
     dev_rows = np.full((2, max_blocks), -7, np.int32)
     host_rows = np.full((2, max_blocks), -7, np.int32)

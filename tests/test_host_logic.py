@@ -5,15 +5,21 @@ import ctypes as C
 from pathlib import Path
 
 import numpy as np
+import pytest
 
 GOLD = Path(__file__).resolve().parent / "golden"
 _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 
 
-def _lib():
-    import granite_b200 as g
-    lib = g.lib
+@pytest.fixture(scope="module", params=["standin", "reference_headers"])
+def host_lib(request):
+    """The test drivers of the C++ host faces: over the product library's classes, and - where it was
+    built from the Granite checkout - the same class bodies compiled against Granite's real headers."""
+    from host_drivers import build as drivers
+    if request.param == "reference_headers" and not drivers.dropin_available():
+        pytest.skip("oracle/_ref/libgranite_dropin.so not built (needs the Granite checkout)")
+    lib = drivers.load(request.param)
     lib.granite_host_paged_pool_script.restype = C.c_int
     lib.granite_host_paged_pool_script.argtypes = [C.c_int, C.c_int, C.c_int, _i32p, C.c_int, _i32p, _i32p, _i32p,
                                                    _i32p, C.c_int, _i32p, _i32p]
@@ -37,8 +43,8 @@ def _run_script(lib, ms, mt, bs, ops, mb):
     return res, seq_lens, tlens, tables, int(nfree[0]), int(ntot[0])
 
 
-def test_page_manager_replays_reference_scripts_bit_for_bit():
-    lib = _lib()
+def test_page_manager_replays_reference_scripts_bit_for_bit(host_lib):
+    lib = host_lib
     g = np.load(GOLD / "ref_paged_pool.npz")
     for i in range(3):
         ms, mt, bs, mb = (int(x) for x in g[f"cfg{i}"])
@@ -50,11 +56,11 @@ def test_page_manager_replays_reference_scripts_bit_for_bit():
         assert [nfree, ntot] == list(g[f"free{i}"])
 
 
-def test_block_manager_invariants():
+def test_block_manager_invariants(host_lib):
     """LIFO free list: first blocks handed out are the highest indices; exhaustion returns -1 and
     keeps what was taken; truncate frees tail blocks; double / out-of-range frees are ignored
     (src/llm/paged_kv_cache.cpp:73-98, :120-145, :169-187)."""
-    lib = _lib()
+    lib = host_lib
     ops = [(0, 0, 0),            # acquire slot 0
            (1, 0, 33),           # 33 tokens -> 3 blocks: 7, 6, 5
            (6, 0, 0), (6, 0, 16), (6, 0, 32), (7, 0, 35), (6, 0, 48),
@@ -74,8 +80,8 @@ def test_block_manager_invariants():
     assert tables[0, 0] == 7 and nfree == 7
 
 
-def test_speculation_tree_matches_reference():
-    lib = _lib()
+def test_speculation_tree_matches_reference(host_lib):
+    lib = host_lib
     g = np.load(GOLD / "ref_spec_tree.npz")
     for i in range(4):
         parents = np.ascontiguousarray(g[f"parents{i}"], np.int32)
@@ -96,10 +102,10 @@ def test_speculation_tree_matches_reference():
         assert np.array_equal(out[: int(n_out[0])], g[f"ap_path{i}"])
 
 
-def test_accepted_nodes_are_the_nodes_behind_the_reference_path():
+def test_accepted_nodes_are_the_nodes_behind_the_reference_path(host_lib):
     """find_accepted_nodes must name the nodes whose tokens open the reference's accepted path: the
     path is those tokens, optionally closed by the target's own choice at the first mismatch."""
-    lib = _lib()
+    lib = host_lib
     g = np.load(GOLD / "ref_spec_tree.npz")
     for i in range(6):
         parents = np.ascontiguousarray(g[f"ap_parents{i}"], np.int32)
@@ -117,8 +123,8 @@ def test_accepted_nodes_are_the_nodes_behind_the_reference_path():
             assert path[-1] == targets[len(nodes)]
 
 
-def test_rope_tables_of_the_host_mirror_match_reference():
-    lib = _lib()
+def test_rope_tables_of_the_host_mirror_match_reference(host_lib):
+    lib = host_lib
     g = np.load(GOLD / "ref_rope.npz")
     for i in range(3):
         max_seq, d = (int(x) for x in g[f"t{i}_cfg"])
