@@ -623,6 +623,76 @@ def measure_tree16(compute, dev, reps: int = 200):
     return measure_tree(compute, dev, reps, nodes=16, with_cpu=False)
 
 
+def measure_generic(compute, dev, reps: int = 50):
+    """What the plain fp32 kernel (shapes outside the tuned kernels' tiling) costs against the tuned kernels on
+    the nearest tuned shape, and the operator-form kernel on a mid-sized tensor.  Side measurement."""
+    import ctypes as C
+    import torch
+    import granite_b200 as g
+    from granite_b200 import synth
+    out = {}
+    # decode: 16 sequences, lengths uniform [1024, 8192], Hq 32, Hkv 8: head_dim 128 (tuned) against 96 (plain)
+    for d in (128, 96):
+        case = synth.paged_case(3003, 16, 1024, 8192, 32, 8, d, device=dev)
+        tables = torch.from_numpy(case.tables).to(dev)
+        lens = torch.from_numpy(case.seq_lens).to(dev)
+        o = torch.zeros((16, 32, d), device=dev)
+
+        def step(i):
+            compute.batched_paged_attention_decode(case.q, case.k_pool, case.v_pool, tables, lens, o, 16, 32, 8, d, synth.PAGE,
+                                                   case.max_blocks, 1.0 / float(np.sqrt(d)), num_blocks=case.num_blocks)
+        for i in range(3):
+            step(i)
+        compute.sync()
+        ms = region_ms_per_launch(dev, step, reps)
+        out[f"decode_head_dim_{d}"] = {"ms": ms, "gbs": case.algorithmic_bytes() / ms / 1e6,
+                                       "kernel": "paged_decode_splitkv" if d == 128 else "generic_attention"}
+    out["decode_slowdown_of_plain_kernel"] = out["decode_head_dim_128"]["gbs"] / out["decode_head_dim_96"]["gbs"]
+    # prefill: 1024 tokens, Hq 8, Hkv 2, fp16 in/out
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    for d in (128, 96):
+        seq, hq, hkv = 1024, 8, 2
+        q = torch.randn((seq, hq, d), device=dev, generator=gen).half()
+        k = torch.randn((hkv, seq, d), device=dev, generator=gen).half()
+        v = torch.randn((hkv, seq, d), device=dev, generator=gen).half()
+        o = torch.zeros((seq, hq, d), device=dev, dtype=torch.float16)
+
+        def step(i):
+            compute.multihead_attention(q, k, v, o, hq, hkv, seq, seq, d, 1.0 / float(np.sqrt(d)), seq, q_dtype=1, out_dtype=1)
+        for i in range(3):
+            step(i)
+        compute.sync()
+        ms = region_ms_per_launch(dev, step, reps)
+        flops = 4 * d * hq * seq * (seq + 1) // 2
+        out[f"prefill_head_dim_{d}"] = {"ms": ms, "tflops": flops / ms / 1e9,
+                                        "kernel": "prefill_causal_fa" if d == 128 else "generic_attention"}
+    out["prefill_slowdown_of_plain_kernel"] = out["prefill_head_dim_128"]["tflops"] / out["prefill_head_dim_96"]["tflops"]
+    # operator form (one head): fp16 [T, D] layout with the causal limit, 256 queries over 4096 keys, D 128
+    from granite_b200 import capi
+
+    class SdpaArgs(C.Structure):
+        _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("output", C.c_void_p), ("seq_q", C.c_uint32),
+                    ("seq_kv", C.c_uint32), ("head_dim", C.c_uint32), ("dtype", C.c_uint32), ("k_transposed", C.c_uint32),
+                    ("causal", C.c_uint32), ("start_pos", C.c_uint32), ("scale", C.c_float)]
+    sq, skv, d = 256, 4096, 128
+    q = torch.randn((sq, d), device=dev, generator=gen).half()
+    k = torch.randn((skv, d), device=dev, generator=gen).half()
+    v = torch.randn((skv, d), device=dev, generator=gen).half()
+    o = torch.zeros((sq, d), device=dev, dtype=torch.float16)
+    a = SdpaArgs(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), sq, skv, d, 1, 0, 1, skv - sq, 1.0 / float(np.sqrt(d)))
+    g.lib.granite_cuda_sdpa.argtypes = [C.c_void_p, C.POINTER(SdpaArgs)]
+
+    def step(i):
+        capi.check(g.lib.granite_cuda_sdpa(compute.handle, C.byref(a)))
+    for i in range(3):
+        step(i)
+    compute.sync()
+    ms = region_ms_per_launch(dev, step, reps)
+    out["sdpa_operator_256x4096x128"] = {"ms": ms, "tflops": 4 * d * sq * skv / ms / 1e9, "kernel": "sdpa_operator"}
+    return out
+
+
 class Gather:
     """Buffers every rank's output rows are gathered into: symmetric memory whose peer addresses the
     decode kernel stores to directly, or - where that cannot be set up on every rank - plain buffers
@@ -771,7 +841,7 @@ def measure_long_context(compute, dev, dist, world: int, rank: int, steps: int =
     return res
 
 
-SECONDARY = {"single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
+SECONDARY = {"generic": measure_generic, "single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
              "paged_prefill": measure_paged_prefill}
 
 
@@ -785,7 +855,7 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
-    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "tree16", "step_write", "paged_prefill", "single_decode"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "tree16", "step_write", "paged_prefill", "single_decode", "generic"],
                     help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (profiling captures)")
     ap.add_argument("--head-dim", type=int, default=0, choices=[0, 64, 128],

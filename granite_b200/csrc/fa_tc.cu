@@ -211,9 +211,11 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         return it;
     };
 
-    // threads 32.. work out the items of the first rounds (thread 0 is busy with the barriers)
-    if (threadIdx.x >= 32 && (int)threadIdx.x - 32 < min(n_rounds, kMaxCachedItems))
-        sh->items[threadIdx.x - 32] = derive_item((int)threadIdx.x - 32);
+    // Warp 0 sets everything up that the loads need - the barriers (lane 0) and the items of the first
+    // rounds (one per lane) - and then goes straight on as the producer: it only ARRIVES at the start-up
+    // barrier, so the first query and K/V tiles are already in flight while warp 1 allocates tensor memory.
+    static_assert(kMaxCachedItems == 32, "one item per lane of warp 0");
+    if (warp == 0 && lane < min(n_rounds, kMaxCachedItems)) sh->items[lane] = derive_item(lane);
     auto item_of = [&](int r) { return r < kMaxCachedItems ? sh->items[r] : derive_item(r); };
     if (threadIdx.x == 0) {
         mbar_init(&sh->q_full, 1);
@@ -238,9 +240,14 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         tmem_relinquish();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("bar.arrive 1, %0;" ::"r"(kTcThreads) : "memory");
+    } else {
+        asm volatile("bar.sync 1, %0;" ::"r"(kTcThreads) : "memory");
+    }
     tc_fence_after_sync();
-    const uint32_t tmem = sh->tmem_base;
+    const uint32_t tmem = warp == 0 ? 0u : sh->tmem_base;  // the producer never touches tensor memory
 
     if (warp < 4) {
         setmaxnreg_dec<56>();  // producer / MMA warpgroup gives registers up

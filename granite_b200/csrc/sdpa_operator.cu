@@ -73,6 +73,28 @@ int launch_sdpa_operator(granite_cuda_compute* c, const GraniteCudaSdpaArgs& a) 
     if (!a.q || !a.k || !a.v || !a.output) return fail(GRANITE_CUDA_NULL_POINTER, "sdpa: null buffer");
     if (a.seq_q == 0 || a.seq_kv == 0 || a.head_dim == 0) return fail(GRANITE_CUDA_INVALID_SHAPE, "sdpa: empty shape");
     if (a.dtype > 1) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "sdpa: dtype must be 0 (fp32) or 1 (fp16)");
+    // The Metal operator's layout (fp16, K row-major, keys limited to q + start_pos + 1) with a head_dim the
+    // tensor-core kernel is tiled for IS causal prefill of one head: it runs there, on tcgen05, instead of on
+    // the one-block-per-row kernel below.
+    if (a.dtype == 1 && !a.k_transposed && a.causal && a.seq_q >= 2 && (a.head_dim == 128 || a.head_dim == 64)) {
+        GraniteCudaAttentionArgs p{};
+        p.q = a.q;
+        p.k = a.k;
+        p.v = a.v;
+        p.output = a.output;
+        p.num_heads = 1;
+        p.num_kv_heads = 1;
+        p.seq_q = a.seq_q;
+        p.seq_kv = a.seq_kv;
+        p.head_dim = a.head_dim;
+        p.max_seq = a.seq_kv;
+        p.q_dtype = 1;
+        p.out_dtype = 1;
+        p.scale = a.scale;
+        p.start_pos = a.start_pos;
+        p.batch_size = 1;
+        return launch_prefill(c, p);
+    }
     const size_t smem = (size_t)a.seq_kv * sizeof(float);
     if (smem > 200 * 1024) return fail(GRANITE_CUDA_INVALID_SHAPE, "sdpa operator: seq_kv above 51200 is not supported");
     LaunchScope t(c, "sdpa_operator");

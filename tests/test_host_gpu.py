@@ -57,7 +57,8 @@ def test_operator_known_answer_2x3x4(host_lib):
 
 
 @pytest.mark.parametrize("dtype,sq,skv,d,start_pos", [(0, 7, 33, 16, 0), (0, 50, 300, 128, 0), (1, 5, 9, 64, 0),
-                                                      (1, 6, 40, 32, 11)])
+                                                      (1, 6, 40, 32, 11), (1, 200, 700, 128, 500), (1, 130, 130, 64, 0),
+                                                      (1, 300, 300, 128, 0)])
 def test_operator_layouts(host_lib, dtype, sq, skv, d, start_pos):
     """fp32: K pre-transposed, no mask (Vulkan contract); fp16: K row-major with the causal limit
     q + start_pos + 1 (Metal contract); default scale 1/sqrt(D)."""
