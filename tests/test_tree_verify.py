@@ -154,3 +154,46 @@ def test_full_tree_config_sample(compute):
         vr = case.v_pool[rows].cpu().numpy().astype(np.float32)
         ref = _oracle_one(q[b], kr, vr, kt[b], vt[b], parents[b])
         assert_attention_close(got[b], ref, f"tree config, sequence {b}")
+
+
+@pytest.mark.parametrize("lens,hq,hkv,n,q_fp16", [
+    ([4096] * 4, 32, 8, 64, True),                 # few equal items
+    ([9000, 16, 0, 1300, 2049, 40], 16, 4, 64, True),   # ragged: one long prefix among short and empty ones
+    ([5000, 1200], 8, 2, 33, False),               # fp32 queries (hi + lo tiles)
+    ([1100] * 30, 8, 8, 16, True),                 # many items of nine steps, four heads per tile
+    ([20000], 4, 1, 64, True),                     # one long sequence, one KV head
+])
+def test_long_and_ragged_prefixes(compute, lens, hq, hkv, n, q_fp16):
+    """Few work items with long, ragged or empty paged prefixes; every sequence against the CPU checker, and a
+    second call on the same compute object must pass as well."""
+    import torch
+    from oracle import pyoracle
+    batch = len(lens)
+    q, kt, vt, parents = _tree_inputs(300 + n + batch, batch, n, hq, hkv)
+    if q_fp16:
+        q = q.astype(np.float16).astype(np.float32)
+    case = synth.paged_case(seed=78, batch=batch, len_lo=0, len_hi=0, num_heads=hq, num_kv_heads=hkv,
+                            seq_lens=np.array(lens, np.int32), spare_blocks=2)
+    dev = "cuda:0"
+    k_np, v_np = case.k_pool.view(np.uint16), case.v_pool.view(np.uint16)
+    args = (torch.from_numpy(q.astype(np.float16) if q_fp16 else q).to(dev), torch.from_numpy(case.k_pool).to(dev),
+            torch.from_numpy(case.v_pool).to(dev), torch.from_numpy(kt).to(dev), torch.from_numpy(vt).to(dev),
+            torch.from_numpy(parents).to(dev))
+    tables_d = torch.from_numpy(case.tables).to(dev)
+    lens_d = torch.from_numpy(case.seq_lens).to(dev)
+    outs = []
+    for _ in range(2):
+        out = torch.full((batch, hq, n, D), float("nan"), device=dev)
+        compute.attention_tree(*args, out, hq, hkv, n, 0, D, 1.0 / np.sqrt(D), batch_size=batch, block_tables=tables_d,
+                               cache_lens=lens_d, max_blocks_per_seq=case.max_blocks, num_blocks=case.num_blocks,
+                               q_dtype=int(q_fp16))
+        compute.sync()
+        outs.append(out.cpu().numpy())
+    tables = np.where(case.tables < 0, 0, case.tables)
+    for b, L in enumerate(lens):
+        kr, bad = pyoracle.paged_gather(k_np, tables[b], L, 16)
+        vr, _ = pyoracle.paged_gather(v_np, tables[b], L, 16)
+        assert bad == 0
+        ref = _oracle_one(q[b], pyoracle.f16_bits_to_f32(kr), pyoracle.f16_bits_to_f32(vr), kt[b], vt[b], parents[b])
+        assert_attention_close(outs[0][b], ref, f"sequence {b} of lens {lens}")
+        assert_attention_close(outs[1][b], ref, f"second call, sequence {b} of lens {lens}")
