@@ -31,7 +31,7 @@ constexpr int kHeadDim = 128;  // the benchmarked head size; the decode kernel i
 constexpr int kPageTokens = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxSlots = 32;
+constexpr int kMaxSlots = 64;
 constexpr int kMaxGatherDst = 16;
 
 struct DecodeParams {
@@ -46,6 +46,15 @@ struct DecodeParams {
     int n_head_tiles;     // num_kv_heads / tile_heads
     int heads_per_warp;   // query heads of the group owned by one consumer warp
     int active_warps;     // consumer warps that own at least one query head
+    // Fewer than eight KV heads in the tile (1, 2 or 4): the warps of a head do not split its query heads -
+    // all of them would then read every page - but its PAGES: warp `sub` of a head takes every page_split-th page
+    // for all query heads of the group, and the warps' partial results are combined through shared memory at
+    // the end of each segment.  1: off (every warp walks every page).
+    int page_split;
+    int slot_arrivals;    // warps that release a page slot (active_warps, or tile_heads when pages are split)
+    int dump_offset;      // byte offset of the warps' exchange area behind the barriers
+    int dump_bytes;       // bytes of one warp's dump
+    int per_round;        // pages the producer issues per round (two slots each)
     int slots;            // ring depth
     int n_ctas;
     int contiguous;       // 1: k/v are [batch, Hkv, max_seq, D], table is the identity
@@ -324,12 +333,20 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)p.slots * slot_bytes);
     uint64_t* empty = full + kMaxSlots;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxSlots);
+    // page split: per KV head of the tile, "the other warps have dumped" and "the dumps have been read"
+    uint64_t* dumped = empty + kMaxSlots + 8;
+    uint64_t* drained = dumped + 4;
+    float* dump_area = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(empty + kMaxSlots) + p.dump_offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < p.slots; i++) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], p.active_warps);
+            mbar_init(&empty[i], p.slot_arrivals);
+        }
+        for (int i = 0; i < 4; i++) {
+            mbar_init(&dumped[i], max(p.page_split - 1, 1));
+            mbar_init(&drained[i], 1);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -356,8 +373,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
         }
         // One TMA instruction moves a whole K (or V) page of the head tile: the box spans
         // {64 halfs, 16 rows, the head's 64-wide chunks, tile_heads heads} and lands as
-        // [head][chunk][row][64].  Lane 0 issues K, lane 1 issues V.
-        const CUtensorMap* map = lane == 1 ? &vmap : &kmap;
+        // [head][chunk][row][64].
         while (walk.next(seg)) {
             const int head0 = seg.head_tile * p.tile_heads;
             for (int j0 = 0; j0 < seg.npages; j0 += 32) {
@@ -375,24 +391,38 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     }
                 }
                 const int n = min(32, seg.npages - j0);
-                for (int jj = 0; jj < n; jj++) {
-                    const int entry = __shfl_sync(0xffffffffu, e, jj);
-                    int slot_k = slot; uint32_t ph_k = phase; advance();
-                    int slot_v = slot; uint32_t ph_v = phase; advance();
+                // Several pages per round: lane 2k issues K of the round's k-th page, lane 2k + 1 its V, each after
+                // its own slot has been released, so the boxes of a round are in flight together.  (A round never
+                // uses more than half the ring, so a slot's parity is unambiguous.)
+                const int per_round = p.per_round;
+                for (int jj0 = 0; jj0 < n; jj0 += per_round) {
+                    const int cnt = min(per_round, n - jj0);
+                    const int entry = __shfl_sync(0xffffffffu, e, (jj0 + (lane >> 1)) & 31);
                     int ok = 1;
-                    if (lane < 2) {
-                        const int my_slot = lane ? slot_v : slot_k;
-                        ok = mbar_wait(&empty[my_slot], (lane ? ph_v : ph_k) ^ 1, abort_flag);
+                    if (lane < 2 * cnt) {
+                        int my_slot = slot + lane;
+                        uint32_t my_phase = phase;
+                        if (my_slot >= p.slots) {
+                            my_slot -= p.slots;
+                            my_phase ^= 1;
+                        }
+                        ok = mbar_wait(&empty[my_slot], my_phase ^ 1, abort_flag);
                         if (ok) {
                             mbar_arrive_expect_tx(&full[my_slot], slot_bytes);
                             // contiguous cache: dim 3 runs over (sequence, head); pool: over heads
                             const int w = p.contiguous ? seg.seq * p.num_kv_heads + head0 : head0;
-                            tma_load_4d(smem + (size_t)my_slot * slot_bytes, map, &full[my_slot], 0, entry * kPageTokens, 0, w);
+                            tma_load_4d(smem + (size_t)my_slot * slot_bytes, (lane & 1) ? &vmap : &kmap, &full[my_slot], 0,
+                                        entry * kPageTokens, 0, w);
                         }
                     }
                     if (!__all_sync(0xffffffffu, ok)) {
                         if (lane == 0) atomicOr(p.status, kStatusTimeout);
                         return;
+                    }
+                    slot += 2 * cnt;
+                    if (slot >= p.slots) {
+                        slot -= p.slots;
+                        phase ^= 1;
                     }
                 }
             }
@@ -403,9 +433,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     // ---------------------------------------------------------------- consumer warps
     const int kvh_local = warp % p.tile_heads;
     const int sub = warp / p.tile_heads;
-    const int first_q = sub * p.heads_per_warp;  // first query head of the group owned here
+    const bool split = p.page_split > 1;
+    const int first_q = split ? 0 : sub * p.heads_per_warp;  // first query head of the group owned here
     if (first_q >= p.group) return;              // idle warp (not counted in active_warps)
     const int n_q = min(p.heads_per_warp, p.group - first_q);
+    int segments_done = 0;                       // page split: parity of the exchange barriers
     const int g = lane >> 2, t = lane & 3;
 
     // per-lane shared-memory offsets of the ldmatrix rows
@@ -477,6 +509,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     slot_v[pp] = slot; ph_v[pp] = phase; advance();
                 }
             }
+            if (split && (j / PP) % p.page_split != sub) continue;  // another warp of this head takes these pages
 
             // ---- S^T = K Q^T
             float sa[PP][NT][4], sb[PP][NT][4];
@@ -625,6 +658,65 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             }
         }
 
+        if (split) {
+            // ---- the warps of this head combine their shares of the segment's pages.  Every lane's state
+            // (running maxima, partial sums, accumulator fragment) is dumped as it stands - all warps hold the same
+            // fragment layout - and warp 0 of the head folds the dumps into its own, lane by lane.
+            constexpr int kPerLane = NT * (kDSteps * 4 + 4);
+            const uint32_t par = segments_done & 1;
+            segments_done++;
+            if (sub > 0) {
+                // the previous segment's dumps must have been read before they are overwritten
+                if (!__all_sync(0xffffffffu, mbar_wait(&drained[kvh_local], par ^ 1, abort_flag))) {
+                    if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                    return;
+                }
+                float* d = dump_area + ((size_t)(kvh_local * (p.page_split - 1) + (sub - 1)) * kPerLane) * 32 + lane;
+                int k = 0;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    d[32 * k++] = m_run[nt][0];
+                    d[32 * k++] = m_run[nt][1];
+                    d[32 * k++] = l_run[nt][0];
+                    d[32 * k++] = l_run[nt][1];
+#pragma unroll
+                    for (int mt = 0; mt < kDSteps; mt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) d[32 * k++] = o[nt][mt][i];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&dumped[kvh_local]);
+                continue;  // the result is warp 0's business
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&dumped[kvh_local], par, abort_flag))) {
+                if (lane == 0) atomicOr(p.status, kStatusTimeout);
+                return;
+            }
+            for (int w = 0; w < p.page_split - 1; w++) {
+                const float* d = dump_area + ((size_t)(kvh_local * (p.page_split - 1) + w) * kPerLane) * 32 + lane;
+                int k = 0;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const float m0 = d[32 * k++], m1 = d[32 * k++], l0 = d[32 * k++], l1 = d[32 * k++];
+                    const float mn0 = fmaxf(m_run[nt][0], m0), mn1 = fmaxf(m_run[nt][1], m1);
+                    const float a0 = fast_exp2(m_run[nt][0] - mn0), a1 = fast_exp2(m_run[nt][1] - mn1);
+                    const float b0 = fast_exp2(m0 - mn0), b1 = fast_exp2(m1 - mn1);
+                    m_run[nt][0] = mn0;
+                    m_run[nt][1] = mn1;
+                    l_run[nt][0] = l_run[nt][0] * a0 + l0 * b0;
+                    l_run[nt][1] = l_run[nt][1] * a1 + l1 * b1;
+#pragma unroll
+                    for (int mt = 0; mt < kDSteps; mt++) {
+                        o[nt][mt][0] = o[nt][mt][0] * a0 + d[32 * k++] * b0;
+                        o[nt][mt][1] = o[nt][mt][1] * a1 + d[32 * k++] * b1;
+                        o[nt][mt][2] = o[nt][mt][2] * a0 + d[32 * k++] * b0;
+                        o[nt][mt][3] = o[nt][mt][3] * a1 + d[32 * k++] * b1;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&drained[kvh_local]);
+        }
         // ---- segment result
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
@@ -697,7 +789,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     }
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-        if (merge_seq[i] < 0) continue;
+        if (merge_seq[i] < 0) continue;  // (with split pages only warp 0 of a head ever records one)
         const int kvh = merge_ht[i] * p.tile_heads + kvh_local;
         merge_cut_sequence<D>(p, merge_seq[i], merge_ht[i], kvh * p.group + first_q, n_q, lane);
     }
@@ -804,6 +896,41 @@ static int fused_merge_pays(int batch, int n_head_tiles, int n_ctas) {
     return (long long)batch * n_head_tiles * 4 >= n_ctas ? 1 : 0;
 }
 
+// How the eight consumer warps share a tile of `tile_heads` KV heads whose GQA group has `group` query heads, and
+// the shared-memory window that goes with it.  Fills the shape fields of `p`; returns false when no tiling fits.
+static bool plan_decode_tile(DecodeParams& p, int tile_heads, int group, int D, int smem_optin, size_t* smem_bytes) {
+    const int warps_per_head = kConsumerWarps / tile_heads;
+    p.tile_heads = tile_heads;
+    p.page_split = 1;
+    if (warps_per_head > 1 && group <= 16) {
+        // few KV heads: the warps of a head split its pages, each for all query heads of the group
+        p.page_split = warps_per_head;
+        p.heads_per_warp = group;
+        p.active_warps = kConsumerWarps;
+        p.slot_arrivals = tile_heads;
+    } else {
+        p.heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
+        if (p.heads_per_warp > 16) return false;
+        p.active_warps = ((group + p.heads_per_warp - 1) / p.heads_per_warp) * tile_heads;
+        p.slot_arrivals = p.active_warps;
+    }
+    const int nt = p.heads_per_warp <= 8 ? 1 : 2;
+    p.dump_bytes = nt * (D / 16 * 4 + 4) * 32 * (int)sizeof(float);
+    p.dump_offset = 128;  // behind the abort flag and the exchange barriers
+    const size_t dumps = p.page_split > 1 ? (size_t)(kConsumerWarps - tile_heads) * p.dump_bytes : 0;
+    const int slot_bytes = tile_heads * kPageTokens * D * 2;
+    const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + p.dump_offset + dumps;
+    int slots = (int)((smem_optin - 1024 - (long long)tail) / slot_bytes);
+    if (slots > kMaxSlots) slots = kMaxSlots;
+    if (slots < 2) return false;
+    p.slots = slots;
+    // three pages (six boxes) per producer round, never more than half the ring: measured best for every tile
+    // (one page per round: -6 % on eight-head tiles, -18 % on one-head tiles; seven on a 14-deep ring: -10 %)
+    p.per_round = slots / 2 < 1 ? 1 : (slots / 2 > 3 ? 3 : slots / 2);
+    *smem_bytes = 1024 + (size_t)slots * slot_bytes + tail;
+    return true;
+}
+
 int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArgs& a,
                         bool contiguous, uint32_t max_seq, const DecodeGather* gather) {
     if (gather && gather->n_dst > 0) {
@@ -849,18 +976,16 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     else if (hkv % 8 == 0) tile_heads = 8;
     else return plain();
     const int group = (int)(a.num_heads / a.num_kv_heads);
-    const int warps_per_head = kConsumerWarps / tile_heads;
-    const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
-    if (heads_per_warp > 16) return plain();
-    const int nt = heads_per_warp <= 8 ? 1 : 2;
-    const int subs_active = (group + heads_per_warp - 1) / heads_per_warp;
+    DecodeParams p{};
+    size_t smem_bytes = 0;
+    if (!plan_decode_tile(p, tile_heads, group, D, c->smem_optin, &smem_bytes)) return plain();
+    const int nt = p.heads_per_warp <= 8 ? 1 : 2;
     if (contiguous) {
         if (max_seq == 0) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode: max_seq must be positive");
     } else if (a.num_blocks == 0 || a.max_blocks_per_seq == 0) {
         return fail(GRANITE_CUDA_INVALID_ARGUMENT, "paged decode: empty pool or table");
     }
 
-    DecodeParams p{};
     p.q = a.q;
     p.tables = a.block_tables;
     p.seq_lens = a.seq_lens;
@@ -872,10 +997,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
     p.uniform_len = (int)a.seq_len;
-    p.tile_heads = tile_heads;
     p.n_head_tiles = hkv / tile_heads;
-    p.heads_per_warp = heads_per_warp;
-    p.active_warps = subs_active * tile_heads;
     p.n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds up to 8 partials per lane
     p.contiguous = contiguous ? 1 : 0;
     p.max_seq = (int)max_seq;
@@ -890,14 +1012,6 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         p.gather_head0 = (int)gather->head_offset;
         for (uint32_t r = 0; r < gather->n_dst; r++) p.gather[r] = static_cast<float*>(gather->dst[r]);
     }
-
-    const int slot_bytes = tile_heads * kPageTokens * D * 2;
-    const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
-    int slots = (int)((c->smem_optin - 1024 - tail) / slot_bytes);
-    if (slots > kMaxSlots) slots = kMaxSlots;
-    if (slots < 2) return fail(GRANITE_CUDA_INTERNAL_ERROR, "paged decode: not enough shared memory");
-    p.slots = slots;
-    const size_t smem_bytes = 1024 + (size_t)slots * slot_bytes + tail;
 
     // scratch: prefix | first_seq | part_ml | part_o
     size_t off = 0;
@@ -1074,10 +1188,6 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     else if (hkv % 8 == 0) tile_heads = 8;
     else return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: num_kv_heads must be 1, 2, 4 or a multiple of 8");
     const int group = (int)(a.num_heads / a.num_kv_heads);
-    const int warps_per_head = kConsumerWarps / tile_heads;
-    const int heads_per_warp = (group + warps_per_head - 1) / warps_per_head;
-    if (heads_per_warp > 16)
-        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: more than 16 query heads per consumer warp");
 
     int device = 0;
     GB_CUDA_TRY(cudaGetDevice(&device));
@@ -1089,6 +1199,9 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     DecodeParams p{};
+    size_t smem_bytes = 0;
+    if (!plan_decode_tile(p, tile_heads, group, kHeadDim, setup->smem_optin, &smem_bytes))
+        return fail(GRANITE_CUDA_INVALID_ARGUMENT, "static decode: more than 16 query heads per consumer warp");
     p.q = a.q;
     p.tables = a.block_tables;
     p.seq_lens = a.seq_lens;
@@ -1100,21 +1213,11 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
     p.uniform_len = (int)a.seq_len;
-    p.tile_heads = tile_heads;
     p.n_head_tiles = hkv / tile_heads;
-    p.heads_per_warp = heads_per_warp;
-    p.active_warps = ((group + heads_per_warp - 1) / heads_per_warp) * tile_heads;
     p.n_ctas = setup->sm_count;
     p.contiguous = 0;
     p.max_seq = 0;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    const int slot_bytes = tile_heads * kPageTokens * kHeadDim * 2;
-    const size_t tail = 2 * kMaxSlots * sizeof(uint64_t) + 64;
-    int slots = (int)((setup->smem_optin - 1024 - tail) / slot_bytes);
-    if (slots > kMaxSlots) slots = kMaxSlots;
-    if (slots < 2) return fail(GRANITE_CUDA_INTERNAL_ERROR, "static decode: not enough shared memory");
-    p.slots = slots;
-    const size_t smem_bytes = 1024 + (size_t)slots * slot_bytes + tail;
 
     unsigned char* ws = setup->scratch;
     p.page_prefix = reinterpret_cast<int*>(ws + kStaticOffPrefix);
@@ -1140,7 +1243,7 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
 
     // The dynamic shared-memory limit is set on every call (it allocates nothing): another entry
     // point, or another library object sharing these kernels, may have set a different one since.
-    auto kern = heads_per_warp <= 8 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>;
+    auto kern = p.heads_per_warp <= 8 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>;
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, setup->smem_optin));
     decode_plan_kernel<<<1, 1024, 0, st>>>(p);
     kern<<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);

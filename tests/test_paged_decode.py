@@ -48,7 +48,11 @@ def _oracle(case, k_np, v_np):
     return ref
 
 
-@pytest.mark.parametrize("hq,hkv", [(32, 8), (32, 4), (64, 8), (8, 8), (16, 2), (8, 1), (32, 16)])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (32, 4), (64, 8), (8, 8), (16, 2), (8, 1), (32, 16),
+                                    # few KV heads: the warps of a head share its pages (groups up to 16) ...
+                                    (16, 1), (9, 1), (1, 1), (4, 4), (64, 4),
+                                    # ... or, with larger groups, its query heads
+                                    (64, 2), (40, 1)])
 def test_paged_decode_matches_cpu(compute, hq, hkv):
     case = synth.paged_case(seed=7 + hq + hkv, batch=5, len_lo=1, len_hi=700, num_heads=hq, num_kv_heads=hkv)
     got, k_np, v_np = _run_paged(compute, case)
