@@ -1104,7 +1104,7 @@ def main():
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one paged_decode_splitkv
 # launch, from an ncu capture of a 16-sequence case of the same kernel (ncu --set full
 # --clock-control none, one launch); DRAM traffic grows in proportion to the tokens read.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0048
 
 if __name__ == "__main__":
     sys.exit(main())
