@@ -956,7 +956,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     auto plain = [&]() {
         if (gather && gather->dst_heads != 0 && gather->dst_heads != a.num_heads)
             return fail(GRANITE_CUDA_INVALID_ARGUMENT,
-                        "decode gather: a head-sharded destination needs head_dim 128 or 64, 16-token pages and 1, 2, 4 or 8k KV heads");
+                        "decode gather: a head-sharded destination needs head_dim 128 or 64 and 16-token pages");
         int rc = launch_generic_decode(c, a, contiguous, max_seq);
         if (rc == GRANITE_CUDA_SUCCESS && gather) {
             const uint64_t row_bytes = (uint64_t)a.num_heads * a.head_dim * 4;
@@ -965,16 +965,14 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         }
         return rc;
     };
-    // shapes outside this kernel's tiling (head_dim 128, 16-token pages, 1, 2, 4 or 8k KV heads, at
-    // most 16 query heads per consumer warp) run on the plain kernel
+    // shapes outside this kernel's tiling (head_dim 128 or 64, 16-token pages, at most 16 query heads per
+    // consumer warp) run on the plain kernel
     if ((a.head_dim != 128 && a.head_dim != 64) || (!contiguous && a.block_size != kPageTokens))
         return plain();
     const int D = (int)a.head_dim;
     const int hkv = (int)a.num_kv_heads;
-    int tile_heads;
-    if (hkv == 1 || hkv == 2 || hkv == 4) tile_heads = hkv;
-    else if (hkv % 8 == 0) tile_heads = 8;
-    else return plain();
+    // the largest of 8, 4, 2, 1 KV heads per tile that divides the head count (12 heads: three tiles of four)
+    const int tile_heads = hkv % 8 == 0 ? 8 : hkv % 4 == 0 ? 4 : hkv % 2 == 0 ? 2 : 1;
     const int group = (int)(a.num_heads / a.num_kv_heads);
     DecodeParams p{};
     size_t smem_bytes = 0;

@@ -107,8 +107,8 @@ int granite_cuda_memset(granite_cuda_compute_t* c, void* dev_dst, int byte, size
  * MetalCompute::paged_attention_decode (metal_compute.h:869-881, metal_compute.mm:2535-2621).
  * Addressing rule (metal_compute.h:853-861): token pos of a sequence lives at pool row
  * block_table[pos / block_size] * block_size + pos % block_size.
- * Tuned kernel: head_dim 128 or 64, block_size 16, num_kv_heads in {1,2,4} or a multiple of 8; other
- * head dims (multiples of 8 up to 256), page sizes and KV-head counts run on a plain fp32 kernel;
+ * Tuned kernel: head_dim 128 or 64, block_size 16, any num_kv_heads (tiles of 8, 4, 2 or 1 heads); other
+ * head dims (multiples of 8 up to 256) and page sizes run on a plain fp32 kernel;
  * num_heads % num_kv_heads != 0 or a head_dim outside that range returns InvalidArgument as the
  * reference does for an unsupported head_dim (metal_compute.mm:2556-2559).  A sequence of length 0
  * gets a zero row. */
@@ -153,7 +153,7 @@ int granite_cuda_batched_paged_attention_decode_gather(granite_cuda_compute_t* c
  * [dst_head_offset, dst_head_offset + args->num_heads): element (b, h, d) goes to
  * dst + (((dst_row_offset + b) * dst_num_heads + dst_head_offset + h) * head_dim + d).
  * dst_num_heads == 0 means args->num_heads (the by-sequence form above).  Needs the shapes of the
- * tuned decode kernel (head_dim 128 or 64, 16-token pages, 1, 2, 4 or 8k local KV heads).
+ * tuned decode kernel (head_dim 128 or 64, 16-token pages).
  * No reference counterpart; the addressing rule inside the pool shard is the reference's
  * (include/granite/metal_compute.h:853-861) with the local head count. */
 int granite_cuda_batched_paged_attention_decode_gather_heads(granite_cuda_compute_t* c,

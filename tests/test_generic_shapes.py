@@ -1,6 +1,6 @@
 """Shapes beside the benchmarked ones through the same entry points and the same checker: head_dim
 64 (which the reference's GPU path also serves, src/backend/metal/metal_compute.mm:2550-2561) on the
-tuned kernels; head_dim 96 / 256, 32-token pages and odd KV-head counts on the plain fp32 kernel."""
+tuned kernels; head_dim 96 / 256 and 32-token pages on the plain fp32 kernel; odd KV-head counts."""
 import numpy as np
 import pytest
 

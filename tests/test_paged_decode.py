@@ -52,7 +52,9 @@ def _oracle(case, k_np, v_np):
                                     # few KV heads: the warps of a head share its pages (groups up to 16) ...
                                     (16, 1), (9, 1), (1, 1), (4, 4), (64, 4),
                                     # ... or, with larger groups, its query heads
-                                    (64, 2), (40, 1)])
+                                    (64, 2), (40, 1),
+                                    # head counts that are not 1, 2, 4 or 8k: tiles of the largest of 4, 2, 1 that divides
+                                    (12, 3), (24, 12), (14, 7), (6, 6), (40, 10)])
 def test_paged_decode_matches_cpu(compute, hq, hkv):
     case = synth.paged_case(seed=7 + hq + hkv, batch=5, len_lo=1, len_hi=700, num_heads=hq, num_kv_heads=hkv)
     got, k_np, v_np = _run_paged(compute, case)
@@ -173,17 +175,17 @@ def test_head_sharded_gather_is_refused_outside_the_tuned_shapes(compute):
     import torch
     import granite_b200 as g
     dev = "cuda:0"
-    case = synth.paged_case(seed=52, batch=2, len_lo=10, len_hi=50, num_heads=6, num_kv_heads=3)
-    out = torch.zeros((2, 6, 128), device=dev)
-    gathered = torch.zeros((2, 12, 128), device=dev)
+    case = synth.paged_case(seed=52, batch=2, len_lo=10, len_hi=50, num_heads=6, num_kv_heads=3, head_dim=96)
+    out = torch.zeros((2, 6, 96), device=dev)
+    gathered = torch.zeros((2, 12, 96), device=dev)
     args = [torch.from_numpy(x).to(dev) for x in (case.q, case.k_pool, case.v_pool, case.tables, case.seq_lens)]
     with pytest.raises(g.GraniteCudaError) as ei:
-        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 128, synth.PAGE, case.max_blocks, 0.1,
+        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 96, synth.PAGE, case.max_blocks, 0.1,
                                                num_blocks=case.num_blocks, gather_ptrs=[gathered.data_ptr()],
                                                gather_num_heads=12, gather_head_offset=6)
     assert ei.value.code == g.ErrorCode.InvalidArgument
     with pytest.raises(g.GraniteCudaError):  # the slice would run past the destination row
-        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 128, synth.PAGE, case.max_blocks, 0.1,
+        compute.batched_paged_attention_decode(*args, out, 2, 6, 3, 96, synth.PAGE, case.max_blocks, 0.1,
                                                num_blocks=case.num_blocks, gather_ptrs=[gathered.data_ptr()],
                                                gather_num_heads=8, gather_head_offset=4)
 
