@@ -61,6 +61,9 @@ def _cases():
         ("nine", synth.paged_case(seed=41, batch=9, len_lo=1, len_hi=6000, num_heads=32, num_kv_heads=8)),
         ("three, 64 heads", synth.paged_case(seed=42, batch=3, len_lo=1, len_hi=300, num_heads=64, num_kv_heads=8)),
         ("forty once more", synth.paged_case(seed=44, batch=40, len_lo=100, len_hi=900)),
+        # two and one KV heads: the warps of a head share its pages and exchange their state in shared memory
+        ("fifty, two KV heads", synth.paged_case(seed=48, batch=50, len_lo=0, len_hi=700, num_heads=16, num_kv_heads=2)),
+        ("five, one KV head", synth.paged_case(seed=49, batch=5, len_lo=1, len_hi=3000, num_heads=8, num_kv_heads=1)),
     ]
 
 
