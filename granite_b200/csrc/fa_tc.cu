@@ -20,7 +20,8 @@
 // MMAs of the next virtual step run while the softmax of the current one is still working.
 // Roles (384 threads):
 //   warp 0      TMA producer: Q once per item, then K_j / V_j into shared-memory rings
-//               (128-byte swizzle; a paged prefix tile is 8 pages = 32 boxes issued by the warp)
+//               (128-byte swizzle; a paged tile is 8 pages = 8 boxes of 4 KB issued by eight lanes).  It also
+//               works out the CTA's items at start-up, and starts loading before tensor memory is allocated
 //   warp 1      one thread issues the score MMAs S_b = Q_t K_j^T (operands in shared memory)
 //   warps 2, 3  one thread each issues half of the output MMAs O_t += P_b V_j: warp 2 the fp16
 //               "hi" part of P, warp 3 the "lo" part (P from TMEM, V from shared memory,
