@@ -233,12 +233,15 @@ def test_unsupported_shapes_are_rejected(compute):
         assert ei.value.code == g.ErrorCode.InvalidArgument
 
 
-@pytest.mark.parametrize("seq_kv,max_seq", [(512, 512), (1, 64), (100, 256), (2048, 4096), (333, 333)])
-def test_contiguous_decode_matches_cpu(compute, seq_kv, max_seq):
+@pytest.mark.parametrize("seq_kv,max_seq,hq,hkv", [(512, 512, 32, 8), (1, 64, 32, 8), (100, 256, 32, 8), (2048, 4096, 32, 8),
+                                                   (333, 333, 32, 8),
+                                                   # few KV heads: the warps of a head share its pages
+                                                   (3000, 4096, 8, 1), (700, 1024, 16, 2), (129, 256, 32, 4), (900, 900, 12, 3)])
+def test_contiguous_decode_matches_cpu(compute, seq_kv, max_seq, hq, hkv):
     """multihead_attention with seq_q == 1 (config: batch 1, Hq 32, Hkv 8, D 128, ctx 512)."""
     import torch
     from oracle import pyoracle
-    hq, hkv, d = 32, 8, 128
+    d = 128
     rng = np.random.default_rng(1001 + seq_kv)
     q = rng.standard_normal((hq, d), np.float32)
     k = rng.standard_normal((hkv, max_seq, d), np.float32).astype(np.float16)
