@@ -2,7 +2,7 @@
  * granite_cuda.h - C ABI of the B200 (sm_100a) attention backend for Granite.
  *
  * This is the drop-in boundary: a CUDA compute class / backend / operator inside Granite binds
- * exactly these entry points (see INTEGRATION.md for the binding a maintainer adds).  Plain
+ * exactly these entry points (the integration notes shipped beside this header show the binding a maintainer adds).  Plain
  * pointers and sizes only; no C++ or torch types cross it.
  *
  * Conventions (following the reference):
