@@ -588,7 +588,8 @@ def measure_paged_prefill(compute, dev, reps: int = 200):
 
 def measure_single_decode(compute, dev, reps: int = 200):
     """One sequence, one new token, 512 tokens of contiguous fp16 cache (Hq 32, Hkv 8, D 128): the
-    reference's own CPU-runnable case.  2 MB of traffic: the figure is launch latency, not bandwidth."""
+    reference's own CPU-runnable case, and what single-user decoding looks like.  2 MB of traffic: the figure is
+    launch latency, not bandwidth."""
     import torch
     hq, hkv, d, ctx = 32, 8, 128, 512
     gen = torch.Generator(device=dev)
@@ -624,9 +625,9 @@ def measure_single_decode(compute, dev, reps: int = 200):
     ms_graph = region_ms_per_launch(dev, lambda i: graph.replay(), reps)
     side_compute.shutdown()
     nbytes = 2 * hkv * ctx * d * 2 + hq * d * 4 * 2
-    return {"workload": "decode_contiguous_ctx512", "kernels": "decode_plan + contiguous_decode_splitkv + decode_merge",
+    return {"workload": "decode_contiguous_ctx512", "kernels": "contiguous_decode_direct (one launch: a CTA per KV head, its warps share the pages)",
             "call_ms": ms, "graph_replay_ms": ms_graph, "launches": reps, "algorithmic_bytes": nbytes,
-            "bound": "launch latency (three dependent kernels; a batch this small keeps the separate merge pass)"}
+            "bound": "launch latency (2 MB moved)"}
 
 
 def measure_tree16(compute, dev, reps: int = 200):

@@ -55,6 +55,9 @@ struct DecodeParams {
     int dump_offset;      // byte offset of the warps' exchange area behind the barriers
     int dump_bytes;       // bytes of one warp's dump
     int per_round;        // pages the producer issues per round (two slots each)
+    // 1: small batches of short sequences - one CTA per (sequence, KV head), its eight warps sharing the pages;
+    // no plan kernel, no partials, no merge: one launch.  The grid is batch * num_kv_heads CTAs.
+    int direct;
     int slots;            // ring depth
     int n_ctas;
     int contiguous;       // 1: k/v are [batch, Hkv, max_seq, D], table is the identity
@@ -194,7 +197,23 @@ struct SegmentWalker {
     long long P, P1;
     int total, batch, b, cta, index;
     const int* prefix;
+    int direct_pages;  // direct mode: pages of this CTA's sequence, -1 once handed out; -2: not direct
     __device__ SegmentWalker(const DecodeParams& p, int cta_) {
+        direct_pages = -2;
+        if (p.direct) {
+            // CTA = (sequence, KV head): the whole sequence is one segment
+            cta = cta_;
+            b = cta_ / p.n_head_tiles;
+            int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;
+            const int max_len = p.contiguous ? p.max_seq : p.max_blocks * kPageTokens;
+            if (len < 0 || len > max_len) {
+                atomicOr(p.status, kStatusBadSeqLen);
+                len = 0;
+            }
+            direct_pages = (len + kPageTokens - 1) / kPageTokens;
+            total = p.n_head_tiles;  // reused below as the divisor that yields the head tile
+            return;
+        }
         prefix = p.page_prefix;
         batch = p.batch;
         total = prefix[batch];
@@ -206,6 +225,17 @@ struct SegmentWalker {
         index = 0;
     }
     __device__ bool next(Segment& s) {
+        if (direct_pages != -2) {
+            if (direct_pages <= 0) return false;  // handed out already, or an empty sequence
+            s.seq = b;
+            s.head_tile = cta % total;
+            s.page_begin = 0;
+            s.npages = direct_pages;
+            s.seq_pages = direct_pages;
+            s.slot = -1;
+            direct_pages = -1;
+            return true;
+        }
         if (P >= P1) return false;
         int ht = (int)(P / total);
         int pg = (int)(P - (long long)ht * total);
@@ -352,9 +382,15 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
         mbar_fence_init();
     }
     __syncthreads();
-    if (p.page_prefix[p.batch] == 0) return;
+    if (!p.direct && p.page_prefix[p.batch] == 0) return;
 
     SegmentWalker walk(p, blockIdx.x);
+    if (p.direct && walk.direct_pages == 0) {
+        // an empty sequence: its rows are defined to be zero (the plan kernel does this otherwise)
+        const int kvh = (int)blockIdx.x % p.n_head_tiles;
+        for (int i = threadIdx.x; i < p.group * p.d; i += kDecodeThreads) store_out(p, walk.b, kvh * p.group + i / p.d, i % p.d, 0.f);
+        return;
+    }
     Segment seg;
     int slot = 0;
     uint32_t phase = 0;
@@ -974,9 +1010,16 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     // the largest of 8, 4, 2, 1 KV heads per tile that divides the head count (12 heads: three tiles of four)
     const int tile_heads = hkv % 8 == 0 ? 8 : hkv % 4 == 0 ? 4 : hkv % 2 == 0 ? 2 : 1;
     const int group = (int)(a.num_heads / a.num_kv_heads);
+    const int n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds up to 8 partials per lane
+    // Small batches of short sequences (what single-user decoding is): too few (sequence, head tile) pairs to keep
+    // the split partials few, and at most 128 pages per sequence.  One CTA per (sequence, KV head) then does the
+    // whole job in one launch: its eight warps share the sequence's pages and combine in shared memory.
+    const uint32_t page_cap = a.seq_lens ? (contiguous ? (max_seq + kPageTokens - 1) / kPageTokens : a.max_blocks_per_seq)
+                                         : (a.seq_len + kPageTokens - 1) / kPageTokens;
+    const bool direct = group <= 16 && page_cap <= 128 && !fused_merge_pays((int)a.batch_size, hkv / tile_heads, n_ctas);
     DecodeParams p{};
     size_t smem_bytes = 0;
-    if (!plan_decode_tile(p, tile_heads, group, D, c->smem_optin, &smem_bytes)) return plain();
+    if (!plan_decode_tile(p, direct ? 1 : tile_heads, group, D, c->smem_optin, &smem_bytes)) return plain();
     const int nt = p.heads_per_warp <= 8 ? 1 : 2;
     if (contiguous) {
         if (max_seq == 0) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "decode: max_seq must be positive");
@@ -995,14 +1038,15 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
     p.uniform_len = (int)a.seq_len;
-    p.n_head_tiles = hkv / tile_heads;
-    p.n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds up to 8 partials per lane
+    p.direct = direct ? 1 : 0;
+    p.n_head_tiles = hkv / p.tile_heads;
+    p.n_ctas = n_ctas;
     p.contiguous = contiguous ? 1 : 0;
     p.max_seq = (int)max_seq;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = c->d_status;
     p.d = D;
-    p.fused_merge = fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
+    p.fused_merge = direct ? 0 : fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
     if (gather) {
         p.n_gather = (int)gather->n_dst;
         p.gather_row0 = (long long)gather->row_offset;
@@ -1031,13 +1075,13 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     if (contiguous) {
         // [batch, Hkv, max_seq, D]: rows of one (sequence, head); a box past max_seq reads zeros
         const uint64_t planes = (uint64_t)a.batch_size * hkv;
-        kmap = c->tensor_map_pages(a.k_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, tile_heads);
-        vmap = c->tensor_map_pages(a.v_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, tile_heads);
+        kmap = c->tensor_map_pages(a.k_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, p.tile_heads);
+        vmap = c->tensor_map_pages(a.v_cache, D, max_seq, D * 2, planes, (uint64_t)max_seq * D * 2, kPageTokens, p.tile_heads);
     } else {
         // [num_blocks * 16, Hkv, D]
         const uint64_t rows = (uint64_t)a.num_blocks * kPageTokens;
-        kmap = c->tensor_map_pages(a.k_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, tile_heads);
-        vmap = c->tensor_map_pages(a.v_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, tile_heads);
+        kmap = c->tensor_map_pages(a.k_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, p.tile_heads);
+        vmap = c->tensor_map_pages(a.v_cache, D, rows, (uint64_t)hkv * D * 2, hkv, D * 2, kPageTokens, p.tile_heads);
     }
     if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
@@ -1046,6 +1090,12 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     // always the device's opt-in maximum: the limit belongs to the kernel, not to this call, and the
     // allocation-free entry point launches the same kernels with its own (possibly larger) window
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin));
+    if (direct) {
+        LaunchScope t(c, contiguous ? "contiguous_decode_direct" : "paged_decode_direct");
+        kern<<<p.batch * hkv, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
+        GB_CUDA_TRY(cudaGetLastError());
+        return GRANITE_CUDA_SUCCESS;
+    }
     {
         LaunchScope t(c, "decode_plan");
         decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
