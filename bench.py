@@ -625,7 +625,7 @@ def measure_single_decode(compute, dev, reps: int = 200):
     ms_graph = region_ms_per_launch(dev, lambda i: graph.replay(), reps)
     side_compute.shutdown()
     nbytes = 2 * hkv * ctx * d * 2 + hq * d * 4 * 2
-    return {"workload": "decode_contiguous_ctx512", "kernels": "contiguous_decode_direct (one launch: a CTA per KV head, its warps share the pages)",
+    return {"workload": "decode_contiguous_ctx512", "kernels": "contiguous_decode_direct (one launch: a few CTAs per KV head share the pages, the last to finish combines their partials)",
             "call_ms": ms, "graph_replay_ms": ms_graph, "launches": reps, "algorithmic_bytes": nbytes,
             "bound": "launch latency (2 MB moved)"}
 

@@ -200,13 +200,14 @@ int granite_cuda_compute_create(int device, void* stream, granite_cuda_compute_t
         }
         c->owns_stream = true;
     }
-    if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess ||
+    if (cudaMalloc(&c->d_status, kStatusBlockBytes) != cudaSuccess ||
         cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
-        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream) != cudaSuccess) {
+        cudaMemsetAsync(c->d_status, 0, kStatusBlockBytes, c->stream) != cudaSuccess) {
         granite_cuda_compute_destroy(c);
         return fail(GRANITE_CUDA_OUT_OF_MEMORY, "compute_create: status word allocation failed");
     }
     *c->h_status = 0;
+    c->d_direct_done = reinterpret_cast<unsigned*>(c->d_status + 64);
     *out = c;
     return GRANITE_CUDA_SUCCESS;
 }
@@ -235,7 +236,8 @@ int granite_cuda_sync(granite_cuda_compute_t* c) {
     c->resolve_timings();
     int st = *c->h_status;
     if (st == 0) return GRANITE_CUDA_SUCCESS;
-    GB_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
+    // (a launch that gave up may have left arrival counters of the one-launch decode half counted)
+    GB_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, kStatusBlockBytes, c->stream));
     if (st & kStatusTimeout) return fail(GRANITE_CUDA_TIMEOUT, "a device-side wait ran out (status " + std::to_string(st) + ")");
     if (st & kStatusBadTable) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a block-table entry was outside the pool");
     if (st & kStatusBadSeqLen) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a sequence length was negative or exceeded its block table");

@@ -24,6 +24,11 @@ enum : int {
     kStatusLayout = 16,      // a kernel found its shared-memory window smaller than its layout
 };
 
+// The status word and, 256 bytes behind it, the arrival counters of the one-launch decode (one per (sequence,
+// KV head) pair) share one small allocation.
+constexpr int kMaxDirectPairs = 192;
+constexpr size_t kStatusBlockBytes = 256 + kMaxDirectPairs * sizeof(unsigned);
+
 void set_error(const std::string& msg);
 int fail(int code, const std::string& msg);
 
@@ -61,6 +66,7 @@ struct granite_cuda_compute {
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
     int* d_status = nullptr;  // device status word
+    unsigned* d_direct_done = nullptr;  // arrival counters of the one-launch decode (same allocation, 256 bytes further)
     int* h_status = nullptr;  // pinned mirror
     uint64_t dispatches = 0;
     uint64_t syncs = 0;

@@ -14,6 +14,10 @@
 // a whole sequence writes its output directly; a sequence cut by a range boundary leaves
 // un-normalised partials (m, l, o); the warp that finishes the sequence's last pages combines them.
 //
+// Small batches of short sequences (single-user decoding) skip the page list: a few CTAs per (sequence, KV head)
+// share the sequence's pages and the last of them to finish combines their partials - one launch, no plan
+// kernel, no merge pass ("direct" below).
+//
 // Inside a CTA: one producer warp walks the block table and has TMA copy each page - 16 rows of
 // up to 8 KV heads, one contiguous 32 KB piece of the pool - into a ring of shared-memory slots
 // (128-byte swizzle, mbarrier full/empty pairs).  Eight consumer warps each own one KV head of
@@ -33,6 +37,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxSlots = 64;
 constexpr int kMaxGatherDst = 16;
+constexpr int kDirectMinPages = 4;  // direct mode: pages a CTA should at least have before a sequence is shared out further
 
 struct DecodeParams {
     const float* q;
@@ -42,7 +47,8 @@ struct DecodeParams {
     int batch, num_heads, num_kv_heads, group;
     int max_blocks, num_blocks;
     int uniform_len;      // used when seq_lens == nullptr
-    int tile_heads;       // KV heads per CTA tile (<= 8)
+    int tile_heads;       // KV heads per CTA tile: 8, 4, 2 or 1
+    int tile_shift;       // log2(tile_heads)
     int n_head_tiles;     // num_kv_heads / tile_heads
     int heads_per_warp;   // query heads of the group owned by one consumer warp
     int active_warps;     // consumer warps that own at least one query head
@@ -55,9 +61,13 @@ struct DecodeParams {
     int dump_offset;      // byte offset of the warps' exchange area behind the barriers
     int dump_bytes;       // bytes of one warp's dump
     int per_round;        // pages the producer issues per round (two slots each)
-    // 1: small batches of short sequences - one CTA per (sequence, KV head), its eight warps sharing the pages;
-    // no plan kernel, no partials, no merge: one launch.  The grid is batch * num_kv_heads CTAs.
+    // >= 1: small batches of short sequences - `direct` CTAs per (sequence, KV head), each with an equal share of
+    // the sequence's pages, its eight warps sharing those; no plan kernel and no merge pass: one launch.  With more
+    // than one CTA per pair each leaves a partial, and the one that arrives last at the pair's counter combines
+    // them.  The grid is (direct, num_kv_heads, batch) CTAs - three-dimensional so that no role divides to find its
+    // place.  0: the range walk over all pages (one-dimensional grid).
     int direct;
+    unsigned* direct_done;  // [batch * num_kv_heads] arrival counters, zero between launches (the last arrival wraps them)
     int slots;            // ring depth
     int n_ctas;
     int contiguous;       // 1: k/v are [batch, Hkv, max_seq, D], table is the identity
@@ -192,18 +202,25 @@ struct Segment {
     int slot;        // partial slot (2*cta or 2*cta+1); -1 when the segment is the whole sequence
 };
 
+// Direct mode: pages per CTA when `n` CTAs share a sequence of `pages` pages (the last shares may be short or empty).
+__host__ __device__ __forceinline__ int direct_share(int pages, int n) { return (pages + n - 1) / n; }
+
 // Walks the CTA's range; every role calls it with the same arguments and sees the same segments.
 struct SegmentWalker {
     long long P, P1;
     int total, batch, b, cta, index;
     const int* prefix;
     int direct_pages;  // direct mode: pages of this CTA's sequence, -1 once handed out; -2: not direct
+    int n_direct;      // direct mode: CTAs per (sequence, KV head)
     __device__ SegmentWalker(const DecodeParams& p, int cta_) {
         direct_pages = -2;
         if (p.direct) {
-            // CTA = (sequence, KV head): the whole sequence is one segment
+            // CTA = (share, KV head, sequence): an equal share of the sequence's pages is its one segment
             cta = cta_;
-            b = cta_ / p.n_head_tiles;
+            n_direct = p.direct;
+            index = (int)blockIdx.x;  // which share
+            total = (int)blockIdx.y;  // the head tile
+            b = (int)blockIdx.z;
             int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;
             const int max_len = p.contiguous ? p.max_seq : p.max_blocks * kPageTokens;
             if (len < 0 || len > max_len) {
@@ -211,7 +228,6 @@ struct SegmentWalker {
                 len = 0;
             }
             direct_pages = (len + kPageTokens - 1) / kPageTokens;
-            total = p.n_head_tiles;  // reused below as the divisor that yields the head tile
             return;
         }
         prefix = p.page_prefix;
@@ -227,14 +243,15 @@ struct SegmentWalker {
     __device__ bool next(Segment& s) {
         if (direct_pages != -2) {
             if (direct_pages <= 0) return false;  // handed out already, or an empty sequence
+            const int share = direct_share(direct_pages, n_direct);
             s.seq = b;
-            s.head_tile = cta % total;
-            s.page_begin = 0;
-            s.npages = direct_pages;
+            s.head_tile = total;
+            s.page_begin = index * share;
+            s.npages = min(share, direct_pages - s.page_begin);
             s.seq_pages = direct_pages;
-            s.slot = -1;
+            s.slot = direct_pages > share ? cta : -1;  // a partial when other CTAs hold pages of the sequence too
             direct_pages = -1;
-            return true;
+            return s.npages > 0;
         }
         if (P >= P1) return false;
         int ht = (int)(P / total);
@@ -343,16 +360,90 @@ __device__ __forceinline__ void merge_cut_sequence(const DecodeParams& p, int b,
     }
 }
 
+// Direct mode with several CTAs per (sequence, KV head): partial `i` of the pair sits in slot `first_slot + i`
+// (the CTA's index); at most 32 of them, one per lane for the weights.  Always combined in slot order.
+template <int D>
+__device__ __forceinline__ void merge_direct(const DecodeParams& p, int b, int hq0, int n_q, int first_slot, int parts, int lane) {
+    // Four heads and four partials at a time, every load of a batch issued before the first is used: the partials
+    // come from L2 (other SMs wrote them), and one warp walking them one by one would pay that latency per load.
+    constexpr int kH = 4, kJ = 4;
+    const bool col_ok = lane * 4 < D;
+    for (int h0 = 0; h0 < n_q; h0 += kH) {
+        float m[kH], l[kH], w[kH], L[kH];
+#pragma unroll
+        for (int u = 0; u < kH; u++) {
+            m[u] = -INFINITY;
+            l[u] = 0.f;
+            if (lane < parts && h0 + u < n_q) {
+                const float2 ml = __ldcg(p.part_ml + (size_t)(first_slot + lane) * p.num_heads + hq0 + h0 + u);
+                m[u] = ml.x;
+                l[u] = ml.y;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kH; u++) {
+            float M = m[u];
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+            w[u] = (lane < parts && h0 + u < n_q) ? fast_exp2(m[u] - M) : 0.f;
+            L[u] = w[u] * l[u];
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) L[u] += __shfl_xor_sync(0xffffffffu, L[u], sh);
+        }
+        float4 acc[kH];
+#pragma unroll
+        for (int u = 0; u < kH; u++) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < parts; j0 += kJ) {
+            float4 o[kH][kJ];
+#pragma unroll
+            for (int u = 0; u < kH; u++)
+#pragma unroll
+                for (int v = 0; v < kJ; v++) {
+                    o[u][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (col_ok && j0 + v < parts && h0 + u < n_q)
+                        o[u][v] = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((size_t)(first_slot + j0 + v) * p.num_heads + hq0 + h0 + u) * D) + lane);
+                }
+#pragma unroll
+            for (int v = 0; v < kJ; v++)  // always in slot order
+#pragma unroll
+                for (int u = 0; u < kH; u++) {
+                    const float wj = __shfl_sync(0xffffffffu, w[u], (j0 + v) & 31);  // 0 beyond the last partial (o is 0 there too)
+                    acc[u].x += wj * o[u][v].x;
+                    acc[u].y += wj * o[u][v].y;
+                    acc[u].z += wj * o[u][v].z;
+                    acc[u].w += wj * o[u][v].w;
+                }
+        }
+#pragma unroll
+        for (int u = 0; u < kH; u++)
+            if (col_ok && h0 + u < n_q) {
+                const float inv = 1.0f / L[u];
+                store_out4(p, b, hq0 + h0 + u, lane * 4, make_float4(acc[u].x * inv, acc[u].y * inv, acc[u].z * inv, acc[u].w * inv));
+            }
+    }
+}
+
 #ifndef GB_DECODE_PAGES_PER_ITER_D128
 #define GB_DECODE_PAGES_PER_ITER_D128 1
 #endif
 #ifndef GB_DECODE_PAGES_PER_ITER_D64
 #define GB_DECODE_PAGES_PER_ITER_D64 2
 #endif
-template <int NT, int D, int PP = (D == 64 ? GB_DECODE_PAGES_PER_ITER_D64 : GB_DECODE_PAGES_PER_ITER_D128)>
+// kSplit: the build for tiles of fewer than eight KV heads, whose warps share a head's pages (page_split > 1) -
+// a build of its own so that the exchange and merge code costs the eight-head kernel no registers.
+template <int NT, int D, bool kSplit, int PP = (D == 64 ? GB_DECODE_PAGES_PER_ITER_D64 : GB_DECODE_PAGES_PER_ITER_D128)>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
-                    const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
+                    const __grid_constant__ CUtensorMap vmap, const __grid_constant__ DecodeParams p) {
+    {
+        // The parameters span several constant-cache lines, all cold at the start of a launch: one load from each
+        // line now lets their misses overlap instead of stalling the roles one field at a time (a short call is
+        // mostly start-up latency).
+        int touch = 0;
+#pragma unroll
+        for (int i = 0; i < (int)sizeof(DecodeParams); i += 64) touch |= reinterpret_cast<const int*>(&p)[i / 4];
+        asm volatile("" ::"r"(touch));
+    }
     constexpr int kDSteps = D / 16;                     // 16-wide steps along head_dim
     constexpr int kChunks = D / 64;                     // 128-byte swizzle blocks per row
     constexpr int kHeadPageBytes = kPageTokens * D * 2;  // one head's K (or V) page
@@ -369,26 +460,28 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     float* dump_area = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(empty + kMaxSlots) + p.dump_offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < p.slots; i++) {
-            mbar_init(&full[i], 1);
-            mbar_init(&empty[i], p.slot_arrivals);
-        }
-        for (int i = 0; i < 4; i++) {
-            mbar_init(&dumped[i], max(p.page_split - 1, 1));
-            mbar_init(&drained[i], 1);
-        }
-        *abort_flag = 0;
-        mbar_fence_init();
+    // one barrier pair per thread (a single thread initialising up to 136 barriers costs over a thousand clocks,
+    // which a short call feels)
+    for (int i = threadIdx.x; i < p.slots; i += kDecodeThreads) {
+        mbar_init(&full[i], 1);
+        mbar_init(&empty[i], p.slot_arrivals);
     }
+    if (threadIdx.x >= kDecodeThreads - 4) {
+        const int i = threadIdx.x - (kDecodeThreads - 4);
+        mbar_init(&dumped[i], max(p.page_split - 1, 1));
+        mbar_init(&drained[i], 1);
+    }
+    if (threadIdx.x == 0) *abort_flag = 0;
+    mbar_fence_init();
     __syncthreads();
     if (!p.direct && p.page_prefix[p.batch] == 0) return;
 
-    SegmentWalker walk(p, blockIdx.x);
+    const int cta_linear = (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+    SegmentWalker walk(p, cta_linear);
     if (p.direct && walk.direct_pages == 0) {
         // an empty sequence: its rows are defined to be zero (the plan kernel does this otherwise)
-        const int kvh = (int)blockIdx.x % p.n_head_tiles;
-        for (int i = threadIdx.x; i < p.group * p.d; i += kDecodeThreads) store_out(p, walk.b, kvh * p.group + i / p.d, i % p.d, 0.f);
+        if (walk.index == 0)
+            for (int i = threadIdx.x; i < p.group * p.d; i += kDecodeThreads) store_out(p, walk.b, walk.total * p.group + i / p.d, i % p.d, 0.f);
         return;
     }
     Segment seg;
@@ -467,9 +560,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     }
 
     // ---------------------------------------------------------------- consumer warps
-    const int kvh_local = warp % p.tile_heads;
-    const int sub = warp / p.tile_heads;
-    const bool split = p.page_split > 1;
+    const int kvh_local = warp & (p.tile_heads - 1);
+    const int sub = warp >> p.tile_shift;
+    constexpr bool split = kSplit;  // the launcher picks the build by p.page_split > 1
     const int first_q = split ? 0 : sub * p.heads_per_warp;  // first query head of the group owned here
     if (first_q >= p.group) return;              // idle warp (not counted in active_warps)
     const int n_q = min(p.heads_per_warp, p.group - first_q);
@@ -707,18 +800,15 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                     if (lane == 0) atomicOr(p.status, kStatusTimeout);
                     return;
                 }
-                float* d = dump_area + ((size_t)(kvh_local * (p.page_split - 1) + (sub - 1)) * kPerLane) * 32 + lane;
+                // (16-byte pieces, lane-interleaved: group 0 of an n-tile is its maxima and sums, group 1 + mt the
+                // four accumulators of step mt)
+                float4* d = reinterpret_cast<float4*>(dump_area) + ((size_t)(kvh_local * (p.page_split - 1) + (sub - 1)) * (kPerLane / 4)) * 32 + lane;
                 int k = 0;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    d[32 * k++] = m_run[nt][0];
-                    d[32 * k++] = m_run[nt][1];
-                    d[32 * k++] = l_run[nt][0];
-                    d[32 * k++] = l_run[nt][1];
+                    d[32 * k++] = make_float4(m_run[nt][0], m_run[nt][1], l_run[nt][0], l_run[nt][1]);
 #pragma unroll
-                    for (int mt = 0; mt < kDSteps; mt++)
-#pragma unroll
-                        for (int i = 0; i < 4; i++) d[32 * k++] = o[nt][mt][i];
+                    for (int mt = 0; mt < kDSteps; mt++) d[32 * k++] = make_float4(o[nt][mt][0], o[nt][mt][1], o[nt][mt][2], o[nt][mt][3]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&dumped[kvh_local]);
@@ -728,25 +818,71 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 if (lane == 0) atomicOr(p.status, kStatusTimeout);
                 return;
             }
+            // The new maxima first, then every dump weighted against them: no dump's arithmetic waits for the one
+            // before it, so the shared-memory loads of all of them are in flight together.
+            const float4* d0 = reinterpret_cast<const float4*>(dump_area) + ((size_t)(kvh_local * (p.page_split - 1)) * (kPerLane / 4)) * 32 + lane;
+            float mn[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                mn[nt][0] = m_run[nt][0];
+                mn[nt][1] = m_run[nt][1];
+            }
             for (int w = 0; w < p.page_split - 1; w++) {
-                const float* d = dump_area + ((size_t)(kvh_local * (p.page_split - 1) + w) * kPerLane) * 32 + lane;
-                int k = 0;
+                const float4* d = d0 + (size_t)w * (kPerLane / 4) * 32;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const float m0 = d[32 * k++], m1 = d[32 * k++], l0 = d[32 * k++], l1 = d[32 * k++];
-                    const float mn0 = fmaxf(m_run[nt][0], m0), mn1 = fmaxf(m_run[nt][1], m1);
-                    const float a0 = fast_exp2(m_run[nt][0] - mn0), a1 = fast_exp2(m_run[nt][1] - mn1);
-                    const float b0 = fast_exp2(m0 - mn0), b1 = fast_exp2(m1 - mn1);
-                    m_run[nt][0] = mn0;
-                    m_run[nt][1] = mn1;
-                    l_run[nt][0] = l_run[nt][0] * a0 + l0 * b0;
-                    l_run[nt][1] = l_run[nt][1] * a1 + l1 * b1;
+                    const float4 ml = d[32 * (nt * (kDSteps + 1))];
+                    mn[nt][0] = fmaxf(mn[nt][0], ml.x);
+                    mn[nt][1] = fmaxf(mn[nt][1], ml.y);
+                }
+            }
 #pragma unroll
-                    for (int mt = 0; mt < kDSteps; mt++) {
-                        o[nt][mt][0] = o[nt][mt][0] * a0 + d[32 * k++] * b0;
-                        o[nt][mt][1] = o[nt][mt][1] * a1 + d[32 * k++] * b1;
-                        o[nt][mt][2] = o[nt][mt][2] * a0 + d[32 * k++] * b0;
-                        o[nt][mt][3] = o[nt][mt][3] * a1 + d[32 * k++] * b1;
+            for (int nt = 0; nt < NT; nt++) {
+                const float a0 = fast_exp2(m_run[nt][0] - mn[nt][0]), a1 = fast_exp2(m_run[nt][1] - mn[nt][1]);
+                m_run[nt][0] = mn[nt][0];
+                m_run[nt][1] = mn[nt][1];
+                l_run[nt][0] *= a0;
+                l_run[nt][1] *= a1;
+#pragma unroll
+                for (int mt = 0; mt < kDSteps; mt++) {
+                    o[nt][mt][0] *= a0;
+                    o[nt][mt][1] *= a1;
+                    o[nt][mt][2] *= a0;
+                    o[nt][mt][3] *= a1;
+                }
+            }
+            // every dump's weights, then accumulator step by accumulator step over all dumps: the loop over the
+            // (at most seven) dumps is unrolled and predicated, so that all of its loads are independent
+            constexpr int kMaxDumps = kConsumerWarps - 1;
+            float b[kMaxDumps][NT][2];
+#pragma unroll
+            for (int w = 0; w < kMaxDumps; w++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    b[w][nt][0] = b[w][nt][1] = 0.f;
+                    if (w < p.page_split - 1) {
+                        const float4 ml = d0[((size_t)w * (kPerLane / 4) + nt * (kDSteps + 1)) * 32];
+                        // (a warp that had no page dumps -inf and zeros: weight 0)
+                        b[w][nt][0] = fast_exp2(ml.x - mn[nt][0]);
+                        b[w][nt][1] = fast_exp2(ml.y - mn[nt][1]);
+                        l_run[nt][0] += ml.z * b[w][nt][0];
+                        l_run[nt][1] += ml.w * b[w][nt][1];
+                    }
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+                for (int mt = 0; mt < kDSteps; mt++) {
+#pragma unroll
+                    for (int w = 0; w < kMaxDumps; w++) {
+                        if (w < p.page_split - 1) {
+                            const float4 ov = d0[((size_t)w * (kPerLane / 4) + nt * (kDSteps + 1) + 1 + mt) * 32];
+                            o[nt][mt][0] += ov.x * b[w][nt][0];
+                            o[nt][mt][1] += ov.y * b[w][nt][1];
+                            o[nt][mt][2] += ov.z * b[w][nt][0];
+                            o[nt][mt][3] += ov.w * b[w][nt][1];
+                        }
                     }
                 }
             }
@@ -799,6 +935,26 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
                 for (int r = 0; r < p.n_gather; r++)
                     *reinterpret_cast<float4*>(p.gather[r] + gather_offset(p, seg.seq, hq0 + h) + lane * 4) = v;
             }
+        }
+        if (kSplit && seg.slot >= 0 && p.direct) {
+            // one of several CTAs of this (sequence, KV head): publish the partial and count the arrival; the CTA
+            // that arrives last combines all of them (release: fence before the count; acquire: after).  The
+            // counter wraps to zero with the last arrival, so it needs no reset between launches.  One acquire-release
+            // atomic at GPU scope instead of fence + atomic + fence: the warp barrier orders the other lanes' stores
+            // before it and their later loads after it.
+            __syncwarp();
+            const int parts = (seg.seq_pages + direct_share(seg.seq_pages, p.direct) - 1) / direct_share(seg.seq_pages, p.direct);
+            int last = 0;
+            if (lane == 0) {
+                unsigned old;
+                asm volatile("atom.acq_rel.gpu.global.inc.u32 %0, [%1], %2;"
+                             : "=r"(old)
+                             : "l"(p.direct_done + (size_t)seg.seq * p.n_head_tiles + seg.head_tile), "r"((unsigned)(parts - 1))
+                             : "memory");
+                last = old == (unsigned)(parts - 1);
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) merge_direct<D>(p, seg.seq, hq0, n_q, seg.slot - (int)blockIdx.x, parts, lane);
         }
         if (seg.slot >= 0 && p.fused_merge) {
             // publish the partial, then count this warp's pages of the sequence; the warp whose
@@ -937,6 +1093,7 @@ static int fused_merge_pays(int batch, int n_head_tiles, int n_ctas) {
 static bool plan_decode_tile(DecodeParams& p, int tile_heads, int group, int D, int smem_optin, size_t* smem_bytes) {
     const int warps_per_head = kConsumerWarps / tile_heads;
     p.tile_heads = tile_heads;
+    p.tile_shift = tile_heads == 8 ? 3 : tile_heads == 4 ? 2 : tile_heads == 2 ? 1 : 0;
     p.page_split = 1;
     if (warps_per_head > 1 && group <= 16) {
         // few KV heads: the warps of a head split its pages, each for all query heads of the group
@@ -1012,11 +1169,15 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     const int group = (int)(a.num_heads / a.num_kv_heads);
     const int n_ctas = c->sm_count < kMaxMergeParts ? c->sm_count : kMaxMergeParts;  // the merge holds up to 8 partials per lane
     // Small batches of short sequences (what single-user decoding is): too few (sequence, head tile) pairs to keep
-    // the split partials few, and at most 128 pages per sequence.  One CTA per (sequence, KV head) then does the
-    // whole job in one launch: its eight warps share the sequence's pages and combine in shared memory.
+    // the split partials few, and at most 128 pages per sequence.  A few CTAs per (sequence, KV head) then do the
+    // whole job in one launch: each takes an equal share of the sequence's pages (at least four - one SM's TMA
+    // unit moves a one-head page box per ~250 clocks, so a whole sequence on one SM would be bound by that), its
+    // eight warps share them and combine in shared memory, and the last CTA of a pair to finish combines the
+    // pair's partials.
     const uint32_t page_cap = a.seq_lens ? (contiguous ? (max_seq + kPageTokens - 1) / kPageTokens : a.max_blocks_per_seq)
                                          : (a.seq_len + kPageTokens - 1) / kPageTokens;
-    const bool direct = group <= 16 && page_cap <= 128 && !fused_merge_pays((int)a.batch_size, hkv / tile_heads, n_ctas);
+    const bool direct = group <= 16 && page_cap <= 128 && !fused_merge_pays((int)a.batch_size, hkv / tile_heads, n_ctas) &&
+                        (int)a.batch_size * hkv <= kMaxDirectPairs;
     DecodeParams p{};
     size_t smem_bytes = 0;
     if (!plan_decode_tile(p, direct ? 1 : tile_heads, group, D, c->smem_optin, &smem_bytes)) return plain();
@@ -1038,7 +1199,13 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.max_blocks = (int)a.max_blocks_per_seq;
     p.num_blocks = (int)a.num_blocks;
     p.uniform_len = (int)a.seq_len;
-    p.direct = direct ? 1 : 0;
+    if (direct) {
+        const int pairs = (int)a.batch_size * hkv;
+        int per_pair = (int)(page_cap + kDirectMinPages - 1) / kDirectMinPages;
+        per_pair = std::min(per_pair, std::min(n_ctas / pairs, 32));  // one lane per partial in the merge
+        p.direct = std::max(per_pair, 1);
+        p.direct_done = c->d_direct_done;
+    }
     p.n_head_tiles = hkv / p.tile_heads;
     p.n_ctas = n_ctas;
     p.contiguous = contiguous ? 1 : 0;
@@ -1085,14 +1252,17 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     }
     if (!kmap || !vmap) return GRANITE_CUDA_EXECUTION_FAILED;
 
-    auto kern = D == 128 ? (nt == 1 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>)
-                         : (nt == 1 ? paged_decode_kernel<1, 64> : paged_decode_kernel<2, 64>);
+    auto kern = p.page_split > 1
+                    ? (D == 128 ? (nt == 1 ? paged_decode_kernel<1, 128, true> : paged_decode_kernel<2, 128, true>)
+                                : (nt == 1 ? paged_decode_kernel<1, 64, true> : paged_decode_kernel<2, 64, true>))
+                    : (D == 128 ? (nt == 1 ? paged_decode_kernel<1, 128, false> : paged_decode_kernel<2, 128, false>)
+                                : (nt == 1 ? paged_decode_kernel<1, 64, false> : paged_decode_kernel<2, 64, false>));
     // always the device's opt-in maximum: the limit belongs to the kernel, not to this call, and the
     // allocation-free entry point launches the same kernels with its own (possibly larger) window
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin));
     if (direct) {
         LaunchScope t(c, contiguous ? "contiguous_decode_direct" : "paged_decode_direct");
-        kern<<<p.batch * hkv, kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
+        kern<<<dim3(p.direct, hkv, p.batch), kDecodeThreads, smem_bytes, c->stream>>>(*kmap, *vmap, p);
         GB_CUDA_TRY(cudaGetLastError());
         return GRANITE_CUDA_SUCCESS;
     }
@@ -1291,7 +1461,8 @@ extern "C" int granite_cuda_batched_paged_attention_decode_static(const GraniteC
 
     // The dynamic shared-memory limit is set on every call (it allocates nothing): another entry
     // point, or another library object sharing these kernels, may have set a different one since.
-    auto kern = p.heads_per_warp <= 8 ? paged_decode_kernel<1, 128> : paged_decode_kernel<2, 128>;
+    auto kern = p.page_split > 1 ? (p.heads_per_warp <= 8 ? paged_decode_kernel<1, 128, true> : paged_decode_kernel<2, 128, true>)
+                                 : (p.heads_per_warp <= 8 ? paged_decode_kernel<1, 128, false> : paged_decode_kernel<2, 128, false>);
     GB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, setup->smem_optin));
     decode_plan_kernel<<<1, 1024, 0, st>>>(p);
     kern<<<p.n_ctas, kDecodeThreads, smem_bytes, st>>>(kmap, vmap, p);

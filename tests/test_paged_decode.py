@@ -100,15 +100,33 @@ def test_cut_sequences_merged_inside_the_decode_kernel(compute, hq, hkv, d):
         assert np.array_equal(got, again), name
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (32, 4, 128), (16, 2, 128), (16, 1, 128), (12, 3, 128), (32, 8, 64)])
+def test_one_launch_decode_of_small_batches(compute, hq, hkv, d):
+    """Small batches of short sequences (at most 128 pages) take the one-launch path: a few CTAs per
+    (sequence, KV head) with an equal share of the pages each, the last one to arrive combining their partials.
+    Lengths around the share boundaries, sequences with fewer pages than CTAs (empty shares), empty sequences,
+    the same bits on a second run, and calls of different shapes one after the other (the arrival counters
+    must be back at zero after every launch)."""
+    for lens in ([1], [16], [17], [63], [64], [65], [512], [2047], [2048], [0], [5, 0, 2048], [100, 1999], [777, 33, 1, 1200]):
+        case = synth.paged_case(seed=41 + len(lens), batch=len(lens), len_lo=0, len_hi=0, num_heads=hq, num_kv_heads=hkv,
+                                head_dim=d, seq_lens=np.array(lens, np.int32), spare_blocks=2)
+        got, k_np, v_np = _run_paged(compute, case, poison_unused=True)
+        assert_attention_close(got, _oracle(case, k_np, v_np), f"lens={lens} Hq={hq} Hkv={hkv} D={d}")
+        again, _, _ = _run_paged(compute, case, poison_unused=True)
+        assert np.array_equal(got, again), f"lens={lens}"
+
+
 @pytest.mark.parametrize("name,lens,d", [("in-kernel merge", [0] + [3000, 40, 1] * 15 + [20000, 0], 128),
                                          ("merge pass", [700, 0, 33, 5000, 16], 128),
+                                         ("one launch", [700, 0, 33, 2048, 16], 128),
                                          ("head_dim 64", list(range(1, 1200, 29)), 64),
                                          ("plain kernel", [100, 0, 900], 96)])
 def test_decode_with_fused_gather(compute, name, lens, d):
     """The decode that also stores every final row into gather buffers (here two buffers on the same
     GPU standing in for peers): rows row_offset .. row_offset + batch hold exactly the output, every
     other row is untouched.  Covers rows written by the decode kernel itself, by the warp that merges a
-    cut sequence, by the separate merge pass, the zero rows of empty sequences and the plain kernel."""
+    cut sequence, by the separate merge pass, by the one-launch path's last CTA, the zero rows of empty
+    sequences and the plain kernel."""
     import torch
     dev = "cuda:0"
     case = synth.paged_case(seed=31, batch=len(lens), len_lo=0, len_hi=0, head_dim=d, seq_lens=np.array(lens, np.int32))
