@@ -88,8 +88,8 @@ def unshard_heads(gathered: np.ndarray) -> np.ndarray:
 # Throughput of the decode kernel with this many KV heads per page box, relative to eight (32 KB
 # boxes).  With fewer heads the warps of a head share its pages instead of its query heads, which keeps
 # the kernel near its rate down to two heads; one-head pages are 4 KB boxes, bound by how fast they can be
-# issued.  Measured on B200 on the long-context lengths, 4.8 GB of K/V per call: 6.91, 6.72, 6.00 and 4.66 TB/s.
-HEADS_PER_BOX_EFFICIENCY = {8: 1.0, 4: 0.97, 2: 0.87, 1: 0.67}
+# issued.  Measured on B200 on the long-context lengths, 4.8 GB of K/V per call: 6.89, 6.67, 6.27 and 5.04 TB/s.
+HEADS_PER_BOX_EFFICIENCY = {8: 1.0, 4: 0.97, 2: 0.91, 1: 0.73}
 
 
 def predicted_cost(lengths, num_kv_heads: int, n_ranks: int, split: str) -> float:
