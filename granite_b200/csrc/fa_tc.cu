@@ -84,9 +84,6 @@ struct TcItem {
     bool valid;
 };
 
-#ifndef GB_FA_STAGED
-#define GB_FA_STAGED 0
-#endif
 constexpr int kMaxCachedItems = 32;  // work items of a CTA kept in shared memory (later rounds are derived on the fly)
 
 struct TcSmem {
@@ -699,27 +696,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         for (int h = 0; h < 2; h++) {
                             if (tree_step && h == 1) continue;
                             uint32_t hi[16], lo[16];
-#if GB_FA_STAGED
-                            // the half's 16 pairs stage by stage, so that every instruction's operands are sixteen
-                            // instructions old when it issues
-                            uint64_t tt[16];
-#pragma unroll
-                            for (int i = 0; i < 8; i++)
-#pragma unroll
-                                for (int q = 0; q < 2; q++)
-                                    tt[2 * i + q] = fma_f32x2(f32x2(__uint_as_float(x[h][4 * i + 2 * q]), __uint_as_float(x[h][4 * i + 2 * q + 1])),
-                                                              scale2, neg_m2[q]);
-#pragma unroll
-                            for (int k = 0; k < 16; k++) {
-                                float t0, t1;
-                                f32x2_get(tt[k], t0, t1);
-                                tt[k] = f32x2(fast_exp2(t0), fast_exp2(t1));
-                            }
-#pragma unroll
-                            for (int k = 0; k < 16; k++) ls[k & 1][(k >> 1) & 1] = add_f32x2(ls[k & 1][(k >> 1) & 1], tt[k]);
-#pragma unroll
-                            for (int k = 0; k < 16; k++) split_hi_lo_x2(tt[k], hi[k], lo[k]);
-#else
 #pragma unroll
                             for (int i = 0; i < 8; i++)
 #pragma unroll
@@ -732,7 +708,6 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                                     ls[q][i & 1] = add_f32x2(ls[q][i & 1], pp);
                                     split_hi_lo_x2(pp, hi[2 * i + q], lo[2 * i + q]);
                                 }
-#endif
                             tmem_st_16x128b_x8(s_frag + 32 * h, hi);
                             tmem_st_16x128b_x8(s_frag + 64 + 32 * h, lo);
                         }
