@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-One step = one batched paged decode call (plan kernel + split-KV kernel, which also merges cut sequences) over one batch of
+One step = one batched paged decode call (one launch of the split-KV kernel, which plans for itself and merges cut sequences) over one batch of
 synthetic sequences whose K/V pages already live in HBM.  Workload at N = 1: 64 sequences, context
 lengths uniform in [1024, 32768], page 16, shuffled block table, Hq 32 / Hkv 8 / D 128, fp16 K/V,
 fp32 Q and output.  At N > 1 every rank owns its own batch of that shape (sequences are
@@ -978,6 +978,11 @@ def main():
     for i in range(args.warmup):
         step(i)
     barrier()
+    # kernels one step launches, counted by the library (a batch of this size needs no plan kernel: one launch)
+    d0 = compute.get_profiling_stats()[0]
+    step(0)
+    launches_per_step = compute.get_profiling_stats()[0] - d0
+    barrier()
     compute.enable_kernel_timing(True)
     compute.reset_kernel_timing()
     ms_per_step, ms_best, regions, clocks = timed_regions(dev, dist, world, step, args.steps, clock_index=dev.index)
@@ -1100,8 +1105,9 @@ def main():
                     "ms_per_step": e2e_ms, "ms_per_step_best": e2e_best, "steps": e2e_steps, "regions": e2e_regions,
                     "note": "host Q, block tables and lengths copied in (one pinned staging block), output copied out, sync per step; "
                             "K/V pages are cache state resident in HBM" + ("; the rows also go to every other rank (fused gather)" if world > 1 else "")},
-            # per rank and step: decode_plan + paged_decode_splitkv (which also stores the rows to the other ranks)
-            "gpu_launches": 2 * args.steps,
+            # per rank: the library's own launch count of one step (paged_decode_splitkv, which plans for itself,
+            # merges cut sequences and stores the rows to the other ranks) x the steps of a timed region
+            "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "secondary": secondary,
         }
@@ -1116,7 +1122,7 @@ def main():
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one paged_decode_splitkv
 # launch, from an ncu capture of a 16-sequence case of the same kernel (ncu --set full
 # --clock-control none, one launch); DRAM traffic grows in proportion to the tokens read.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0048
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0045
 
 if __name__ == "__main__":
     sys.exit(main())

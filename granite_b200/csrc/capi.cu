@@ -56,6 +56,20 @@ int granite_cuda_compute::ensure_scratch(size_t bytes) {
     return GRANITE_CUDA_SUCCESS;
 }
 
+int granite_cuda_compute::ensure_page_counters(size_t count) {
+    if (count <= pages_done_count) return GRANITE_CUDA_SUCCESS;
+    GB_CUDA_TRY(cudaStreamSynchronize(stream));  // growing: nothing in flight may still count in the old array
+    if (d_pages_done) cudaFree(d_pages_done);
+    d_pages_done = nullptr;
+    pages_done_count = 0;
+    const size_t want = count + count / 4 + 1024;
+    if (cudaMalloc(&d_pages_done, want * sizeof(int)) != cudaSuccess)
+        return fail(GRANITE_CUDA_OUT_OF_MEMORY, "decode page counters: cudaMalloc failed");
+    GB_CUDA_TRY(cudaMemsetAsync(d_pages_done, 0, want * sizeof(int), stream));
+    pages_done_count = want;
+    return GRANITE_CUDA_SUCCESS;
+}
+
 const CUtensorMap* granite_cuda_compute::encode_map(const TensorMapKey& key) {
     const uint64_t tick = ++tensor_map_tick;
     auto it = tensor_maps.find(key);
@@ -220,6 +234,7 @@ void granite_cuda_compute_destroy(granite_cuda_compute_t* c) {
     for (cudaEvent_t e : c->event_pool) cudaEventDestroy(e);
     if (c->scratch) cudaFree(c->scratch);
     if (c->d_status) cudaFree(c->d_status);
+    if (c->d_pages_done) cudaFree(c->d_pages_done);
     if (c->h_status) cudaFreeHost(c->h_status);
     if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -238,6 +253,7 @@ int granite_cuda_sync(granite_cuda_compute_t* c) {
     if (st == 0) return GRANITE_CUDA_SUCCESS;
     // (a launch that gave up may have left arrival counters of the one-launch decode half counted)
     GB_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, kStatusBlockBytes, c->stream));
+    if (c->d_pages_done) GB_CUDA_TRY(cudaMemsetAsync(c->d_pages_done, 0, c->pages_done_count * sizeof(int), c->stream));
     if (st & kStatusTimeout) return fail(GRANITE_CUDA_TIMEOUT, "a device-side wait ran out (status " + std::to_string(st) + ")");
     if (st & kStatusBadTable) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a block-table entry was outside the pool");
     if (st & kStatusBadSeqLen) return fail(GRANITE_CUDA_INVALID_ARGUMENT, "a sequence length was negative or exceeded its block table");

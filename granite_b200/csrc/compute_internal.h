@@ -66,6 +66,9 @@ struct granite_cuda_compute {
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
     int* d_status = nullptr;  // device status word
+    int* d_pages_done = nullptr;        // page counters of the decode without a plan kernel: zero between launches
+    size_t pages_done_count = 0;
+    int ensure_page_counters(size_t count);
     unsigned* d_direct_done = nullptr;  // arrival counters of the one-launch decode (same allocation, 256 bytes further)
     int* h_status = nullptr;  // pinned mirror
     uint64_t dispatches = 0;

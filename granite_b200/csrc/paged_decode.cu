@@ -37,6 +37,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxSlots = 64;
 constexpr int kMaxGatherDst = 16;
+constexpr int kSelfPlanMaxBatch = 192;  // sequences a CTA plans for itself (one per thread, prefix array in shared memory)
 constexpr int kDirectMinPages = 4;  // direct mode: pages a CTA should at least have before a sequence is shared out further
 
 struct DecodeParams {
@@ -75,6 +76,10 @@ struct DecodeParams {
     float scale_log2;     // scale * log2(e)
     int* status;
     int* page_prefix;     // [batch + 1]
+    // 1: no plan kernel ran - every CTA builds the page prefix sums of the (small) batch in its own shared memory,
+    // finds the first sequence of its range there, and the page counters reset themselves
+    int self_plan;
+    int plan_offset;      // byte offset of that prefix array behind the barriers
     int* cta_first_seq;   // [n_ctas]
     int d;                // head_dim: 128 or 64
     float* part_o;        // [2 * n_ctas][num_heads][d]
@@ -212,7 +217,7 @@ struct SegmentWalker {
     const int* prefix;
     int direct_pages;  // direct mode: pages of this CTA's sequence, -1 once handed out; -2: not direct
     int n_direct;      // direct mode: CTAs per (sequence, KV head)
-    __device__ SegmentWalker(const DecodeParams& p, int cta_) {
+    __device__ SegmentWalker(const DecodeParams& p, int cta_, const int* prefix_) {
         direct_pages = -2;
         if (p.direct) {
             // CTA = (share, KV head, sequence): an equal share of the sequence's pages is its one segment
@@ -230,14 +235,25 @@ struct SegmentWalker {
             direct_pages = (len + kPageTokens - 1) / kPageTokens;
             return;
         }
-        prefix = p.page_prefix;
+        prefix = prefix_;
         batch = p.batch;
         total = prefix[batch];
         cta = cta_;
         long long T = (long long)total * p.n_head_tiles;
         P = range_start(T, p.n_ctas, cta);
         P1 = range_start(T, p.n_ctas, cta + 1);
-        b = p.cta_first_seq[cta];
+        if (p.self_plan) {
+            // largest b with prefix[b] <= p0 (what the plan kernel tabulates per CTA otherwise)
+            const int p0 = total > 0 ? (int)(P % total) : 0;
+            int lo = 0, hi = batch;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (prefix[mid] <= p0) lo = mid; else hi = mid;
+            }
+            b = lo;
+        } else {
+            b = p.cta_first_seq[cta];
+        }
         index = 0;
     }
     __device__ bool next(Segment& s) {
@@ -284,9 +300,9 @@ struct SegmentWalker {
 // warp that is not last simply moves on.  Partials are read through L2 (written by other SMs).
 constexpr int kMaxMergeParts = 256;  // >= the largest grid the decode kernel is launched with
 template <int D>
-__device__ __forceinline__ void merge_cut_sequence(const DecodeParams& p, int b, int ht, int hq0, int n_q, int lane) {
-    const int total = p.page_prefix[p.batch];
-    const int s0 = p.page_prefix[b], s1 = p.page_prefix[b + 1];
+__device__ __forceinline__ void merge_cut_sequence(const DecodeParams& p, const int* prefix, int b, int ht, int hq0, int n_q, int lane) {
+    const int total = prefix[p.batch];
+    const int s0 = prefix[b], s1 = prefix[b + 1];
     const long long T = (long long)total * p.n_head_tiles;
     const long long A = (long long)ht * total + s0, B = (long long)ht * total + s1;  // the sequence's pages [A, B)
     auto cta_of = [&](long long P) {
@@ -473,11 +489,47 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     }
     if (threadIdx.x == 0) *abort_flag = 0;
     mbar_fence_init();
-    __syncthreads();
-    if (!p.direct && p.page_prefix[p.batch] == 0) return;
+    const int* prefix = p.page_prefix;
+    if (p.self_plan) {
+        // The plan for a small batch, by every CTA for itself (one sequence per thread): page counts, their
+        // inclusive scan, the prefix array in shared memory.  Saves the plan kernel's launch in front of every step.
+        int* s_prefix = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(empty + kMaxSlots) + p.plan_offset);
+        int* s_warp = s_prefix + p.batch + 1;  // [kDecodeThreads / 32] warp totals
+        int pages = 0;
+        if ((int)threadIdx.x < p.batch) {
+            int len = p.seq_lens ? p.seq_lens[threadIdx.x] : p.uniform_len;
+            const int max_len = p.contiguous ? p.max_seq : p.max_blocks * kPageTokens;
+            if (len < 0 || len > max_len) {
+                atomicOr(p.status, kStatusBadSeqLen);
+                len = 0;
+            }
+            pages = (len + kPageTokens - 1) / kPageTokens;
+        }
+        int incl = pages;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        for (int w = 0; w < warp; w++) incl += s_warp[w];
+        if ((int)threadIdx.x < p.batch) s_prefix[threadIdx.x + 1] = incl;
+        if (threadIdx.x == 0) s_prefix[0] = 0;
+        __syncthreads();
+        if (blockIdx.x == 0 && (int)threadIdx.x < p.batch && pages == 0) {
+            // rows of empty sequences are defined to be zero (rare: one thread per such sequence)
+            for (int h = 0; h < p.num_heads; h++)
+                for (int i = 0; i < p.d; i++) store_out(p, threadIdx.x, h, i, 0.f);
+        }
+        prefix = s_prefix;
+    } else {
+        __syncthreads();
+    }
+    if (!p.direct && prefix[p.batch] == 0) return;
 
     const int cta_linear = (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
-    SegmentWalker walk(p, cta_linear);
+    SegmentWalker walk(p, cta_linear, prefix);
     if (p.direct && walk.direct_pages == 0) {
         // an empty sequence: its rows are defined to be zero (the plan kernel does this otherwise)
         if (walk.index == 0)
@@ -965,6 +1017,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
             if (lane == 0) {
                 int* done = p.pages_done + ((size_t)seg.seq * p.n_head_tiles + seg.head_tile) * kConsumerWarps + warp;
                 last = atomicAdd(done, seg.npages) + seg.npages == seg.seq_pages;
+                if (last) *done = 0;  // nobody else counts on it any more: ready for the next launch without a plan kernel
                 __threadfence();
             }
             last = __shfl_sync(0xffffffffu, last, 0);
@@ -983,7 +1036,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
     for (int i = 0; i < 2; i++) {
         if (merge_seq[i] < 0) continue;  // (with split pages only warp 0 of a head ever records one)
         const int kvh = merge_ht[i] * p.tile_heads + kvh_local;
-        merge_cut_sequence<D>(p, merge_seq[i], merge_ht[i], kvh * p.group + first_q, n_q, lane);
+        merge_cut_sequence<D>(p, prefix, merge_seq[i], merge_ht[i], kvh * p.group + first_q, n_q, lane);
     }
 }
 
@@ -1214,6 +1267,17 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.status = c->d_status;
     p.d = D;
     p.fused_merge = direct ? 0 : fused_merge_pays(p.batch, p.n_head_tiles, p.n_ctas);
+    // Batches of up to 192 sequences whose cut sequences are merged inside the decode kernel need no plan kernel
+    // if the prefix array (and nine warp totals) still fits behind the page ring without costing a slot.
+    {
+        const size_t plan_bytes = ((size_t)p.batch + 1 + kDecodeThreads / 32) * sizeof(int);
+        const size_t spare = (size_t)c->smem_optin - smem_bytes;
+        if (!direct && p.fused_merge && p.batch <= kSelfPlanMaxBatch && plan_bytes <= spare) {
+            p.self_plan = 1;
+            p.plan_offset = (int)(smem_bytes - 1024 - (size_t)p.slots * p.tile_heads * kPageTokens * D * 2 - 2 * kMaxSlots * sizeof(uint64_t));
+            smem_bytes += plan_bytes;
+        }
+    }
     if (gather) {
         p.n_gather = (int)gather->n_dst;
         p.gather_row0 = (long long)gather->row_offset;
@@ -1237,6 +1301,13 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
     p.part_ml = reinterpret_cast<float2*>(ws + off_ml);
     p.part_o = reinterpret_cast<float*>(ws + off_o);
     p.pages_done = reinterpret_cast<int*>(ws + off_done);
+    if (p.self_plan) {
+        // no plan kernel zeroes the page counters: they live in an allocation of their own that starts at zero and
+        // that the kernel leaves at zero (the warp that completes a count resets it)
+        rc = c->ensure_page_counters((size_t)p.batch * p.n_head_tiles * kConsumerWarps);
+        if (rc) return rc;
+        p.pages_done = c->d_pages_done;
+    }
 
     const CUtensorMap *kmap, *vmap;
     if (contiguous) {
@@ -1266,7 +1337,7 @@ int launch_paged_decode(granite_cuda_compute* c, const GraniteCudaPagedDecodeArg
         GB_CUDA_TRY(cudaGetLastError());
         return GRANITE_CUDA_SUCCESS;
     }
-    {
+    if (!p.self_plan) {
         LaunchScope t(c, "decode_plan");
         decode_plan_kernel<<<1, 1024, 0, c->stream>>>(p);
     }
