@@ -137,7 +137,8 @@ int granite_cuda_batched_paged_attention_decode(granite_cuda_compute_t* c,
  * sharded across GPUs, every rank needs all output rows.  Each final row (sequence b, all heads) is
  * stored by the attention kernel itself to args->output and to dst_ptrs[r] + (dst_row_offset + b) rows,
  * r < n_dst (<= 16) - buffers [total sequences, num_heads, head_dim] fp32 that may live on other GPUs
- * (peer-mapped, e.g. symmetric memory) or on this one.  Plain stores over NVLink from the kernel that
+ * (peer-mapped, e.g. symmetric memory), on this one, or in pinned host memory (the rows then reach the host
+ * while the kernel runs, without a device-to-host copy behind it).  Plain stores over NVLink from the kernel that
  * produced the row: no extra launch, no multicast, no waiting on another GPU.  Ordering towards a
  * reader on another GPU is the caller's (stream completion plus its own signal between ranks).
  * No reference counterpart (the reference runs on one GPU). */
