@@ -150,6 +150,29 @@ def test_decode_with_fused_gather(compute, name, lens, d):
         assert torch.isnan(g[:offset]).all() and torch.isnan(g[offset + case.batch:]).all(), name
 
 
+@pytest.mark.parametrize("lens", [[700, 0, 33, 2048, 16], list(range(1, 3000, 61))])
+def test_decode_gather_into_pinned_host_memory(compute, lens):
+    """A gather destination may be pinned host memory: the kernel stores the rows over PCIe itself, and after the
+    stream is drained the host buffer holds exactly the device output (one-launch path and in-kernel merge)."""
+    import torch
+    dev = "cuda:0"
+    case = synth.paged_case(seed=37, batch=len(lens), len_lo=0, len_hi=0, seq_lens=np.array(lens, np.int32))
+    q = torch.from_numpy(case.q).to(dev)
+    k = torch.from_numpy(case.k_pool).to(dev)
+    v = torch.from_numpy(case.v_pool).to(dev)
+    tables = torch.from_numpy(case.tables).to(dev)
+    seq_lens = torch.from_numpy(case.seq_lens).to(dev)
+    out = torch.full((case.batch, case.num_heads, 128), float("nan"), device=dev)
+    host = torch.full((case.batch + 3, case.num_heads, 128), float("nan")).pin_memory()
+    compute.batched_paged_attention_decode(q, k, v, tables, seq_lens, out, case.batch, case.num_heads, case.num_kv_heads,
+                                           128, synth.PAGE, case.max_blocks, 1.0 / np.sqrt(128.0), num_blocks=case.num_blocks,
+                                           gather_ptrs=[host.data_ptr()], gather_row_offset=2)
+    compute.sync()
+    assert_attention_close(out.cpu().numpy(), _oracle(case, case.k_pool.view(np.uint16), case.v_pool.view(np.uint16)), "host gather")
+    assert torch.equal(host[2:2 + case.batch], out.cpu())
+    assert torch.isnan(host[:2]).all() and torch.isnan(host[2 + case.batch:]).all()
+
+
 @pytest.mark.parametrize("ranks,hq,hkv", [(2, 32, 8), (4, 32, 8), (8, 64, 8), (2, 16, 16)])
 def test_decode_sharded_by_kv_head(compute, ranks, hq, hkv):
     """Every GPU holds all sequences and num_kv_heads / ranks heads: pool shard [rows, Hkv / ranks, D], the same
@@ -234,6 +257,44 @@ def test_bad_table_entry_is_reported_not_fatal(compute):
     compute.sync()  # status word was cleared; the context is still usable
     case.tables[1, 2] = 0
     _run_paged(compute, case)
+
+
+@pytest.mark.parametrize("batch", [37, 64, 192, 193, 300])
+def test_batches_around_the_self_planning_limit(compute, batch):
+    """Up to 192 sequences every CTA of the decode kernel builds the page prefix sums itself (no plan kernel, the
+    page counters reset themselves); larger batches launch the plan kernel.  Ragged lengths with empty sequences,
+    twice (the second run needs the counters back at zero), then a different batch size on the same object."""
+    rng = np.random.default_rng(900 + batch)
+    lens = rng.integers(0, 1500, size=batch).astype(np.int32)
+    lens[::7] = 0
+    lens[1] = 9000  # cut by many CTAs
+    case = synth.paged_case(seed=43, batch=batch, len_lo=0, len_hi=0, seq_lens=lens)
+    got, k_np, v_np = _run_paged(compute, case, poison_unused=True)
+    ref = _oracle(case, k_np, v_np)
+    assert_attention_close(got, ref, f"batch {batch}")
+    assert not got[lens == 0].any()
+    again, _, _ = _run_paged(compute, case, poison_unused=True)
+    assert np.array_equal(got, again)
+    other = synth.paged_case(seed=44, batch=50, len_lo=200, len_hi=3000)
+    got2, k2, v2 = _run_paged(compute, other)
+    assert_attention_close(got2, _oracle(other, k2, v2), "batch 50 after it")
+
+
+def test_self_planned_batch_of_empty_sequences_and_a_bad_length(compute):
+    import granite_b200 as g
+    case = synth.paged_case(seed=45, batch=64, len_lo=0, len_hi=0, seq_lens=np.zeros(64, np.int32), spare_blocks=4)
+    got, _, _ = _run_paged(compute, case)
+    assert not got.any()  # every row is defined to be zero
+    case = synth.paged_case(seed=46, batch=64, len_lo=100, len_hi=400)
+    good = case.seq_lens.copy()
+    case.seq_lens[5] = case.max_blocks * synth.PAGE + 1
+    with pytest.raises(g.GraniteCudaError) as ei:
+        _run_paged(compute, case)
+    assert ei.value.code == g.ErrorCode.InvalidArgument
+    compute.sync()
+    case.seq_lens[:] = good
+    got, k_np, v_np = _run_paged(compute, case)
+    assert_attention_close(got, _oracle(case, k_np, v_np), "after the bad length")
 
 
 def test_unsupported_shapes_are_rejected(compute):
