@@ -702,7 +702,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int i = 0; i < 4; i++) sa[pp][nt][i] = sb[pp][nt][i] = 0.f;
                 kbase[pp] = smem_base + slot_k[pp] * slot_bytes + k_row * 128;
-                // the verdict is made warp-uniform: a lane that gave up must not leave the others to the
+                // the outcome is made warp-uniform: a lane that gave up must not leave the others to the
                 // warp-wide ldmatrix / shuffles that follow
                 if (has[pp] && !__all_sync(0xffffffffu, mbar_wait(&full[slot_k[pp]], ph_k[pp], abort_flag))) {
                     if (lane == 0) atomicOr(p.status, kStatusTimeout);
