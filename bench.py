@@ -342,6 +342,43 @@ def region_ms_per_launch(dev, step, reps: int, clocks: dict | None = None) -> fl
     return e0.elapsed_time(e1) / reps
 
 
+def measure_prefill_by_length(compute, dev, reps: int = 0):
+    """The prefill kernel at 2048 ... 16384 tokens (Hq 32, Hkv 8, D 128, fp16 in/out): the benchmark's 2048-token
+    launch spends a third of its 50 microseconds on start-up, drain and item boundaries (3.5 work items per CTA);
+    longer prompts show the pipeline's own rate.  Every length is timed as a burst of 10-30 ms (a loop of half a
+    second settles under the power cap: 764 TFLOP/s at 1462 MHz for 16384 tokens, 0.56 of the sustained peak)."""
+    import torch
+    hq, hkv, d = 32, 8, 128
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2002)
+    burst, sustained, kind = tensor_peak()
+    rows = []
+    for seq in (2048, 4096, 8192, 16384):
+        q = torch.randn((seq, hq, d), device=dev, generator=gen).half()
+        k = torch.randn((hkv, seq, d), device=dev, generator=gen).half()
+        v = torch.randn((hkv, seq, d), device=dev, generator=gen).half()
+        out = torch.zeros((seq, hq, d), device=dev, dtype=torch.float16)
+
+        def step(i):
+            compute.multihead_attention(q, k, v, out, hq, hkv, seq, seq, d, 1.0 / float(np.sqrt(d)), seq, q_dtype=1, out_dtype=1)
+
+        for i in range(3):
+            step(i)
+        compute.sync()
+        n = max(10, min(200, int(200 * (2048 / seq) ** 2)))  # about 10-30 ms per length: bursts, like the 2048-token figure
+        clocks = {}
+        ms = region_ms_per_launch(dev, step, n, clocks)
+        flops = 4 * d * hq * seq * (seq + 1) // 2
+        tf = flops / ms / 1e9
+        nb = seq // kT_ROWS
+        rows.append({"seq": seq, "kernel_ms": ms, "launches": n, "tflops": tf, "frac": tf / burst, "frac_of_sustained": tf / sustained,
+                     "kv_steps_per_cta": hq * nb * (nb + 1) / 2 / compute.sm_count, "items_per_cta": hq * nb / compute.sm_count,
+                     "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")})
+        del q, k, v, out
+    return {"workload": "prefill_causal_by_length", "kernel": "prefill_causal_fa", "bound": "tensor", "peak_tflops": burst,
+            "peak_tflops_sustained": sustained, "peak_kind": kind, "lengths": rows}
+
+
 def e2e_ms_per_call(dev, call, reps: int = 30) -> float:
     """Average duration of `call` (host buffers in, result out, sync inside) over `reps` calls, CUDA events."""
     import torch
@@ -853,7 +890,7 @@ def measure_long_context(compute, dev, dist, world: int, rank: int, steps: int =
     return res
 
 
-SECONDARY = {"generic": measure_generic, "single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
+SECONDARY = {"prefill_lengths": measure_prefill_by_length, "generic": measure_generic, "single_decode": measure_single_decode, "tree16": measure_tree16, "prefill": measure_prefill, "tree": measure_tree, "step_write": measure_decode_step_write,
              "paged_prefill": measure_paged_prefill}
 
 
@@ -867,7 +904,7 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "paged_decode_long_b256"],
                     help="paged_decode_long_b256: 256 sequences, log-uniform [4096, 131072], Hq 64, sharded "
                          "across the ranks by sequence (strong scaling); not the default benchmark line")
-    ap.add_argument("--only", default="", choices=["", "prefill", "tree", "tree16", "step_write", "paged_prefill", "single_decode", "generic"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "prefill_lengths", "tree", "tree16", "step_write", "paged_prefill", "single_decode", "generic"],
                     help="run just one of the secondary workloads (profiling captures)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (profiling captures)")
     ap.add_argument("--head-dim", type=int, default=0, choices=[0, 64, 128],
@@ -1086,6 +1123,7 @@ def main():
         if world == 1:
             with_cpu = not args.no_cpu_baseline
             secondary = {"prefill": measure_prefill(compute, dev, with_cpu=with_cpu),
+                         "prefill_by_length": measure_prefill_by_length(compute, dev),
                          "tree_verify": measure_tree(compute, dev, with_cpu=with_cpu),
                          "decode_step_cache_write": measure_decode_step_write(compute, dev),
                          "paged_prefill": measure_paged_prefill(compute, dev),
