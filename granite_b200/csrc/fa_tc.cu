@@ -88,7 +88,11 @@ constexpr int kMaxCachedItems = 32;  // work items of a CTA kept in shared memor
 
 struct TcSmem {
     uint64_t q_full, q_empty, k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages];
-    uint64_t s_full[2], s_free[2], p_ready[2], o_final;
+    uint64_t s_full[2], s_free[2], p_ready[2];
+    // "the item's output MMAs are done", one barrier per item parity: a deferred read-out waits for item r while
+    // item r + 1 runs, and a one-step item r + 1 could otherwise complete the same barrier a second time before a
+    // slow warp has looked at it (the wait would then block on a phase that never ends)
+    uint64_t o_final[2];
     uint32_t tmem_base;
     int abort_flag;
     TcItem items[kMaxCachedItems];  // item of round r, worked out once at start-up instead of by every role at every item boundary
@@ -232,7 +236,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             mbar_init(&sh->s_free[i], 2);
             mbar_init(&sh->p_ready[i], 256);
         }
-        mbar_init(&sh->o_final, 2);
+        mbar_init(&sh->o_final[0], 2);
+        mbar_init(&sh->o_final[1], 2);
         sh->abort_flag = 0;
         mbar_fence_init();
     }
@@ -446,6 +451,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     // one tile per item: O alternates between the two accumulators from item to item,
                     // so the previous item's result can be read out while this one accumulates
                     const uint32_t o_sel = kTiles == 1 ? (items_done & 1) : 0;
+                    uint64_t* o_final = &sh->o_final[items_done & 1];
                     items_done++;
                     for (int j = 0; j < it.n_steps && ok; j++) {
                         ok = mbar_wait(&sh->v_full[st], ph, abort_flag);
@@ -471,7 +477,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         }
                         if (!ok) break;
                         tc_commit(&sh->v_empty[st]);
-                        if (j + 1 == it.n_steps) tc_commit(&sh->o_final);
+                        if (j + 1 == it.n_steps) tc_commit(o_final);
                         if (++st == kStages) {
                             st = 0;
                             ph ^= 1;
@@ -504,7 +510,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         constexpr bool kDefer = kTiles == 1;
         struct Readout {
             int halves_left;     // 0: nothing pending
-            uint32_t phase;      // o_final parity of the item
+            uint64_t* o_final;   // the item's "output MMAs done" barrier ...
+            uint32_t phase;      // ... and its parity for this item
             uint32_t o_frag;     // the item's O accumulator, this warp's 16 lanes
             float inv[2];        // 1 / row sum of the thread's two rows
             bool store[2];       // the row is a live output row
@@ -514,7 +521,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         auto readout_half = [&](Readout& e) {
             const int h = p.d_chunks - e.halves_left;
             if (h == 0) {
-                if (ok) ok = mbar_wait(&sh->o_final, e.phase, abort_flag);
+                if (ok) ok = mbar_wait(e.o_final, e.phase, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tcgen05.ld below needs the whole warp
                 tc_fence_after_sync();
             }
@@ -750,7 +757,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
             for (int t = 0; t < kTiles; t++) {
                 Readout e;
                 e.halves_left = p.d_chunks;
-                e.phase = items_done & 1;
+                e.o_final = &sh->o_final[items_done & 1];
+                e.phase = (items_done >> 1) & 1;
                 e.o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
 #pragma unroll
                 for (int q = 0; q < 2; q++) {
