@@ -520,6 +520,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
         pend.halves_left = 0;
         auto readout_half = [&](Readout& e) {
             const int h = p.d_chunks - e.halves_left;
+            ok = __all_sync(0xffffffffu, ok);  // warp-uniform before anything that the whole warp must execute together
             if (h == 0) {
                 if (ok) ok = mbar_wait(e.o_final, e.phase, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tcgen05.ld below needs the whole warp
@@ -615,9 +616,10 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                     const int b = vs & 1;
                     const uint32_t s_frag = frag_base + b * kT;
                     const uint32_t o_frag = frag_base + 2 * kT + (t + o_sel) * kT;
-                    if (ok) ok = mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
-                    ok = __all_sync(0xffffffffu, ok);  // warp-uniform: everything below is warp-wide
-                    if (!ok) continue;  // a role gave up: nothing below synchronises with another warp
+                    // No vote and no early exit in the pace-setting loop (they cost 1-3 % of a launch): a wait that gives
+                    // up only clears the flag.  Every later wait then returns at once through the abort flag, the steps
+                    // that are left run on stale scores, and nothing of the item is stored (the read-out checks the flag).
+                    ok &= mbar_wait(&sh->s_full[b], (vs >> 1) & 1, abort_flag);
                     tc_fence_after_sync();
                     // the two rows' scores: x[h][4i + 2q + e] = row q, column 64 h + 8 i + 2 tq + e
                     uint32_t x[2][32];
@@ -668,7 +670,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         const bool grow0 = mx[0] > m_used[0] + kLazyLog2, grow1 = mx[1] > m_used[1] + kLazyLog2;
                         if (__any_sync(0xffffffffu, grow0 || grow1)) {
                             // O_t must be quiescent: wait until both halves of its previous output MMA are done
-                            ok = __all_sync(0xffffffffu, mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag));
+                            ok = __all_sync(0xffffffffu, ok && mbar_wait(&sh->s_free[(vs - kTiles) & 1], ((vs - kTiles) >> 1) & 1, abort_flag));
                             tc_fence_after_sync();
                             const float alpha0 = grow0 ? fast_exp2(m_used[0] - mx[0]) : 1.0f;
                             const float alpha1 = grow1 ? fast_exp2(m_used[1] - mx[1]) : 1.0f;
@@ -729,7 +731,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ C
                         // keys past the live length carry P = 0, but their V rows may hold anything (even
                         // NaN): zero them in shared memory before the MMAs read the tile
                         const int st = kvs % kStages;
-                        ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag));
+                        ok = __all_sync(0xffffffffu, ok && mbar_wait(&sh->v_full[st], (kvs / kStages) & 1, abort_flag));
                         const int first_bad = (kTree ? it.cache_len : p.seq_kv) - k0;
                         uint8_t* vt = v_smem + st * kTileBytes;
                         const int row_units = 8 * p.d_chunks;  // 16-byte units per V row
